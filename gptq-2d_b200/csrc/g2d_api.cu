@@ -1,0 +1,228 @@
+// C ABI of the sweep: argument checks, workspace carving and the launch schedule.
+#include <math.h>
+
+#include "g2d_common.cuh"
+
+#include <vector>
+
+namespace g2d {
+unsigned long long g_launches = 0;
+}
+
+using namespace g2d;
+
+namespace {
+
+// Optional per-launch timing of the fused sweep (profiling entry point only): one event pair per launch.
+struct LaunchTimer {
+    struct Item { cudaEvent_t begin, end; int kind; };
+    std::vector<Item> items;
+    cudaStream_t stream;
+    bool ok = true;
+    void begin(int kind) {
+        Item it{};
+        it.kind = kind;
+        ok = ok && cudaEventCreate(&it.begin) == cudaSuccess && cudaEventCreate(&it.end) == cudaSuccess;
+        if (ok) ok = cudaEventRecord(it.begin, stream) == cudaSuccess;
+        items.push_back(it);
+    }
+    void end() {
+        if (ok && !items.empty()) ok = cudaEventRecord(items.back().end, stream) == cudaSuccess;
+    }
+};
+
+// Algorithmic multiply-adds (x2 = flops) of one band update in tile mode: exact, no padding counted.
+double band_flops(int64_t m, int64_t n, int64_t s0, int64_t s1, int64_t s_end) {
+    const int64_t nI = ceil_div(m, TILE), nJ = ceil_div(n, TILE);
+    double flops = 0;
+    for (int64_t TI = 0; TI < nI; ++TI)
+        for (int64_t TJ = 0; TJ < nJ; ++TJ) {
+            if (TI + TJ < s1 || TI + TJ >= s_end) continue;
+            const double rows = (double)(TI == nI - 1 ? m - TI * TILE : TILE), cols = (double)(TJ == nJ - 1 ? n - TJ * TILE : TILE);
+            int64_t lo = s0 - TJ, hi = s1 - TJ;
+            lo = lo < 0 ? 0 : lo; hi = hi > TI ? TI : hi;
+            if (hi > lo) flops += 2.0 * rows * cols * (double)((hi - lo) * TILE);
+            lo = s0 - TI; hi = s1 - TI;
+            lo = lo < 0 ? 0 : lo; hi = hi > TJ ? TJ : hi;
+            if (hi > lo) flops += 2.0 * rows * cols * (double)((hi - lo) * TILE);
+        }
+    return flops;
+}
+
+constexpr int kDefaultOuterTiles = 8;  // tile anti-diagonals gathered into one far update (512 stages)
+
+inline size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
+
+int check_sweep(const g2d_sweep_desc *d) {
+    if (!d) return G2D_ERR_BAD_ARGUMENT;
+    if (d->dtype != G2D_F32 && d->dtype != G2D_F64) return G2D_ERR_BAD_ARGUMENT;
+    if (d->batch < 0 || d->m < 0 || d->n < 0) return G2D_ERR_BAD_ARGUMENT;
+    if (d->quant_kind != G2D_Q_ROUND && d->quant_kind != G2D_Q_AFFINE && d->quant_kind != G2D_Q_FORCED) return G2D_ERR_UNSUPPORTED;
+    if (d->outer_tiles < 0) return G2D_ERR_BAD_ARGUMENT;
+    return G2D_OK;
+}
+
+template <typename F>
+int sweep_fused(const g2d_sweep_desc *d, cudaStream_t stream, LaunchTimer *timer = nullptr, double *flops = nullptr) {
+    const int64_t count = d->batch * d->m * d->n;
+    const size_t plane = align256(sizeof(F) * (size_t)count);
+    if (!d->workspace || d->workspace_bytes < 2 * plane) return G2D_ERR_WORKSPACE;
+    if (((uintptr_t)d->workspace & 255) != 0) return G2D_ERR_WORKSPACE;
+    SweepArgs<F> a;
+    a.y = (F *)d->y;
+    a.c = (F *)d->workspace;
+    a.e = (F *)((char *)d->workspace + plane);
+    a.l = (const F *)d->l; a.u = (const F *)d->u;
+    a.l_off = d->l_offsets; a.u_off = d->u_offsets;
+    a.scale = (const F *)d->scale; a.zero = (const F *)d->zero;
+    a.scale_off = d->scale_offsets; a.zero_off = d->zero_offsets;
+    a.srs = d->scale_row_stride; a.scs = d->scale_col_stride; a.zrs = d->zero_row_stride; a.zcs = d->zero_col_stride;
+    a.forced = (const F *)d->forced_z;
+    a.y_pre = (F *)d->y_pre;
+    a.qmin = (F)d->qmin; a.qmax = (F)d->qmax;
+    a.kind = d->quant_kind;
+    a.batch = d->batch; a.m = d->m; a.n = d->n;
+    a.nI = (int)ceil_div(d->m, TILE); a.nJ = (int)ceil_div(d->n, TILE);
+    if (cudaMemsetAsync(a.c, 0, sizeof(F) * (size_t)count, stream) != cudaSuccess) return G2D_ERR_CUDA;
+
+    BandArgs<F> b;
+    b.y = a.y; b.c = a.c; b.e = a.e; b.l = a.l; b.u = a.u; b.l_off = a.l_off; b.u_off = a.u_off;
+    b.batch = a.batch; b.m = a.m; b.n = a.n; b.P = TILE; b.Q = TILE; b.down_into_y = 0; b.mode = BAND_TILE;
+
+    const int waves = a.nI + a.nJ - 1;
+    const int outer = d->outer_tiles > 0 ? d->outer_tiles : kDefaultOuterTiles;
+    for (int S0 = 0; S0 < waves; S0 += outer) {
+        const int S1 = S0 + outer < waves ? S0 + outer : waves;
+        for (int S = S0; S < S1; ++S) {
+            if (timer) timer->begin(0);
+            int status = launch_tile_sweep<F>(a, S, stream);
+            if (timer) timer->end();
+            if (status != G2D_OK) return status;
+            if (S + 1 < S1) {  // near update: into the rest of the outer group
+                b.s0 = S; b.s1 = S + 1; b.s_end = S1;
+                if (timer) timer->begin(1);
+                status = launch_band_update<F>(b, stream);
+                if (timer) timer->end();
+                if (flops) flops[1] += band_flops(d->m, d->n, b.s0, b.s1, b.s_end) * (double)d->batch;
+                if (status != G2D_OK) return status;
+            }
+        }
+        if (S1 < waves) {  // far update: the whole group into everything after it
+            b.s0 = S0; b.s1 = S1; b.s_end = waves;
+            if (timer) timer->begin(2);
+            const int status = launch_band_update<F>(b, stream);
+            if (timer) timer->end();
+            if (flops) flops[2] += band_flops(d->m, d->n, b.s0, b.s1, b.s_end) * (double)d->batch;
+            if (status != G2D_OK) return status;
+        }
+    }
+    return G2D_OK;
+}
+
+int check_stage(const g2d_stage_desc *d) {
+    if (!d) return G2D_ERR_BAD_ARGUMENT;
+    if (d->dtype != G2D_F32 && d->dtype != G2D_F64) return G2D_ERR_BAD_ARGUMENT;
+    if (d->batch < 0 || d->m < 0 || d->n < 0 || d->p <= 0 || d->q <= 0) return G2D_ERR_BAD_ARGUMENT;
+    if (d->m % d->p || d->n % d->q) return G2D_ERR_BAD_ARGUMENT;
+    return G2D_OK;
+}
+
+template <typename F>
+int stage_flush(const g2d_stage_desc *d, int64_t s0, int64_t s1, int64_t s_end, cudaStream_t stream) {
+    BandArgs<F> b;
+    b.y = (F *)d->y; b.c = (F *)d->c; b.e = (const F *)d->e;
+    b.l = (const F *)d->l; b.u = (const F *)d->u; b.l_off = d->l_offsets; b.u_off = d->u_offsets;
+    b.batch = d->batch; b.m = d->m; b.n = d->n; b.P = d->p; b.Q = d->q;
+    b.s0 = s0; b.s1 = s1; b.s_end = s_end; b.down_into_y = 1;
+    b.mode = (d->p == 1 && d->q == 1) ? BAND_PLAIN : BAND_GENERAL;
+    return launch_band_update<F>(b, stream);
+}
+
+}  // namespace
+
+extern "C" const char *g2d_status_string(int status) {
+    switch (status) {
+    case G2D_OK: return "ok";
+    case G2D_ERR_BAD_ARGUMENT: return "bad argument";
+    case G2D_ERR_WORKSPACE: return "workspace missing, misaligned or too small";
+    case G2D_ERR_UNSUPPORTED: return "unsupported combination";
+    case G2D_ERR_CUDA: return "CUDA runtime error";
+    case G2D_ERR_TOO_LARGE: return "size exceeds a fixed maximum";
+    default: return "unknown status";
+    }
+}
+
+extern "C" int g2d_abi_version(void) { return 1; }
+
+extern "C" int g2d_sweep_workspace_bytes(const g2d_sweep_desc *desc, size_t *bytes) {
+    const int status = check_sweep(desc);
+    if (status != G2D_OK || !bytes) return status != G2D_OK ? status : G2D_ERR_BAD_ARGUMENT;
+    const size_t elem = desc->dtype == G2D_F32 ? 4 : 8;
+    *bytes = 2 * align256(elem * (size_t)(desc->batch * desc->m * desc->n));
+    return G2D_OK;
+}
+
+extern "C" int g2d_sweep_fused(const g2d_sweep_desc *desc, void *stream) {
+    const int status = check_sweep(desc);
+    if (status != G2D_OK) return status;
+    if (desc->batch == 0 || desc->m == 0 || desc->n == 0) return G2D_OK;
+    if (!desc->y || !desc->l || !desc->u) return G2D_ERR_BAD_ARGUMENT;
+    if (desc->quant_kind == G2D_Q_AFFINE && (!desc->scale || !desc->zero || !(desc->qmin < desc->qmax))) return G2D_ERR_BAD_ARGUMENT;
+    if (desc->quant_kind == G2D_Q_FORCED && !desc->forced_z) return G2D_ERR_BAD_ARGUMENT;
+    if ((desc->m + TILE - 1) / TILE + (desc->n + TILE - 1) / TILE > 60000) return G2D_ERR_TOO_LARGE;
+    cudaStream_t st = (cudaStream_t)stream;
+    return desc->dtype == G2D_F32 ? sweep_fused<float>(desc, st) : sweep_fused<double>(desc, st);
+}
+
+extern "C" unsigned long long g2d_launch_count(void) { return g_launches; }
+
+extern "C" int g2d_sweep_fused_profile(const g2d_sweep_desc *desc, void *stream, double *out) {
+    int status = check_sweep(desc);
+    if (status != G2D_OK) return status;
+    if (!out) return G2D_ERR_BAD_ARGUMENT;
+    for (int i = 0; i < 9; ++i) out[i] = 0;
+    if (desc->batch == 0 || desc->m == 0 || desc->n == 0) return G2D_OK;
+    if (!desc->y || !desc->l || !desc->u) return G2D_ERR_BAD_ARGUMENT;
+    cudaStream_t st = (cudaStream_t)stream;
+    LaunchTimer timer;
+    timer.stream = st;
+    double flops[3] = {0, 0, 0};
+    status = desc->dtype == G2D_F32 ? sweep_fused<float>(desc, st, &timer, flops) : sweep_fused<double>(desc, st, &timer, flops);
+    if (cudaStreamSynchronize(st) != cudaSuccess) status = status == G2D_OK ? G2D_ERR_CUDA : status;
+    for (auto &it : timer.items) {
+        float ms = 0;
+        if (status == G2D_OK && timer.ok && cudaEventElapsedTime(&ms, it.begin, it.end) == cudaSuccess) {
+            out[it.kind] += ms;
+            out[3 + it.kind] += 1;
+        }
+        if (it.begin) cudaEventDestroy(it.begin);
+        if (it.end) cudaEventDestroy(it.end);
+    }
+    out[7] = flops[1];
+    out[8] = flops[2];
+    const double mm = (double)desc->m, nn = (double)desc->n;
+    out[6] = mm * nn * (mm + nn - 2) * (double)desc->batch;  // algorithmic flops of the whole sweep
+    if (!timer.ok && status == G2D_OK) status = G2D_ERR_CUDA;
+    return status;
+}
+
+extern "C" int g2d_stage_push(const g2d_stage_desc *desc, const void *z, int64_t s, int64_t s1, void *stream) {
+    const int status = check_stage(desc);
+    if (status != G2D_OK) return status;
+    if (desc->batch == 0 || desc->m == 0 || desc->n == 0) return G2D_OK;
+    if (!desc->y || !desc->c || !desc->e || !desc->l || !desc->u || !z) return G2D_ERR_BAD_ARGUMENT;
+    cudaStream_t st = (cudaStream_t)stream;
+    return desc->dtype == G2D_F32 ? launch_stage_push<float>(*desc, (const float *)z, s, s1, st)
+                                  : launch_stage_push<double>(*desc, (const double *)z, s, s1, st);
+}
+
+extern "C" int g2d_stage_flush(const g2d_stage_desc *desc, int64_t s0, int64_t s1, int64_t s_end, void *stream) {
+    const int status = check_stage(desc);
+    if (status != G2D_OK) return status;
+    if (desc->batch == 0 || desc->m == 0 || desc->n == 0) return G2D_OK;
+    if (!desc->y || !desc->c || !desc->e || !desc->l || !desc->u) return G2D_ERR_BAD_ARGUMENT;
+    if (s0 < 0 || s1 <= s0 || s_end < s1) return G2D_ERR_BAD_ARGUMENT;
+    if (s_end == s1) return G2D_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    return desc->dtype == G2D_F32 ? stage_flush<float>(desc, s0, s1, s_end, st) : stage_flush<double>(desc, s0, s1, s_end, st);
+}

@@ -1,0 +1,105 @@
+// Shared definitions of the gptq2d_b200 kernels (sm_100a).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/gptq2d_b200.h"
+
+namespace g2d {
+
+// Geometry of the fused sweep: the matrix is cut into TILE x TILE tiles that are
+// swept one tile anti-diagonal at a time; inside a tile, SUB x SUB sub-tiles are
+// swept by one warp each, again along anti-diagonals.
+constexpr int TILE = 64;
+constexpr int SUB = 16;
+constexpr int NSUB = TILE / SUB;
+constexpr int LD = TILE + 4;  // shared-memory row stride: LD + 1 odd keeps the diagonal walks conflict free
+
+__host__ __device__ inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+// IEEE round-to-nearest-even primitives that the compiler may not contract or approximate.
+__device__ __forceinline__ float div_rn(float a, float b) { return __fdiv_rn(a, b); }
+__device__ __forceinline__ double div_rn(double a, double b) { return __ddiv_rn(a, b); }
+__device__ __forceinline__ float add_rn(float a, float b) { return __fadd_rn(a, b); }
+__device__ __forceinline__ double add_rn(double a, double b) { return __dadd_rn(a, b); }
+__device__ __forceinline__ float sub_rn(float a, float b) { return __fsub_rn(a, b); }
+__device__ __forceinline__ double sub_rn(double a, double b) { return __dsub_rn(a, b); }
+__device__ __forceinline__ float mul_rn(float a, float b) { return __fmul_rn(a, b); }
+__device__ __forceinline__ double mul_rn(double a, double b) { return __dmul_rn(a, b); }
+__device__ __forceinline__ float rint_even(float a) { return rintf(a); }
+__device__ __forceinline__ double rint_even(double a) { return rint(a); }
+
+// (clamp(rint(y / scale + zp), qmin, qmax) - zp) * scale, every step rounded on its own
+// (quantizer_int.py:81-83 / :204-205 of the reference).  Comparisons keep NaN like torch.clamp.
+template <typename F>
+__device__ __forceinline__ F affine_value(F y, F scale, F zp, F qmin, F qmax) {
+    F t = rint_even(add_rn(div_rn(y, scale), zp));
+    t = t < qmin ? qmin : t;
+    t = t > qmax ? qmax : t;
+    return mul_rn(sub_rn(t, zp), scale);
+}
+
+// float -> fp16 / bf16 -> float, round to nearest even (denormals kept).
+__device__ __forceinline__ float round_to_half(float f, int half_kind) {
+    return half_kind == G2D_BF16 ? __bfloat162float(__float2bfloat16_rn(f)) : __half2float(__float2half_rn(f));
+}
+
+// absmax / ((qmax - qmin) / 2) rounded to a 16-bit float through fp32, 0 -> 1 (quantizer_int.py:110-117, :357-363).
+template <typename F>
+__device__ __forceinline__ F absmax_scale_value(F absmax, F divisor, int half_kind) {
+    F s = (F)round_to_half((float)div_rn(absmax, divisor), half_kind);
+    return s == (F)0 ? (F)1 : s;
+}
+
+// Kernel launches made by this library in this process (read by g2d_launch_count).
+extern unsigned long long g_launches;
+inline int check_launch() {
+    ++g_launches;
+    return cudaPeekAtLastError() == cudaSuccess ? G2D_OK : G2D_ERR_CUDA;
+}
+
+// ---- launchers implemented in the .cu files -------------------------------------------------
+
+template <typename F>
+struct SweepArgs {
+    F *y, *c, *e;  // [batch, m, n] each: Y = X + right feedback (Z where done), C = down feedback, E = errors
+    const F *l, *u;
+    const int64_t *l_off, *u_off;
+    const F *scale, *zero;
+    const int64_t *scale_off, *zero_off;
+    int64_t srs, scs, zrs, zcs;
+    const F *forced;
+    F *y_pre;
+    F qmin, qmax;
+    int kind;
+    int64_t batch, m, n;
+    int nI, nJ;  // tiles per column / per row
+};
+
+template <typename F>
+int launch_tile_sweep(const SweepArgs<F> &args, int S, cudaStream_t stream);
+
+enum BandMode { BAND_TILE = 0, BAND_PLAIN = 1, BAND_GENERAL = 2 };
+
+template <typename F>
+struct BandArgs {
+    F *y, *c;
+    const F *e, *l, *u;
+    const int64_t *l_off, *u_off;
+    int64_t batch, m, n;
+    int P, Q;                 // stage(i, j) = i / P + j / Q
+    int64_t s0, s1, s_end;    // sources s0..s1-1, targets s1..s_end-1
+    int down_into_y;          // also add the down product into Y (the generic path keeps Y live)
+    int mode;                 // BandMode
+};
+
+template <typename F>
+int launch_band_update(const BandArgs<F> &args, cudaStream_t stream);
+
+template <typename F>
+int launch_stage_push(const g2d_stage_desc &d, const F *z, int64_t s, int64_t s1, cudaStream_t stream);
+
+}  // namespace g2d

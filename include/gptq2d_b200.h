@@ -1,0 +1,167 @@
+/*
+ * gptq2d_b200 -- C ABI of the B200 (sm_100a) GPTQ-2D rounding engine.
+ *
+ * Every entry point is extern "C", takes plain device pointers and sizes,
+ * launches its kernels asynchronously on the CUDA stream it is given, never
+ * allocates, never synchronizes and never reads device memory from the host,
+ * so a call can be captured in a CUDA graph.  Buffers are owned by the caller.
+ * Return value: 0 (G2D_OK) or a negative g2d_status; g2d_status_string names it.
+ *
+ * Each declaration cites the function of the reference (IST-DASLab/GPTQ-2D,
+ * file:line within that project) whose work it replaces.
+ */
+#ifndef GPTQ2D_B200_H
+#define GPTQ2D_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum g2d_status {
+    G2D_OK = 0,
+    G2D_ERR_BAD_ARGUMENT = -1,   /* a size, stride, enum or pointer is invalid */
+    G2D_ERR_WORKSPACE = -2,      /* workspace pointer missing or too small */
+    G2D_ERR_UNSUPPORTED = -3,    /* a combination this build does not implement */
+    G2D_ERR_CUDA = -4,           /* a CUDA runtime call failed (launch, attribute) */
+    G2D_ERR_TOO_LARGE = -5       /* a size exceeds a documented fixed maximum */
+} g2d_status;
+
+typedef enum g2d_dtype { G2D_F32 = 0, G2D_F64 = 1 } g2d_dtype;
+typedef enum g2d_half { G2D_FP16 = 0, G2D_BF16 = 1 } g2d_half;
+
+typedef enum g2d_quant_kind {
+    G2D_Q_ROUND = 0,   /* quantizer_int.py:18-35  round half to even */
+    G2D_Q_AFFINE = 1,  /* quantizer_int.py:63-107 (clamp(rint(y/scale + zp), qmin, qmax) - zp) * scale */
+    G2D_Q_FORCED = 4   /* commit the given values (teacher-forced replay for parity checks) */
+} g2d_quant_kind;
+
+/* One batched sweep problem.  Matrices are row-major; batch b of a [batch, m, n]
+ * buffer starts b*m*n elements in.  L, U, scale and zero point are addressed as
+ * base + offsets[b] (element offsets, device array of `batch` int64) so that
+ * broadcast batch dimensions are not copied; a NULL offsets pointer means 0. */
+typedef struct g2d_sweep_desc {
+    int32_t dtype;               /* g2d_dtype shared by every floating-point buffer */
+    int32_t quant_kind;          /* g2d_quant_kind */
+    int64_t batch, m, n;
+    void *y;                     /* [batch, m, n]: X on entry, Z on return */
+    const void *l;               /* [.., m, m] unit lower; read only strictly below the diagonal */
+    const int64_t *l_offsets;
+    const void *u;               /* [.., n, n] unit upper; read only strictly above the diagonal */
+    const int64_t *u_offsets;
+    const void *scale;           /* AFFINE: [.., m, n] through (scale_row_stride, scale_col_stride) */
+    const int64_t *scale_offsets;
+    const void *zero;            /* AFFINE: zero points, same addressing with its own strides */
+    const int64_t *zero_offsets;
+    int64_t scale_row_stride, scale_col_stride, zero_row_stride, zero_col_stride;
+    double qmin, qmax;           /* AFFINE clamp; +-infinity disables it */
+    const void *forced_z;        /* FORCED: [batch, m, n] values to commit */
+    void *y_pre;                 /* optional [batch, m, n]: every entry's value when it was rounded */
+    void *workspace;             /* g2d_sweep_workspace_bytes() bytes, 256-byte aligned */
+    size_t workspace_bytes;
+    int32_t outer_tiles;         /* tile anti-diagonals per far update; 0 selects the default */
+    int32_t reserved;
+} g2d_sweep_desc;
+
+const char *g2d_status_string(int status);
+/* ABI version of this header: bumped whenever a struct or signature changes. */
+int g2d_abi_version(void);
+
+/* Fused tile-wavefront sweep with the quantizer inside the kernels.
+ * Replaces gptq_2d (gptq_2d.py:1379-1418) = _gptq_2d_blocked (:1295-1375) with its per-stage
+ * quantizer call and the kernels _push_kernel (:243), _add_own_errors_kernel (:381),
+ * _repack_errors_kernel (:632), _flush_down_kernel (:765), _flush_right_kernel (:935),
+ * for quantizers this library knows: round_quantizer (quantizer_int.py:18) and
+ * affine_quantizer_torch/_triton (quantizer_int.py:63, :208). */
+int g2d_sweep_workspace_bytes(const g2d_sweep_desc *desc, size_t *bytes);
+int g2d_sweep_fused(const g2d_sweep_desc *desc, void *stream);
+
+/* Profiling variant of g2d_sweep_fused (no counterpart in the reference): the same launches, each
+ * bracketed by a CUDA event pair on `stream`; synchronizes the stream before returning, so it cannot be
+ * captured.  out[0..2] = total milliseconds of the tile-sweep / near-update / far-update launches,
+ * out[3..5] = their launch counts, out[6] = algorithmic flops of the whole sweep m n (m + n - 2) per
+ * batch, out[7], out[8] = algorithmic flops executed by the near / far updates. */
+int g2d_sweep_fused_profile(const g2d_sweep_desc *desc, void *stream, double *out);
+
+/* Kernel launches made by this library in this process so far (host-side counter). */
+unsigned long long g2d_launch_count(void);
+
+/* Generic per-stage path: the caller's own quantizer runs between these calls, one coarse
+ * anti-diagonal (stage) at a time, and sees live Y as the reference promises (gptq_2d.py:1395-1400).
+ * Geometry shared by the three calls. y, c, e are [batch, m, n]; c must start at zero. */
+typedef struct g2d_stage_desc {
+    int32_t dtype;
+    int32_t p, q;                /* super-entry shape; 1, 1 for plain entries */
+    int32_t reserved;
+    int64_t batch, m, n;
+    void *y;                     /* live Y (X plus every push so far; quantized where done) */
+    void *c;                     /* running buffer C = L E (gptq_2d.py:1324) */
+    void *e;                     /* errors E of every finished entry, natural [batch, m, n] layout */
+    const void *l;
+    const int64_t *l_offsets;
+    const void *u;
+    const int64_t *u_offsets;
+} g2d_stage_desc;
+
+/* Stage s of the block [.., s1): take the quantized values z ([batch, d, p, q] contiguous, d the
+ * number of super-entries of the stage), form E = z - Y, complete C on the sources, commit Y = z,
+ * and push the errors down through L and the completed C right through U to the stages s+1..s1-1.
+ * Replaces _push_kernel (gptq_2d.py:243-346) + _add_own_errors_kernel (:381-409) for plain entries and
+ * _push_down_super_entry_kernel (:428-505) + _push_right_super_entry_kernel (:536-601) otherwise. */
+int g2d_stage_push(const g2d_stage_desc *desc, const void *z, int64_t s, int64_t s1, void *stream);
+
+/* Apply the errors of the stages s0..s1-1 to the stages s1..s_end-1: C += L E and Y += L E + C U with
+ * the sums restricted to the sources of those stages.  Replaces _flush_block (gptq_2d.py:1090-1119) =
+ * _repack_errors_kernel (:632) + _flush_down_kernel (:765) + _flush_right_kernel (:935). */
+int g2d_stage_flush(const g2d_stage_desc *desc, int64_t s0, int64_t s1, int64_t s_end, void *stream);
+
+/* Strided affine quantizer: out[b, k] = affine(y[b*matrix_size + start + k*step]) for k < count, with
+ * scale / zero point read at the same position of their own matrices (base + offsets[b]).
+ * Replaces _affine_quantize_kernel (quantizer_int.py:160-205). */
+int g2d_affine_quantize(int dtype, int64_t batch, int64_t matrix_size, int64_t start, int64_t step, int64_t count,
+                        const void *y, const void *scale, const int64_t *scale_offsets, const void *zero,
+                        const int64_t *zero_offsets, double qmin, double qmax, void *out, void *stream);
+
+/* Super-entry affine quantizer: entry (k, r, c) of the selection lies k*stride_d + r*stride_p + c*stride_q
+ * past `first` in Y, scale and zero point alike; out is [batch, d, p, q] contiguous.
+ * Replaces _affine_quantize_super_entry_kernel (quantizer_int.py:247-299). */
+int g2d_affine_quantize_super_entry(int dtype, int64_t batch, int64_t matrix_size, int64_t first, int64_t d, int32_t p,
+                                    int32_t q, int64_t stride_d, int64_t stride_p, int64_t stride_q, const void *y,
+                                    const void *scale, const int64_t *scale_offsets, const void *zero,
+                                    const int64_t *zero_offsets, double qmin, double qmax, void *out, void *stream);
+
+/* Row scales absmax / ((qmax - qmin) / 2), rounded to fp16 / bf16 through fp32, 0 -> 1.
+ * Replaces _int_abs_max_scale_kernel (quantizer_int.py:357-385). */
+int g2d_absmax_scale(int dtype, int64_t rows, int64_t size, int64_t row_stride, int64_t col_stride, const void *x,
+                     double qmin, double qmax, int half, void *out, void *stream);
+
+/* Dynamic abs-max rounding of every row of the selected super-entries.
+ * Replaces _int_abs_max_quantize_kernel (quantizer_int.py:407-439). */
+int g2d_absmax_quantize_super_entry(int dtype, int64_t batch, int64_t matrix_size, int64_t first, int64_t d, int32_t p,
+                                    int32_t q, int64_t stride_d, int64_t stride_p, int64_t stride_q, const void *y,
+                                    double qmin, double qmax, int half, void *out, void *stream);
+
+/* Bitshift-trellis (Viterbi) search of `rows` sequences of T values: out = scale[row] * values of the
+ * closest path, states optional ([rows, T/V] int64).  table is [2^L, V] in dtype, V <= 2, K*V <= 8.
+ * workspace: g2d_trellis_workspace_bytes().  Replaces _viterbi_step_kernel, _viterbi_final_kernel and
+ * _viterbi_backtrack_kernel (quantizer_trellis.py:146-268) as driven by _trellis_quantize_triton (:271-341). */
+int g2d_trellis_workspace_bytes(int dtype, int64_t rows, int32_t T, int32_t L, int32_t K, int32_t V, size_t *bytes);
+int g2d_trellis_quantize(int dtype, int64_t rows, int32_t T, const void *x, const void *table, int32_t L, int32_t K,
+                         int32_t V, int32_t tail_biting, const void *scale, void *out, int64_t *states,
+                         void *workspace, size_t workspace_bytes, void *stream);
+
+/* Unit (block) lower triangular factor of the inverse of a symmetric positive definite matrix:
+ * a^{-1} = out Lambda out^T with size x size identity diagonal blocks.  a is [n, n] and is overwritten
+ * (scratch); workspace: g2d_ldl_workspace_bytes().  status_flag (device int32, may be NULL) receives the
+ * 1-based index of a non-positive pivot, or stays 0.
+ * Replaces ldl_of_inverse (gptq_2d_reference.py:41-49) with _unit_diagonal_blocks (:29-38). */
+int g2d_ldl_workspace_bytes(int dtype, int64_t n, size_t *bytes);
+int g2d_ldl_of_inverse(int dtype, int64_t n, void *a, int32_t size, void *out, int32_t *status_flag, void *workspace,
+                       size_t workspace_bytes, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GPTQ2D_B200_H */
