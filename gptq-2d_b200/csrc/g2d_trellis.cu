@@ -1,0 +1,259 @@
+// Bitshift-trellis (QTIP) quantizer: Viterbi search as a shared-memory dynamic program.
+//
+// Replaces _viterbi_step_kernel / _viterbi_final_kernel / _viterbi_backtrack_kernel of the reference
+// (quantizer_trellis.py:146-268) and reproduces _trellis_quantize_torch (:121-143) bit for bit: costs are
+// (table - x)^2 summed over the V <= 2 values without fused multiply-adds, the running cost is added last,
+// and every minimum takes the first index among equals.
+//
+// A state is an L-bit window; a step shifts in KV = K*V bits, so state s has the predecessors
+// h * G + (s >> KV), h < 2^KV, G = 2^(L-KV).  All 2^KV states that share (s >> KV)... equivalently, the cost of a
+// state is the minimum over its group of predecessors plus its own local cost, so only the G group minima
+// of every step are kept:  B_t[g] = min_h (B_{t-1}[(h G + g) >> KV] + local_t[h G + g]).
+// One CTA runs R sequences at once: B_t and B_{t-1} of each live in shared memory (2 R G values), every
+// table entry is loaded once per step for all R sequences, and one barrier separates the steps.  The
+// arg-min h of every (step, group) goes to global scratch (one byte each) for the walk back.
+#include "g2d_common.cuh"
+
+namespace g2d {
+
+constexpr int VT = 512;  // threads per CTA
+
+template <typename F>
+__device__ __forceinline__ F local_cost(const F *__restrict__ table, int64_t s, int V, F x0, F x1) {
+    const F d0 = sub_rn(table[s * V], x0);
+    F c = mul_rn(d0, d0);
+    if (V == 2) {
+        const F d1 = sub_rn(table[s * V + 1], x1);
+        c = add_rn(c, mul_rn(d1, d1));
+    }
+    return c;
+}
+
+template <typename F>
+__device__ __forceinline__ F pos_inf() { return (F)INFINITY; }
+
+template <typename F, int R>
+__global__ void __launch_bounds__(VT) viterbi_kernel(int64_t rows, int T, const F *__restrict__ x, const F *__restrict__ table,
+                                                     int Lbits, int shift, int V, int tail_biting, const F *__restrict__ scale,
+                                                     F *__restrict__ out, int64_t *__restrict__ states, uint8_t *__restrict__ choices) {
+    extern __shared__ __align__(16) unsigned char g2d_vsmem[];
+    const int64_t S = (int64_t)1 << Lbits, G = S >> shift;
+    const int H = 1 << shift;
+    const int steps = T / V;
+    F *B = reinterpret_cast<F *>(g2d_vsmem);  // [2][R][G]
+    __shared__ F red_val[VT / 32][R];
+    __shared__ long long red_arg[VT / 32][R];
+    __shared__ long long seq_state[R];    // state at the step the walk back starts from / stops at
+    __shared__ long long seq_overlap[R];  // tail-biting overlap bits, -1 when unconstrained
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int64_t slots = steps > 1 ? steps - 1 : 1;
+
+    for (int64_t row0 = (int64_t)blockIdx.x * R; row0 < rows; row0 += (int64_t)gridDim.x * R) {
+        if (tid < R) seq_overlap[tid] = -1;
+        __syncthreads();
+        for (int pass = tail_biting ? 0 : 1; pass < 2; ++pass) {
+            const int half = steps / 2;
+            const int roll = pass == 0 ? steps - half : 0;
+            const int stop = pass == 0 ? half : 0;
+            // ---- forward: group minima of the steps 0 .. steps-2 ----
+            for (int t = 0; t + 1 < steps; ++t) {
+                const F *prev = B + (size_t)((t + 1) & 1) * R * G;
+                F *next = B + (size_t)(t & 1) * R * G;
+                F x0[R], x1[R];
+                long long ov[R];
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    const int64_t row = row0 + r < rows ? row0 + r : rows - 1;
+                    const F *xt = x + row * T + (int64_t)((t + roll) % steps) * V;
+                    x0[r] = xt[0];
+                    x1[r] = V == 2 ? xt[1] : (F)0;
+                    ov[r] = seq_overlap[r];
+                }
+                for (int64_t g = tid; g < G; g += VT) {
+                    F best[R];
+                    int arg[R];
+#pragma unroll
+                    for (int r = 0; r < R; ++r) { best[r] = pos_inf<F>(); arg[r] = 0; }
+                    for (int h = 0; h < H; ++h) {
+                        const int64_t s = (int64_t)h * G + g;
+                        const F t0 = table[s * V], t1 = V == 2 ? table[s * V + 1] : (F)0;
+                        const int64_t low = s >> shift;
+#pragma unroll
+                        for (int r = 0; r < R; ++r) {
+                            const F d0 = sub_rn(t0, x0[r]);
+                            F c = mul_rn(d0, d0);
+                            if (V == 2) {
+                                const F d1 = sub_rn(t1, x1[r]);
+                                c = add_rn(c, mul_rn(d1, d1));
+                            }
+                            if (t == 0) {
+                                if (ov[r] >= 0 && low != ov[r]) c = pos_inf<F>();
+                            } else {
+                                c = add_rn(prev[(size_t)r * G + low], c);
+                            }
+                            if (h == 0 || c < best[r]) { best[r] = c; arg[r] = h; }
+                        }
+                    }
+#pragma unroll
+                    for (int r = 0; r < R; ++r) {
+                        next[(size_t)r * G + g] = best[r];
+                        if (row0 + r < rows) choices[((row0 + r) * slots + t) * G + g] = (uint8_t)arg[r];
+                    }
+                }
+                __syncthreads();
+            }
+            // ---- last step: first arg-min over all states, with the final mask ----
+            {
+                const int t = steps - 1;
+                const F *prev = B + (size_t)((t + 1) & 1) * R * G;
+                F best[R];
+                long long arg[R];
+#pragma unroll
+                for (int r = 0; r < R; ++r) { best[r] = pos_inf<F>(); arg[r] = S; }
+                F x0[R], x1[R];
+                long long ov[R];
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    const int64_t row = row0 + r < rows ? row0 + r : rows - 1;
+                    const F *xt = x + row * T + (int64_t)((t + roll) % steps) * V;
+                    x0[r] = xt[0];
+                    x1[r] = V == 2 ? xt[1] : (F)0;
+                    ov[r] = seq_overlap[r];
+                }
+                for (int64_t s = tid; s < S; s += VT) {
+                    const F t0 = table[s * V], t1 = V == 2 ? table[s * V + 1] : (F)0;
+                    const int64_t low = s >> shift;
+#pragma unroll
+                    for (int r = 0; r < R; ++r) {
+                        const F d0 = sub_rn(t0, x0[r]);
+                        F c = mul_rn(d0, d0);
+                        if (V == 2) {
+                            const F d1 = sub_rn(t1, x1[r]);
+                            c = add_rn(c, mul_rn(d1, d1));
+                        }
+                        if (t == 0) {
+                            if (ov[r] >= 0 && low != ov[r]) c = pos_inf<F>();
+                        } else {
+                            c = add_rn(prev[(size_t)r * G + low], c);
+                        }
+                        if (ov[r] >= 0 && (s & (G - 1)) != ov[r]) c = pos_inf<F>();
+                        // ascending s within a thread: strict < keeps the first minimum
+                        if (arg[r] == S || c < best[r]) { best[r] = c; arg[r] = s; }
+                    }
+                }
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    F b = best[r];
+                    long long a = arg[r];
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) {
+                        const F ob = __shfl_xor_sync(0xffffffffu, b, o);
+                        const long long oa = __shfl_xor_sync(0xffffffffu, a, o);
+                        if (oa < S && (a >= S || ob < b || (ob == b && oa < a))) { b = ob; a = oa; }
+                    }
+                    if (lane == 0) { red_val[warp][r] = b; red_arg[warp][r] = a; }
+                }
+                __syncthreads();
+                if (tid < R) {
+                    F b = red_val[0][tid];
+                    long long a = red_arg[0][tid];
+                    for (int w = 1; w < VT / 32; ++w) {
+                        const F ob = red_val[w][tid];
+                        const long long oa = red_arg[w][tid];
+                        if (oa < S && (a >= S || ob < b || (ob == b && oa < a))) { b = ob; a = oa; }
+                    }
+                    seq_state[tid] = a;
+                }
+                __syncthreads();
+            }
+            // ---- walk back: thread r follows sequence r ----
+            if (tid < R && row0 + tid < rows) {
+                const int64_t row = row0 + tid;
+                long long state = seq_state[tid];
+                const F sc = scale ? scale[row] : (F)1;
+                for (int t = steps - 1; t >= stop; --t) {
+                    if (pass == 1) {
+                        for (int v = 0; v < V; ++v) out[row * T + (int64_t)t * V + v] = mul_rn(table[state * V + v], sc);
+                        if (states) states[row * steps + t] = state;
+                    }
+                    if (t > stop) {
+                        const long long low = state >> shift;
+                        state = (long long)choices[(row * slots + (t - 1)) * G + low] * G + low;
+                    }
+                }
+                if (pass == 0) seq_overlap[tid] = state >> shift;
+            }
+            __syncthreads();
+        }
+    }
+}
+
+template <typename F, int R>
+static int launch_viterbi(int64_t rows, int T, const void *x, const void *table, int L, int K, int V, int tail, const void *scale,
+                          void *out, int64_t *states, void *workspace, cudaStream_t st) {
+    static bool configured[64] = {};
+    const int64_t G = ((int64_t)1 << L) >> (K * V);
+    const size_t smem = sizeof(F) * 2 * R * (size_t)G;
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return G2D_ERR_CUDA;
+    if (!configured[device]) {
+        if (cudaFuncSetAttribute(viterbi_kernel<F, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) return G2D_ERR_CUDA;
+        configured[device] = true;
+    }
+    int64_t blocks = ceil_div(rows, R);
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    viterbi_kernel<F, R><<<(unsigned)blocks, VT, smem, st>>>(rows, T, (const F *)x, (const F *)table, L, K * V, V, tail, (const F *)scale,
+                                                             (F *)out, states, (uint8_t *)workspace);
+    return check_launch();
+}
+
+template <typename F>
+static int trellis_dispatch(int64_t rows, int T, const void *x, const void *table, int L, int K, int V, int tail, const void *scale,
+                            void *out, int64_t *states, void *workspace, cudaStream_t st) {
+    const int64_t G = ((int64_t)1 << L) >> (K * V);
+    const size_t per_seq = sizeof(F) * 2 * (size_t)G;
+    const size_t budget = 200 * 1024;
+    if (per_seq > budget) return G2D_ERR_TOO_LARGE;
+    // more sequences per CTA share each table read; fewer keep more SMs busy on short antidiagonals
+    int R = 1;
+    if (rows >= 2 * 148 && 2 * per_seq <= budget) R = 2;
+    if (rows >= 4 * 148 && 4 * per_seq <= budget) R = 4;
+    switch (R) {
+    case 4: return launch_viterbi<F, 4>(rows, T, x, table, L, K, V, tail, scale, out, states, workspace, st);
+    case 2: return launch_viterbi<F, 2>(rows, T, x, table, L, K, V, tail, scale, out, states, workspace, st);
+    default: return launch_viterbi<F, 1>(rows, T, x, table, L, K, V, tail, scale, out, states, workspace, st);
+    }
+}
+
+}  // namespace g2d
+
+using namespace g2d;
+
+static int trellis_check(int dtype, int64_t rows, int32_t T, int32_t L, int32_t K, int32_t V) {
+    if (dtype != G2D_F32 && dtype != G2D_F64) return G2D_ERR_BAD_ARGUMENT;
+    if (rows < 0 || T <= 0 || V < 1 || V > 2 || K < 1 || K * V > 8 || L < K * V || L > 24 || T % V != 0) return G2D_ERR_BAD_ARGUMENT;
+    return G2D_OK;
+}
+
+extern "C" int g2d_trellis_workspace_bytes(int dtype, int64_t rows, int32_t T, int32_t L, int32_t K, int32_t V, size_t *bytes) {
+    const int status = trellis_check(dtype, rows, T, L, K, V);
+    if (status != G2D_OK || !bytes) return status != G2D_OK ? status : G2D_ERR_BAD_ARGUMENT;
+    const int64_t steps = T / V, slots = steps > 1 ? steps - 1 : 1, G = ((int64_t)1 << L) >> (K * V);
+    *bytes = ((size_t)rows * slots * G + 255) & ~(size_t)255;
+    return G2D_OK;
+}
+
+extern "C" int g2d_trellis_quantize(int dtype, int64_t rows, int32_t T, const void *x, const void *table, int32_t L, int32_t K,
+                                    int32_t V, int32_t tail_biting, const void *scale, void *out, int64_t *states,
+                                    void *workspace, size_t workspace_bytes, void *stream) {
+    const int status = trellis_check(dtype, rows, T, L, K, V);
+    if (status != G2D_OK) return status;
+    if (rows == 0) return G2D_OK;
+    if (!x || !table || !out) return G2D_ERR_BAD_ARGUMENT;
+    size_t need = 0;
+    g2d_trellis_workspace_bytes(dtype, rows, T, L, K, V, &need);
+    if (!workspace || workspace_bytes < need) return G2D_ERR_WORKSPACE;
+    cudaStream_t st = (cudaStream_t)stream;
+    return dtype == G2D_F32 ? trellis_dispatch<float>(rows, T, x, table, L, K, V, tail_biting, scale, out, states, workspace, st)
+                            : trellis_dispatch<double>(rows, T, x, table, L, K, V, tail_biting, scale, out, states, workspace, st);
+}
