@@ -57,6 +57,7 @@ _SIGNATURES = {
     "g2d_abi_version": (ctypes.c_int, []),
     "g2d_sweep_workspace_bytes": (ctypes.c_int, [ctypes.POINTER(SweepDesc), ctypes.POINTER(ctypes.c_size_t)]),
     "g2d_sweep_fused": (ctypes.c_int, [ctypes.POINTER(SweepDesc), _vp]),
+    "g2d_sweep_fused_static": (ctypes.c_int, [ctypes.POINTER(SweepDesc), _vp]),
     "g2d_sweep_fused_profile": (ctypes.c_int, [ctypes.POINTER(SweepDesc), _vp, ctypes.POINTER(ctypes.c_double)]),
     "g2d_launch_count": (ctypes.c_ulonglong, []),
     "g2d_stage_push": (ctypes.c_int, [ctypes.POINTER(StageDesc), _vp, _i64, _i64, _vp]),

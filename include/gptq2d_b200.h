@@ -78,6 +78,22 @@ int g2d_abi_version(void);
 int g2d_sweep_workspace_bytes(const g2d_sweep_desc *desc, size_t *bytes);
 int g2d_sweep_fused(const g2d_sweep_desc *desc, void *stream);
 
+/* g2d_sweep_fused for callers that cannot allocate device memory (no counterpart in the reference, whose
+ * Python driver always allocates its buffers with torch).  Meant for a plugin inside a host application that
+ * has reserved the whole device and offers no allocator, or for a latency-bound service that must not call
+ * cudaMalloc (a device-wide synchronisation) while running: the caller passes inputs and outputs only
+ * (desc->workspace and desc->workspace_bytes are ignored) and the two scratch planes come from a fixed
+ * G2D_STATIC_SCRATCH_BYTES array that each device holds from library load to process exit.
+ *  - Limit: g2d_sweep_workspace_bytes(desc) <= G2D_STATIC_SCRATCH_BYTES, i.e. batch*m*n <= 4 Mi fp32 or 2 Mi fp64
+ *    elements (2048 x 2048 fp32); larger problems return G2D_ERR_TOO_LARGE ("size exceeds a fixed maximum").
+ *  - The first call on each device looks up the array's device address (with that device current); make that
+ *    first call before any stream capture begins.
+ *  - All calls on a device share the array, which keeps the previous call's contents (the sweep clears what it
+ *    needs cleared).  Two calls that overlap on the GPU, e.g. on different streams, race: serialise them.
+ *  - Calls no cudaMalloc / cudaFree and no allocating library routine; same results as g2d_sweep_fused. */
+#define G2D_STATIC_SCRATCH_BYTES (32u * 1024u * 1024u)
+int g2d_sweep_fused_static(const g2d_sweep_desc *desc, void *stream);
+
 /* Profiling variant of g2d_sweep_fused (no counterpart in the reference): the same launches, each
  * bracketed by a CUDA event pair on `stream`; synchronizes the stream before returning, so it cannot be
  * captured.  out[0..2] = total milliseconds of the tile-sweep / near-update / far-update launches,
