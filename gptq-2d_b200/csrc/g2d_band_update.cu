@@ -21,6 +21,10 @@ constexpr int BK = 16;       // k chunk
 constexpr int BTH = 64;      // threads per CTA
 constexpr int BLD = BT + 4;  // shared row stride of the staged operands
 
+// Thread (ty, tx) of the 8 x 8 thread grid owns rows ty*4 + {0..3} and 32 + ty*4 + {0..3} (columns likewise with tx),
+// so that its shared-memory reads are two 16-byte vectors that never collide with its neighbours'.
+__device__ __forceinline__ int own(int t, int x) { return x < 4 ? t * 4 + x : 32 + t * 4 + (x - 4); }
+
 template <typename F, int MODE>
 struct BandGeom {
     int P, Q;
@@ -63,9 +67,9 @@ __device__ __forceinline__ void band_product(F (&acc)[8][8], const F *__restrict
         for (int kk = 0; kk < BK; ++kk) {
             F a[8], b[8];
 #pragma unroll
-            for (int x = 0; x < 8; ++x) a[x] = As[kk * BLD + ty * 8 + x];
+            for (int x = 0; x < 8; ++x) a[x] = As[kk * BLD + own(ty, x)];
 #pragma unroll
-            for (int y = 0; y < 8; ++y) b[y] = Bs[kk * BLD + tx * 8 + y];
+            for (int y = 0; y < 8; ++y) b[y] = Bs[kk * BLD + own(tx, y)];
 #pragma unroll
             for (int x = 0; x < 8; ++x)
 #pragma unroll
@@ -75,10 +79,97 @@ __device__ __forceinline__ void band_product(F (&acc)[8][8], const F *__restrict
     }
 }
 
+template <typename F>
+__device__ __forceinline__ void ld4(const F *p, F (&v)[4]);
+template <>
+__device__ __forceinline__ void ld4<float>(const float *p, float (&v)[4]) {
+    const float4 t = *reinterpret_cast<const float4 *>(p);
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+}
+template <>
+__device__ __forceinline__ void ld4<double>(const double *p, double (&v)[4]) {
+    const double2 a = *reinterpret_cast<const double2 *>(p), b = *reinterpret_cast<const double2 *>(p + 2);
+    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+}
+template <typename F>
+__device__ __forceinline__ void st4(F *p, const F (&v)[4]);
+template <>
+__device__ __forceinline__ void st4<float>(float *p, const float (&v)[4]) {
+    *reinterpret_cast<float4 *>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+template <>
+__device__ __forceinline__ void st4<double>(double *p, const double (&v)[4]) {
+    *reinterpret_cast<double2 *>(p) = make_double2(v[0], v[1]);
+    *reinterpret_cast<double2 *>(p + 2) = make_double2(v[2], v[3]);
+}
+
+// Interior tiles in tile mode: no masks, 16-byte vector loads, the next k chunk travels from global memory to
+// registers while the current one is multiplied out of shared memory (two shared buffers, one barrier per chunk).
+// Thread (ty, tx) owns rows ty*4 + {0..3} and 32 + ty*4 + {0..3}, columns tx*4 + {0..3} and 32 + tx*4 + {0..3}:
+// acc[x][y] with x, y < 4 the first group and >= 4 the second.
+template <typename F>
+__device__ __forceinline__ void band_product_fast(F (&acc)[8][8], const F *__restrict__ A, int64_t lda, const F *__restrict__ B,
+                                                  int64_t ldb, int64_t i0, int64_t j0, int64_t k_lo, int64_t k_hi, F *As, F *Bs) {
+    const int tid = threadIdx.x, ty = tid >> 3, tx = tid & 7;
+    constexpr int BUF = BK * BLD;
+    F ra[4][4], rb[4][4];
+    auto fetch = [&](int64_t k0) {
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+            const int id = t * BTH + tid;
+            ld4(A + (i0 + (id >> 2)) * lda + k0 + (id & 3) * 4, ra[t]);
+            ld4(B + (k0 + (id >> 4)) * ldb + j0 + (id & 15) * 4, rb[t]);
+        }
+    };
+    auto stash = [&](int buf) {
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+            const int id = t * BTH + tid;
+            const int row = id >> 2, kq = (id & 3) * 4;
+#pragma unroll
+            for (int x = 0; x < 4; ++x) As[buf * BUF + (kq + x) * BLD + row] = ra[t][x];
+            st4(Bs + buf * BUF + (id >> 4) * BLD + (id & 15) * 4, rb[t]);
+        }
+    };
+    fetch(k_lo);
+    stash(0);
+    __syncthreads();
+    int buf = 0;
+    for (int64_t k0 = k_lo; k0 < k_hi; k0 += BK) {
+        const bool more = k0 + BK < k_hi;
+        if (more) fetch(k0 + BK);
+        const F *as = As + buf * BUF, *bs = Bs + buf * BUF;
+#pragma unroll
+        for (int kk = 0; kk < BK; ++kk) {
+            F a[8], b[8];
+            F t4[4];
+            ld4(as + kk * BLD + ty * 4, t4);
+#pragma unroll
+            for (int x = 0; x < 4; ++x) a[x] = t4[x];
+            ld4(as + kk * BLD + 32 + ty * 4, t4);
+#pragma unroll
+            for (int x = 0; x < 4; ++x) a[4 + x] = t4[x];
+            ld4(bs + kk * BLD + tx * 4, t4);
+#pragma unroll
+            for (int x = 0; x < 4; ++x) b[x] = t4[x];
+            ld4(bs + kk * BLD + 32 + tx * 4, t4);
+#pragma unroll
+            for (int x = 0; x < 4; ++x) b[4 + x] = t4[x];
+#pragma unroll
+            for (int x = 0; x < 8; ++x)
+#pragma unroll
+                for (int y = 0; y < 8; ++y) acc[x][y] += a[x] * b[y];
+        }
+        if (more) stash(buf ^ 1);
+        __syncthreads();
+        buf ^= 1;
+    }
+}
+
 template <typename F, int MODE>
 __global__ void __launch_bounds__(BTH) band_update_kernel(BandArgs<F> P, int nTI, int nTJ, int a_lo) {
-    __shared__ __align__(16) F As[BK * BLD];
-    __shared__ __align__(16) F Bs[BK * BLD];
+    __shared__ __align__(16) F As[2 * BK * BLD];
+    __shared__ __align__(16) F Bs[2 * BK * BLD];
     // blockIdx.y selects a target tile anti-diagonal, blockIdx.x a tile on it
     const int A = a_lo + (int)blockIdx.y;
     const int ti_lo = max(0, A - nTJ + 1), ti_hi = min(A + 1, nTI);
@@ -107,19 +198,24 @@ __global__ void __launch_bounds__(BTH) band_update_kernel(BandArgs<F> P, int nTI
         const F *eg = P.e + batch * m * n;
         const F *lg = P.l + (P.l_off ? P.l_off[batch] : 0);
         const F *ug = P.u + (P.u_off ? P.u_off[batch] : 0);
+        // interior tiles of the fused sweep take the vectorised, double-buffered product
+        const bool fast = MODE == BAND_TILE && i0 + BT <= m && j0 + BT <= n && m % 4 == 0 && n % 4 == 0 &&
+                          ((reinterpret_cast<uintptr_t>(yg) | reinterpret_cast<uintptr_t>(cg) | reinterpret_cast<uintptr_t>(eg) |
+                            reinterpret_cast<uintptr_t>(lg) | reinterpret_cast<uintptr_t>(ug)) % (4 * sizeof(F)) == 0);
         F acc[8][8];
         if (dk_lo < dk_hi) {
 #pragma unroll
             for (int x = 0; x < 8; ++x)
 #pragma unroll
                 for (int y = 0; y < 8; ++y) acc[x][y] = (F)0;
-            band_product<F, MODE, true>(acc, lg, m, eg, n, i0, j0, m, n, dk_lo, dk_hi, g, As, Bs);
+            if (fast) band_product_fast<F>(acc, lg, m, eg, n, i0, j0, dk_lo, dk_hi, As, Bs);
+            else band_product<F, MODE, true>(acc, lg, m, eg, n, i0, j0, m, n, dk_lo, dk_hi, g, As, Bs);
 #pragma unroll
             for (int x = 0; x < 8; ++x) {
-                const int64_t i = i0 + ty * 8 + x;
+                const int64_t i = i0 + own(ty, x);
 #pragma unroll
                 for (int y = 0; y < 8; ++y) {
-                    const int64_t j = j0 + tx * 8 + y;
+                    const int64_t j = j0 + own(tx, y);
                     if (i < m && j < n) {
                         const int64_t st = g.stage(i, j);
                         if (st >= P.s1 && st < P.s_end) {
@@ -136,13 +232,14 @@ __global__ void __launch_bounds__(BTH) band_update_kernel(BandArgs<F> P, int nTI
             for (int x = 0; x < 8; ++x)
 #pragma unroll
                 for (int y = 0; y < 8; ++y) acc[x][y] = (F)0;
-            band_product<F, MODE, false>(acc, cg, n, ug, n, i0, j0, m, n, rk_lo, rk_hi, g, As, Bs);
+            if (fast) band_product_fast<F>(acc, cg, n, ug, n, i0, j0, rk_lo, rk_hi, As, Bs);
+            else band_product<F, MODE, false>(acc, cg, n, ug, n, i0, j0, m, n, rk_lo, rk_hi, g, As, Bs);
 #pragma unroll
             for (int x = 0; x < 8; ++x) {
-                const int64_t i = i0 + ty * 8 + x;
+                const int64_t i = i0 + own(ty, x);
 #pragma unroll
                 for (int y = 0; y < 8; ++y) {
-                    const int64_t j = j0 + tx * 8 + y;
+                    const int64_t j = j0 + own(tx, y);
                     if (i < m && j < n) {
                         const int64_t st = g.stage(i, j);
                         if (st >= P.s1 && st < P.s_end) yg[i * n + j] += acc[x][y];

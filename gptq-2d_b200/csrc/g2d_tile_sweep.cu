@@ -14,105 +14,204 @@
 //   * inside a sub-tile the 16 + 16 lanes of a warp own its columns and rows.  Lane j < 16 holds
 //     the down feedback ("C") of column j, lane 16 + i the right feedback ("Y") of row i, both
 //     skewed so that the entries of anti-diagonal s sit in register s mod 16 of every lane: the
-//     stage loop is fully unrolled and indexes registers statically.
+//     stage loop is fully unrolled and indexes registers statically.  The feedback coefficients
+//     of a sub-tile come from zero-padded copies of the diagonal blocks of L and U^T, so the
+//     pushes need no bounds predicates: out-of-range pushes multiply by zero.
 #include "g2d_common.cuh"
 
 namespace g2d {
+
+constexpr int DLD = SUB + 1;            // row stride of a padded diagonal block
+constexpr int DROWS = 2 * SUB;          // rows of a padded diagonal block (the lower half is zero)
+constexpr int DBLK = DROWS * DLD;       // elements per padded block
+constexpr int TTH = NSUB * 32;          // threads per CTA
+
+template <typename F>
+__device__ __forceinline__ void load4(const F *p, F (&v)[4]);
+template <>
+__device__ __forceinline__ void load4<float>(const float *p, float (&v)[4]) {
+    const float4 t = *reinterpret_cast<const float4 *>(p);
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+}
+template <>
+__device__ __forceinline__ void load4<double>(const double *p, double (&v)[4]) {
+    const double2 a = *reinterpret_cast<const double2 *>(p), b = *reinterpret_cast<const double2 *>(p + 2);
+    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+}
+template <typename F>
+__device__ __forceinline__ void store4(F *p, const F (&v)[4]);
+template <>
+__device__ __forceinline__ void store4<float>(float *p, const float (&v)[4]) {
+    *reinterpret_cast<float4 *>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+template <>
+__device__ __forceinline__ void store4<double>(double *p, const double (&v)[4]) {
+    *reinterpret_cast<double2 *>(p) = make_double2(v[0], v[1]);
+    *reinterpret_cast<double2 *>(p + 2) = make_double2(v[2], v[3]);
+}
 
 template <typename F>
 __device__ __forceinline__ void mm16(F *__restrict__ D, const F *__restrict__ A, const F *__restrict__ B, int lane) {
     // D[16x16] += A[16x16] * B[16x16], all in shared memory with row stride LD; 2 x 4 outputs per lane.
     const int r = (lane >> 2) * 2, c = (lane & 3) * 4;
-    F d[2][4];
+    F d0[4], d1[4];
+    load4(D + r * LD + c, d0);
+    load4(D + (r + 1) * LD + c, d1);
 #pragma unroll
-    for (int x = 0; x < 2; ++x)
+    for (int k = 0; k < SUB; k += 4) {
+        F a0[4], a1[4];
+        load4(A + r * LD + k, a0);
+        load4(A + (r + 1) * LD + k, a1);
 #pragma unroll
-        for (int y = 0; y < 4; ++y) d[x][y] = D[(r + x) * LD + c + y];
+        for (int kk = 0; kk < 4; ++kk) {
+            F b[4];
+            load4(B + (k + kk) * LD + c, b);
 #pragma unroll
-    for (int k = 0; k < SUB; ++k) {
-        const F a0 = A[r * LD + k], a1 = A[(r + 1) * LD + k];
-        F b[4];
-#pragma unroll
-        for (int y = 0; y < 4; ++y) b[y] = B[k * LD + c + y];
-#pragma unroll
-        for (int y = 0; y < 4; ++y) {
-            d[0][y] += a0 * b[y];
-            d[1][y] += a1 * b[y];
+            for (int y = 0; y < 4; ++y) {
+                d0[y] += a0[kk] * b[y];
+                d1[y] += a1[kk] * b[y];
+            }
         }
     }
-#pragma unroll
-    for (int x = 0; x < 2; ++x)
-#pragma unroll
-        for (int y = 0; y < 4; ++y) D[(r + x) * LD + c + y] = d[x][y];
+    store4(D + r * LD + c, d0);
+    store4(D + (r + 1) * LD + c, d1);
 }
 
-template <typename F>
-__global__ void __launch_bounds__(NSUB * 32) tile_sweep_kernel(SweepArgs<F> P, int S) {
+template <typename F, int KIND>
+__global__ void __launch_bounds__(TTH) tile_sweep_kernel(SweepArgs<F> P, int S) {
     extern __shared__ __align__(16) unsigned char g2d_smem[];
     F *Ys = reinterpret_cast<F *>(g2d_smem);  // X + right feedback; the errors E once a sub-tile is swept
     F *Cs = Ys + TILE * LD;                   // down feedback; the completed C once a sub-tile is swept
     F *LUs = Cs + TILE * LD;                  // strict lower part: L[I, I]; strict upper part: U[J, J]
+    F *Dg = LUs + TILE * LD;                  // [2][NSUB] zero-padded diagonal blocks: L[a, a] and U[b, b]^T, strictly lower
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int k = lane & 15, half = lane >> 4;
     const int I = max(0, S - P.nJ + 1) + (int)blockIdx.x, J = S - I;
     const int64_t i0 = (int64_t)I * TILE, j0 = (int64_t)J * TILE;
     const int64_t m = P.m, n = P.n;
+    const bool full = i0 + TILE <= m && j0 + TILE <= n;
 
     for (int64_t batch = blockIdx.y; batch < P.batch; batch += gridDim.y) {
         F *yg = P.y + batch * m * n, *cg = P.c + batch * m * n, *eg = P.e + batch * m * n;
         const F *lg = P.l + (P.l_off ? P.l_off[batch] : 0);
         const F *ug = P.u + (P.u_off ? P.u_off[batch] : 0);
-        const F *sg = P.kind == G2D_Q_AFFINE ? P.scale + (P.scale_off ? P.scale_off[batch] : 0) : nullptr;
-        const F *zg = P.kind == G2D_Q_AFFINE ? P.zero + (P.zero_off ? P.zero_off[batch] : 0) : nullptr;
-        const F *fg = P.kind == G2D_Q_FORCED ? P.forced + batch * m * n : nullptr;
+        const F *sg = KIND == G2D_Q_AFFINE ? P.scale + (P.scale_off ? P.scale_off[batch] : 0) : nullptr;
+        const F *zg = KIND == G2D_Q_AFFINE ? P.zero + (P.zero_off ? P.zero_off[batch] : 0) : nullptr;
+        const F *fg = KIND == G2D_Q_FORCED ? P.forced + batch * m * n : nullptr;
         F *pre = P.y_pre ? P.y_pre + batch * m * n : nullptr;
 
-        // ---- load the tile: consecutive threads read consecutive columns ----
-        for (int idx = tid; idx < TILE * TILE; idx += NSUB * 32) {
-            const int r = idx / TILE, c = idx % TILE;
-            const int64_t gi = i0 + r, gj = j0 + c;
-            const bool in = gi < m && gj < n;
-            Ys[r * LD + c] = in ? yg[gi * n + gj] : (F)0;
-            Cs[r * LD + c] = in ? cg[gi * n + gj] : (F)0;
-            F coef = (F)0;
-            if (r > c) {
-                if (gi < m) coef = lg[gi * m + i0 + c];
-            } else if (r < c) {
-                if (gj < n) coef = ug[(j0 + r) * n + gj];
+        // ---- load the tile; all global loads of a pass are issued before its shared-memory stores ----
+        const bool vec = full && (n % 4 == 0) && (m % 4 == 0) &&
+                         ((reinterpret_cast<uintptr_t>(yg) | reinterpret_cast<uintptr_t>(cg) | reinterpret_cast<uintptr_t>(eg) |
+                           reinterpret_cast<uintptr_t>(lg) | reinterpret_cast<uintptr_t>(ug)) % (4 * sizeof(F)) == 0);
+        if (vec) {
+            constexpr int PER = TILE * TILE / 4 / TTH;  // vectors per thread and array
+#pragma unroll
+            for (int pass = 0; pass < 2; ++pass) {
+                F va[PER][4], vb[PER][4];
+#pragma unroll
+                for (int t = 0; t < PER; ++t) {
+                    const int idx = t * TTH + tid, r = idx / (TILE / 4), c = (idx % (TILE / 4)) * 4;
+                    if (pass == 0) {
+                        load4(yg + (i0 + r) * n + j0 + c, va[t]);
+                        load4(cg + (i0 + r) * n + j0 + c, vb[t]);
+                    } else {
+                        load4(lg + (i0 + r) * m + i0 + c, va[t]);
+                        load4(ug + (j0 + r) * n + j0 + c, vb[t]);
+                    }
+                }
+#pragma unroll
+                for (int t = 0; t < PER; ++t) {
+                    const int idx = t * TTH + tid, r = idx / (TILE / 4), c = (idx % (TILE / 4)) * 4;
+                    if (pass == 0) {
+                        store4(Ys + r * LD + c, va[t]);
+                        store4(Cs + r * LD + c, vb[t]);
+                    } else {
+                        F lu[4];
+#pragma unroll
+                        for (int x = 0; x < 4; ++x) lu[x] = r > c + x ? va[t][x] : (r < c + x ? vb[t][x] : (F)0);
+                        store4(LUs + r * LD + c, lu);
+                    }
+                }
             }
-            LUs[r * LD + c] = coef;
+        } else {
+            constexpr int UN = 8;
+            for (int base = 0; base < TILE * TILE; base += TTH * UN) {
+                F vy[UN], vc[UN], vl[UN];
+#pragma unroll
+                for (int t = 0; t < UN; ++t) {
+                    const int idx = base + t * TTH + tid, r = idx / TILE, c = idx % TILE;
+                    const int64_t gi = i0 + r, gj = j0 + c;
+                    const bool in = gi < m && gj < n;
+                    vy[t] = in ? yg[gi * n + gj] : (F)0;
+                    vc[t] = in ? cg[gi * n + gj] : (F)0;
+                    vl[t] = (F)0;
+                    if (r > c) {
+                        if (gi < m) vl[t] = lg[gi * m + i0 + c];
+                    } else if (r < c) {
+                        if (gj < n) vl[t] = ug[(j0 + r) * n + gj];
+                    }
+                }
+#pragma unroll
+                for (int t = 0; t < UN; ++t) {
+                    const int idx = base + t * TTH + tid, r = idx / TILE, c = idx % TILE;
+                    Ys[r * LD + c] = vy[t];
+                    Cs[r * LD + c] = vc[t];
+                    LUs[r * LD + c] = vl[t];
+                }
+            }
+        }
+        __syncthreads();
+        for (int idx = tid; idx < 2 * NSUB * DBLK; idx += TTH) {
+            const int which = idx / (NSUB * DBLK), blk = idx / DBLK % NSUB, r = idx % DBLK / DLD, c = idx % DLD;
+            F v = (F)0;
+            if (r < SUB && c < r) v = which == 0 ? LUs[(blk * SUB + r) * LD + blk * SUB + c] : LUs[(blk * SUB + c) * LD + blk * SUB + r];
+            Dg[idx] = v;
         }
         __syncthreads();
 
         F sc[SUB], zp[SUB];  // quantizer parameters of this lane's entries, skewed like acc
         bool have_params = false;
+        unsigned valid = 0xFFFFu;  // bit r: the entry held in register r lies inside the matrix
+
+        // parameters (and the in-range mask) of sub-tile (warp, b) for this lane
+        auto fetch_params = [&](int b) {
+            const int r0 = warp * SUB, c0 = b * SUB;
+            unsigned bits = 0;
+#pragma unroll
+            for (int r = 0; r < SUB; ++r) {
+                const int o = (r - k) & (SUB - 1);
+                const int64_t gi = i0 + r0 + (half ? k : o), gj = j0 + c0 + (half ? o : k);
+                const bool in = full || (gi < m && gj < n);
+                bits |= in ? (1u << r) : 0u;
+                if (KIND == G2D_Q_AFFINE) {
+                    sc[r] = in ? sg[gi * P.srs + gj * P.scs] : (F)1;
+                    zp[r] = in ? zg[gi * P.zrs + gj * P.zcs] : (F)0;
+                } else if (KIND == G2D_Q_FORCED) {
+                    sc[r] = in ? fg[gi * n + gj] : (F)0;
+                }
+            }
+            valid = bits;
+        };
 
         for (int w = 0; w < 2 * NSUB - 1; ++w) {
             const int a = warp, b = w - warp;
             if (b >= 0 && b < NSUB) {
                 const int r0 = a * SUB, c0 = b * SUB;
-                if (!have_params && P.kind != G2D_Q_ROUND) {
-#pragma unroll
-                    for (int r = 0; r < SUB; ++r) {
-                        const int o = (r - k) & (SUB - 1);
-                        const int64_t gi = i0 + r0 + (half ? k : o), gj = j0 + c0 + (half ? o : k);
-                        const bool in = gi < m && gj < n;
-                        if (P.kind == G2D_Q_AFFINE) {
-                            sc[r] = in ? sg[gi * P.srs + gj * P.scs] : (F)1;
-                            zp[r] = in ? zg[gi * P.zrs + gj * P.zcs] : (F)0;
-                        } else {
-                            sc[r] = in ? fg[gi * n + gj] : (F)0;
-                        }
-                    }
-                }
+                if (!have_params) fetch_params(b);
                 F acc[SUB];
 #pragma unroll
                 for (int r = 0; r < SUB; ++r) {
                     const int o = (r - k) & (SUB - 1);
                     acc[r] = half ? Ys[(r0 + k) * LD + c0 + o] : Cs[(r0 + o) * LD + c0 + k];
                 }
-                const int base = half ? c0 : r0, step = half ? 1 : LD;
+                // lane-constant addresses; stage s adds a compile-time offset
+                F *const cs_ptr = Cs + (r0 + k) * LD + c0 - k;          // row owner: completed C of (k, s - k)
+                F *const ys_ptr = Ys + (r0 - k) * LD + c0 + k;          // column owner: error of (s - k, k)
+                F *const z_ptr = yg + (i0 + r0 + k) * n + j0 + c0 - k;  // row owner: Z of (k, s - k)
+                F *const pre_ptr = pre ? pre + (i0 + r0 + k) * n + j0 + c0 - k : nullptr;
+                const F *const dg = Dg + (half * NSUB + (half ? b : a)) * DBLK;
 #pragma unroll
                 for (int s = 0; s < 2 * SUB - 1; ++s) {
                     const int r = s & (SUB - 1);
@@ -123,57 +222,36 @@ __global__ void __launch_bounds__(NSUB * 32) tile_sweep_kernel(SweepArgs<F> P, i
                     const F other = __shfl_sync(0xffffffffu, acc[r], half ? srcw : SUB + srcw);
                     const F yacc = half ? acc[r] : other, cacc = half ? other : acc[r];
                     const F yv = yacc + cacc;
-                    const int li = half ? k : srcw, lj = half ? srcw : k;
-                    const int64_t gi = i0 + r0 + li, gj = j0 + c0 + lj;
-                    const bool in = active && gi < m && gj < n;
+                    const bool ok = active && ((valid >> r) & 1u);
                     F z;
-                    if (P.kind == G2D_Q_AFFINE) z = affine_value(yv, sc[r], zp[r], P.qmin, P.qmax);
-                    else if (P.kind == G2D_Q_FORCED) z = sc[r];
+                    if (KIND == G2D_Q_AFFINE) z = affine_value(yv, sc[r], zp[r], P.qmin, P.qmax);
+                    else if (KIND == G2D_Q_FORCED) z = sc[r];
                     else z = rint_even(yv);
-                    const F ev = in ? z - yv : (F)0;
+                    const F ev = ok ? z - yv : (F)0;
                     const F cc = cacc + ev;
-                    if (active) {
-                        if (half) {
-                            Cs[(r0 + li) * LD + c0 + lj] = cc;
-                            if (in) {
-                                yg[gi * n + gj] = z;
-                                if (pre) pre[gi * n + gj] = yv;
-                            }
-                        } else {
-                            Ys[(r0 + li) * LD + c0 + lj] = ev;
-                        }
+                    if (active && half) cs_ptr[s] = cc;
+                    if (active && !half) ys_ptr[s * LD] = ev;
+                    if (ok && half) {
+                        z_ptr[s] = z;
+                        if (pre_ptr) pre_ptr[s] = yv;
                     }
-                    // push: the column owner sends its error down through L, the row owner its completed C right through U
-                    const F val = half ? cc : ev;
-                    const F *cp = LUs + (base + srcw) * LD + base + srcw;
+                    // push: the column owner sends its error down through L, the row owner its completed C right
+                    // through U; rows past the block's end and inactive lanes multiply by zero
+                    const F val = active ? (half ? cc : ev) : (F)0;
+                    const F *cp = dg + srcw * (DLD + 1);
                     constexpr int kMaxPush = SUB - 1;
                     const int dd_hi = s < SUB ? kMaxPush : 2 * SUB - 2 - s;  // static bound: src >= s - (SUB - 1)
 #pragma unroll
-                    for (int dd = 1; dd <= kMaxPush; ++dd) {
-                        if (dd <= dd_hi) {
-                            if (active && dd <= SUB - 1 - src) acc[(r + dd) & (SUB - 1)] += cp[dd * step] * val;
-                        }
-                    }
+                    for (int dd = 1; dd <= kMaxPush; ++dd)
+                        if (dd <= dd_hi) acc[(r + dd) & (SUB - 1)] += cp[dd * DLD] * val;
                 }
             }
             // fetch the parameters of the next sub-tile of this warp while the updates run
             {
                 const int bn = w + 1 - warp;
                 have_params = false;
-                if (bn >= 0 && bn < NSUB && P.kind != G2D_Q_ROUND) {
-                    const int r0 = warp * SUB, c0 = bn * SUB;
-#pragma unroll
-                    for (int r = 0; r < SUB; ++r) {
-                        const int o = (r - k) & (SUB - 1);
-                        const int64_t gi = i0 + r0 + (half ? k : o), gj = j0 + c0 + (half ? o : k);
-                        const bool in = gi < m && gj < n;
-                        if (P.kind == G2D_Q_AFFINE) {
-                            sc[r] = in ? sg[gi * P.srs + gj * P.scs] : (F)1;
-                            zp[r] = in ? zg[gi * P.zrs + gj * P.zcs] : (F)0;
-                        } else {
-                            sc[r] = in ? fg[gi * n + gj] : (F)0;
-                        }
-                    }
+                if (bn >= 0 && bn < NSUB) {
+                    fetch_params(bn);
                     have_params = true;
                 }
             }
@@ -199,35 +277,58 @@ __global__ void __launch_bounds__(NSUB * 32) tile_sweep_kernel(SweepArgs<F> P, i
         }
 
         // ---- store the errors and the completed C of the tile; Z went out entry by entry ----
-        for (int idx = tid; idx < TILE * TILE; idx += NSUB * 32) {
-            const int r = idx / TILE, c = idx % TILE;
-            const int64_t gi = i0 + r, gj = j0 + c;
-            if (gi < m && gj < n) {
-                eg[gi * n + gj] = Ys[r * LD + c];
-                cg[gi * n + gj] = Cs[r * LD + c];
+        if (vec) {
+            constexpr int PER = TILE * TILE / 4 / TTH;
+#pragma unroll
+            for (int t = 0; t < PER; ++t) {
+                const int idx = t * TTH + tid, r = idx / (TILE / 4), c = (idx % (TILE / 4)) * 4;
+                F ve[4], vc[4];
+                load4(Ys + r * LD + c, ve);
+                load4(Cs + r * LD + c, vc);
+                store4(eg + (i0 + r) * n + j0 + c, ve);
+                store4(cg + (i0 + r) * n + j0 + c, vc);
+            }
+        } else {
+            for (int idx = tid; idx < TILE * TILE; idx += TTH) {
+                const int r = idx / TILE, c = idx % TILE;
+                const int64_t gi = i0 + r, gj = j0 + c;
+                if (gi < m && gj < n) {
+                    eg[gi * n + gj] = Ys[r * LD + c];
+                    cg[gi * n + gj] = Cs[r * LD + c];
+                }
             }
         }
         __syncthreads();
     }
 }
 
-template <typename F>
-int launch_tile_sweep(const SweepArgs<F> &args, int S, cudaStream_t stream) {
+template <typename F, int KIND>
+static int launch_kind(const SweepArgs<F> &args, int S, cudaStream_t stream) {
     // the opt-in to more than 48 KB of dynamic shared memory is per device
     static bool configured[64] = {};
-    const size_t smem = sizeof(F) * 3 * TILE * LD;
+    const size_t smem = sizeof(F) * (3 * TILE * LD + 2 * NSUB * DBLK + 2 * DBLK);
     int device = 0;
     if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return G2D_ERR_CUDA;
     if (!configured[device]) {
-        if (cudaFuncSetAttribute(tile_sweep_kernel<F>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        if (cudaFuncSetAttribute(tile_sweep_kernel<F, KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
             return G2D_ERR_CUDA;
         configured[device] = true;
     }
     const int i_lo = S - args.nJ + 1 > 0 ? S - args.nJ + 1 : 0;
     const int i_hi = S + 1 < args.nI ? S + 1 : args.nI;
     dim3 grid((unsigned)(i_hi - i_lo), (unsigned)(args.batch < 65535 ? args.batch : 65535));
-    tile_sweep_kernel<F><<<grid, NSUB * 32, smem, stream>>>(args, S);
+    tile_sweep_kernel<F, KIND><<<grid, TTH, smem, stream>>>(args, S);
     return check_launch();
+}
+
+template <typename F>
+int launch_tile_sweep(const SweepArgs<F> &args, int S, cudaStream_t stream) {
+    switch (args.kind) {
+    case G2D_Q_ROUND: return launch_kind<F, G2D_Q_ROUND>(args, S, stream);
+    case G2D_Q_AFFINE: return launch_kind<F, G2D_Q_AFFINE>(args, S, stream);
+    case G2D_Q_FORCED: return launch_kind<F, G2D_Q_FORCED>(args, S, stream);
+    default: return G2D_ERR_UNSUPPORTED;
+    }
 }
 
 template int launch_tile_sweep<float>(const SweepArgs<float> &, int, cudaStream_t);
