@@ -1,0 +1,328 @@
+// Factor preparation: the unit (block) lower triangular L with M^{-1} = L Lambda L^T for a symmetric positive
+// definite M, i.e. ldl_of_inverse + _unit_diagonal_blocks of the reference (gptq_2d_reference.py:29-49), which
+// there is torch.linalg.cholesky + solve_triangular.  Same three steps, blocked by 64 and written for the GPU:
+//
+//   1. reverse-order Cholesky  M = T^T T  (T lower triangular; T^T is the reference's upper factor Um), from the
+//      last block row to the first: factor the diagonal block in one CTA (and invert it), solve the block row to
+//      its left as a product with that inverse, subtract the block row's Gram from the part still to factor;
+//   2. Lf = T^{-1} (= Um^{-T}) by block forward substitution, one block row per launch:
+//      Lf[i, j] = -T[i, i]^{-1} sum_{k = j .. i-1} T[i, k] Lf[k, j],  Lf[i, i] = T[i, i]^{-1};
+//   3. out = Lf D^{-1} with D the size x size diagonal blocks of Lf: identity diagonal blocks, zeros above.
+//
+// M is overwritten (its lower triangle becomes T).  A non-positive pivot stores its 1-based index in *flag.
+#include "g2d_common.cuh"
+
+namespace g2d {
+
+constexpr int FB = 64;        // block edge
+constexpr int FK = 16;        // k chunk of the tile products
+constexpr int FLD = FB + 4;   // shared row stride
+constexpr int FTH = 64;       // threads of a tile-product CTA (8 x 8 outputs each)
+
+__device__ __forceinline__ int own8(int t, int x) { return x < 4 ? t * 4 + x : 32 + t * 4 + (x - 4); }
+
+// acc[8][8] += sum_{k < K} A(i, k) B(k, j) for the 64 x 64 tile of this CTA; la / lb return 0 outside the matrix.
+template <typename F, typename LA, typename LB>
+__device__ __forceinline__ void tile_product(F (&acc)[8][8], int64_t K, LA la, LB lb, F *As, F *Bs, bool a_k_contiguous) {
+    const int tid = threadIdx.x, ty = tid >> 3, tx = tid & 7;
+    for (int64_t k0 = 0; k0 < K; k0 += FK) {
+        F ra[FB * FK / FTH], rb[FB * FK / FTH];
+#pragma unroll
+        for (int t = 0; t < FB * FK / FTH; ++t) {
+            const int idx = t * FTH + tid;
+            const int i = a_k_contiguous ? idx / FK : idx % FB, kk = a_k_contiguous ? idx % FK : idx / FB;
+            ra[t] = k0 + kk < K ? la(i, k0 + kk) : (F)0;
+            const int kb = idx / FB, j = idx % FB;
+            rb[t] = k0 + kb < K ? lb(k0 + kb, j) : (F)0;
+        }
+        __syncthreads();  // the previous chunk has been consumed
+#pragma unroll
+        for (int t = 0; t < FB * FK / FTH; ++t) {
+            const int idx = t * FTH + tid;
+            const int i = a_k_contiguous ? idx / FK : idx % FB, kk = a_k_contiguous ? idx % FK : idx / FB;
+            As[kk * FLD + i] = ra[t];
+            Bs[(idx / FB) * FLD + idx % FB] = rb[t];
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < FK; ++kk) {
+            F a[8], b[8];
+#pragma unroll
+            for (int x = 0; x < 8; ++x) a[x] = As[kk * FLD + own8(ty, x)];
+#pragma unroll
+            for (int y = 0; y < 8; ++y) b[y] = Bs[kk * FLD + own8(tx, y)];
+#pragma unroll
+            for (int x = 0; x < 8; ++x)
+#pragma unroll
+                for (int y = 0; y < 8; ++y) acc[x][y] += a[x] * b[y];
+        }
+    }
+    __syncthreads();
+}
+
+template <typename F>
+__device__ __forceinline__ void zero_acc(F (&acc)[8][8]) {
+#pragma unroll
+    for (int x = 0; x < 8; ++x)
+#pragma unroll
+        for (int y = 0; y < 8; ++y) acc[x][y] = (F)0;
+}
+
+// ---- step 1a: factor the diagonal block kb (bs x bs), M_kk = T_kk^T T_kk, and invert T_kk ----
+template <typename F>
+__global__ void __launch_bounds__(256) ldl_diag_kernel(F *a, int64_t n, int kb, F *tinv, int *flag) {
+    __shared__ F S[FB][FB + 1];   // working block, becomes T_kk (lower)
+    __shared__ int bad;
+    const int tid = threadIdx.x;
+    const int64_t o = (int64_t)kb * FB;
+    const int bs = (int)min((int64_t)FB, n - o);
+    if (tid == 0) bad = 0;
+    for (int idx = tid; idx < FB * FB; idx += 256) {
+        const int r = idx / FB, c = idx % FB;
+        // the working copy is kept symmetric from the stored lower triangle
+        F v = (F)0;
+        if (r < bs && c < bs) v = r >= c ? a[(o + r) * n + o + c] : a[(o + c) * n + o + r];
+        S[r][c] = v;
+        tinv[(int64_t)kb * FB * FB + idx] = (F)0;
+    }
+    __syncthreads();
+    for (int j = bs - 1; j >= 0; --j) {
+        const F d2 = S[j][j];
+        __syncthreads();
+        if (!(d2 > (F)0)) {
+            if (tid == 0) bad = j + 1;
+        }
+        const F d = sqrt(d2);
+        // row j of T: T[j][i] = M'[j][i] / d for i <= j
+        if (tid <= j) S[j][tid] = tid == j ? d : S[j][tid] / d;
+        __syncthreads();
+        // M'[i1][i2] -= T[j][i1] T[j][i2] for i1, i2 < j
+        for (int idx = tid; idx < j * j; idx += 256) {
+            const int i1 = idx / j, i2 = idx % j;
+            S[i1][i2] -= S[j][i1] * S[j][i2];
+        }
+        __syncthreads();
+    }
+    // inverse of the lower triangular T_kk: thread c solves T x = e_c by forward substitution; it keeps its
+    // column in the (zeroed) global block and reads back only what it wrote itself
+    if (tid < bs) {
+        const int c = tid;
+        F *v = tinv + (int64_t)kb * FB * FB;
+        for (int r = c; r < bs; ++r) {
+            F acc = r == c ? (F)1 : (F)0;
+            for (int k = c; k < r; ++k) acc -= S[r][k] * v[k * FB + c];
+            v[r * FB + c] = acc / S[r][r];
+        }
+    }
+    for (int idx = tid; idx < FB * FB; idx += 256) {
+        const int r = idx / FB, c = idx % FB;
+        if (r < bs && c < bs && r >= c) a[(o + r) * n + o + c] = S[r][c];
+    }
+    if (tid == 0 && bad && flag) atomicCAS(flag, 0, (int)(o + bad));
+}
+
+// ---- step 1b: block row to the left of the diagonal block: T[kb, j] = T_kk^{-T} M'[kb, j] ----
+template <typename F>
+__global__ void __launch_bounds__(FTH) ldl_trsm_kernel(F *a, int64_t n, int kb, const F *tinv) {
+    __shared__ __align__(16) F As[FK * FLD];
+    __shared__ __align__(16) F Bs[FK * FLD];
+    const int j = blockIdx.x;  // column tile, j < kb
+    const int64_t o = (int64_t)kb * FB, c0 = (int64_t)j * FB;
+    const int bs = (int)min((int64_t)FB, n - o);
+    const F *ti = tinv + (int64_t)kb * FB * FB;
+    F acc[8][8];
+    zero_acc(acc);
+    // A(r, k) = Tinv[k][r] (transposed), B(k, col) = M'[o + k][c0 + col]
+    tile_product<F>(acc, bs, [&](int r, int64_t k) { return ti[k * FB + r]; },
+                    [&](int64_t k, int col) { return a[(o + k) * n + c0 + col]; }, As, Bs, false);
+    const int tid = threadIdx.x, ty = tid >> 3, tx = tid & 7;
+#pragma unroll
+    for (int x = 0; x < 8; ++x) {
+        const int r = own8(ty, x);
+#pragma unroll
+        for (int y = 0; y < 8; ++y)
+            if (r < bs) a[(o + r) * n + c0 + own8(tx, y)] = acc[x][y];
+    }
+}
+
+// ---- step 1c: M'[TI, TJ] -= T[kb, TI]^T T[kb, TJ] for TJ <= TI < kb (lower triangle of tiles) ----
+template <typename F>
+__global__ void __launch_bounds__(FTH) ldl_syrk_kernel(F *a, int64_t n, int kb) {
+    __shared__ __align__(16) F As[FK * FLD];
+    __shared__ __align__(16) F Bs[FK * FLD];
+    // linear index -> (TI, TJ) with TJ <= TI
+    const int64_t lin = blockIdx.x;
+    int TI = (int)((sqrt(8.0 * (double)lin + 1.0) - 1.0) / 2.0);
+    while ((int64_t)(TI + 1) * (TI + 2) / 2 <= lin) ++TI;
+    while ((int64_t)TI * (TI + 1) / 2 > lin) --TI;
+    const int TJ = (int)(lin - (int64_t)TI * (TI + 1) / 2);
+    const int64_t o = (int64_t)kb * FB, r0 = (int64_t)TI * FB, c0 = (int64_t)TJ * FB;
+    const int bs = (int)min((int64_t)FB, n - o);
+    F acc[8][8];
+    zero_acc(acc);
+    tile_product<F>(acc, bs, [&](int i, int64_t k) { return a[(o + k) * n + r0 + i]; },
+                    [&](int64_t k, int j) { return a[(o + k) * n + c0 + j]; }, As, Bs, false);
+    const int tid = threadIdx.x, ty = tid >> 3, tx = tid & 7;
+#pragma unroll
+    for (int x = 0; x < 8; ++x) {
+        const int64_t r = r0 + own8(ty, x);
+#pragma unroll
+        for (int y = 0; y < 8; ++y) {
+            const int64_t c = c0 + own8(tx, y);
+            if (c <= r) a[r * n + c] -= acc[x][y];
+        }
+    }
+}
+
+// ---- step 2: block row i of Lf = T^{-1}; CTA j < i computes Lf[i, j], CTA i copies T_ii^{-1} ----
+template <typename F>
+__global__ void __launch_bounds__(FTH) ldl_trinv_kernel(const F *a, int64_t n, int i, const F *tinv, F *out) {
+    __shared__ __align__(16) F As[FK * FLD];
+    __shared__ __align__(16) F Bs[FK * FLD];
+    const int j = blockIdx.x;
+    const int64_t r0 = (int64_t)i * FB, c0 = (int64_t)j * FB;
+    const int bs = (int)min((int64_t)FB, n - r0);
+    const F *ti = tinv + (int64_t)i * FB * FB;
+    const int tid = threadIdx.x, ty = tid >> 3, tx = tid & 7;
+    if (j == i) {
+        for (int idx = tid; idx < FB * FB; idx += FTH) {
+            const int r = idx / FB, c = idx % FB;
+            if (r < bs && c < bs) out[(r0 + r) * n + c0 + c] = ti[idx];
+        }
+        return;
+    }
+    F acc[8][8];
+    zero_acc(acc);
+    // R = sum_{k in [j*64, i*64)} T[i rows, k] Lf[k, j cols]
+    const int64_t k_lo = c0, K = r0 - c0;
+    tile_product<F>(acc, K, [&](int r, int64_t k) { return r < bs ? a[(r0 + r) * n + k_lo + k] : (F)0; },
+                    [&](int64_t k, int c) { return out[(k_lo + k) * n + c0 + c]; }, As, Bs, true);
+    // park R in the output block (this CTA owns it), then Lf[i, j] = -T_ii^{-1} R
+    F *rblk = out + r0 * n + c0;
+#pragma unroll
+    for (int x = 0; x < 8; ++x) {
+        const int r = own8(ty, x);
+#pragma unroll
+        for (int y = 0; y < 8; ++y)
+            if (r < bs) rblk[(int64_t)r * n + own8(tx, y)] = acc[x][y];
+    }
+    __syncthreads();
+    zero_acc(acc);
+    tile_product<F>(acc, bs, [&](int r, int64_t k) { return ti[r * FB + k]; }, [&](int64_t k, int c) { return rblk[k * n + c]; }, As, Bs, true);
+#pragma unroll
+    for (int x = 0; x < 8; ++x) {
+        const int r = own8(ty, x);
+#pragma unroll
+        for (int y = 0; y < 8; ++y)
+            if (r < bs) out[(r0 + r) * n + c0 + own8(tx, y)] = -acc[x][y];
+    }
+}
+
+// ---- step 3: out = Lf D^{-1}; one thread per row and diagonal block of `size` columns ----
+template <typename F>
+__global__ void ldl_normalize_kernel(F *out, int64_t n, int size) {
+    const int64_t blocks = n / size;
+    const int64_t total = n * blocks;
+    for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t row = t / blocks, b = t % blocks;  // consecutive threads: consecutive column blocks of one row
+        const int64_t c0 = b * size;
+        F *p = out + row * n + c0;
+        if (c0 > row) {
+            for (int x = 0; x < size; ++x) p[x] = (F)0;
+        } else if (row / size == b) {
+            for (int x = 0; x < size; ++x) p[x] = c0 + x == row ? (F)1 : (F)0;
+        }
+    }
+}
+
+// The normalisation reads the diagonal blocks while other rows are rewritten, so the blocks are copied out first.
+template <typename F>
+__global__ void ldl_copy_diag_kernel(const F *out, int64_t n, int size, F *dblk) {
+    const int64_t total = (n / size) * size * size;
+    for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t b = t / ((int64_t)size * size);
+        const int r = (int)(t / size % size), c = (int)(t % size);
+        dblk[t] = out[(b * size + r) * n + b * size + c];
+    }
+}
+
+template <typename F>
+__global__ void ldl_scale_kernel(F *out, int64_t n, int size, const F *dblk) {
+    const int64_t blocks = n / size;
+    const int64_t total = n * blocks;
+    for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t row = t / blocks, b = t % blocks;
+        const int64_t c0 = b * size;
+        if (row / size <= b) continue;  // diagonal block and above: set by ldl_normalize_kernel
+        F *p = out + row * n + c0;
+        const F *d = dblk + b * size * size;
+        // x D = r with D lower triangular: back substitution from the last column of the block
+        for (int x = size - 1; x >= 0; --x) {
+            F acc = p[x];
+            for (int x2 = x + 1; x2 < size; ++x2) acc -= p[x2] * d[x2 * size + x];
+            p[x] = acc / d[x * size + x];
+        }
+    }
+}
+
+template <typename F>
+int ldl_run(int64_t n, F *a, int size, F *out, int *flag, void *workspace, cudaStream_t st) {
+    const int nb = (int)ceil_div(n, FB);
+    F *tinv = (F *)workspace;                                   // [nb][64][64]
+    F *dblk = tinv + (int64_t)nb * FB * FB;                     // [n / size][size][size]
+    if (flag && cudaMemsetAsync(flag, 0, sizeof(int), st) != cudaSuccess) return G2D_ERR_CUDA;
+    if (cudaMemsetAsync(out, 0, sizeof(F) * (size_t)n * n, st) != cudaSuccess) return G2D_ERR_CUDA;
+    for (int kb = nb - 1; kb >= 0; --kb) {
+        ldl_diag_kernel<F><<<1, 256, 0, st>>>(a, n, kb, tinv, flag);
+        if (check_launch() != G2D_OK) return G2D_ERR_CUDA;
+        if (kb > 0) {
+            ldl_trsm_kernel<F><<<kb, FTH, 0, st>>>(a, n, kb, tinv);
+            if (check_launch() != G2D_OK) return G2D_ERR_CUDA;
+            const int64_t pairs = (int64_t)kb * (kb + 1) / 2;
+            ldl_syrk_kernel<F><<<(unsigned)pairs, FTH, 0, st>>>(a, n, kb);
+            if (check_launch() != G2D_OK) return G2D_ERR_CUDA;
+        }
+    }
+    for (int i = 0; i < nb; ++i) {
+        ldl_trinv_kernel<F><<<i + 1, FTH, 0, st>>>(a, n, i, tinv, out);
+        if (check_launch() != G2D_OK) return G2D_ERR_CUDA;
+    }
+    const int64_t work = n * (n / size);
+    int64_t blocks = ceil_div(work, 256);
+    if (blocks > 148 * 64) blocks = 148 * 64;
+    ldl_copy_diag_kernel<F><<<(unsigned)(ceil_div(n * size, 256) < 148 * 64 ? ceil_div(n * size, 256) : 148 * 64), 256, 0, st>>>(out, n, size, dblk);
+    if (check_launch() != G2D_OK) return G2D_ERR_CUDA;
+    ldl_scale_kernel<F><<<(unsigned)blocks, 256, 0, st>>>(out, n, size, dblk);
+    if (check_launch() != G2D_OK) return G2D_ERR_CUDA;
+    ldl_normalize_kernel<F><<<(unsigned)blocks, 256, 0, st>>>(out, n, size);
+    return check_launch();
+}
+
+}  // namespace g2d
+
+using namespace g2d;
+
+static size_t ldl_bytes(int dtype, int64_t n) {
+    const size_t elem = dtype == G2D_F32 ? 4 : 8;
+    const size_t nb = (size_t)ceil_div(n, FB);
+    return ((nb * FB * FB + (size_t)n * FB) * elem + 255) & ~(size_t)255;
+}
+
+extern "C" int g2d_ldl_workspace_bytes(int dtype, int64_t n, size_t *bytes) {
+    if ((dtype != G2D_F32 && dtype != G2D_F64) || n < 0 || !bytes) return G2D_ERR_BAD_ARGUMENT;
+    *bytes = ldl_bytes(dtype, n);
+    return G2D_OK;
+}
+
+extern "C" int g2d_ldl_of_inverse(int dtype, int64_t n, void *a, int32_t size, void *out, int32_t *status_flag, void *workspace,
+                                  size_t workspace_bytes, void *stream) {
+    if ((dtype != G2D_F32 && dtype != G2D_F64) || n < 0 || size <= 0) return G2D_ERR_BAD_ARGUMENT;
+    if (n == 0) return G2D_OK;
+    if (n % size != 0 || size > FB) return size > FB ? G2D_ERR_TOO_LARGE : G2D_ERR_BAD_ARGUMENT;
+    if (!a || !out) return G2D_ERR_BAD_ARGUMENT;
+    if (!workspace || workspace_bytes < ldl_bytes(dtype, n)) return G2D_ERR_WORKSPACE;
+    if (ceil_div(n, FB) > 46000) return G2D_ERR_TOO_LARGE;  // tile pairs of one launch must fit a 1-D grid
+    cudaStream_t st = (cudaStream_t)stream;
+    return dtype == G2D_F32 ? ldl_run<float>(n, (float *)a, size, (float *)out, status_flag, workspace, st)
+                            : ldl_run<double>(n, (double *)a, size, (double *)out, status_flag, workspace, st);
+}

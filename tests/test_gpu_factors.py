@@ -1,0 +1,79 @@
+"""GPU tests of the factor preparation.  The reference computes these factors with LAPACK / cuSOLVER through
+torch.linalg, so parity is to a tolerance (stated per case) plus the defining properties."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import load_golden
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def K():
+    import kron_factors
+    return kron_factors
+
+
+def cuda(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def check_structure(l, size):
+    n = l.size(0)
+    block = torch.arange(n, device=l.device) // size
+    same = block[:, None] == block[None, :]
+    assert torch.equal(l[same], torch.eye(n, dtype=l.dtype, device=l.device)[same])  # identity diagonal blocks, exactly
+    assert (l[block[:, None] < block[None, :]] == 0).all()
+
+
+def test_golden_factors(K):
+    g = load_golden("factors.npz")
+    for n in (1, 7, 64, 200):
+        m = cuda(g[f"g{n}"])
+        before = m.clone()
+        l = K.ldl_of_inverse(m)
+        assert torch.equal(m, before)  # the input is left alone
+        assert torch.allclose(l.cpu(), torch.from_numpy(g[f"l{n}"]), rtol=0, atol=1e-9)
+        check_structure(l, 1)
+    for size in (1, 2, 4, 16):
+        l = K.ldl_of_inverse(cuda(g["g48"]), size)
+        assert torch.allclose(l.cpu(), torch.from_numpy(g[f"l48_{size}"]), rtol=0, atol=1e-9)
+        check_structure(l, size)
+    l = K.ldl_of_inverse(cuda(g["g256_f32"]))
+    assert (l.cpu() - torch.from_numpy(g["l256_f32"])).abs().max() < 5e-5
+
+
+@pytest.mark.parametrize("n,size", [(130, 1), (130, 5), (1000, 1), (960, 16), (1536, 3)])
+def test_against_oracle_and_properties(K, oracle, n, size):
+    rng = np.random.default_rng(n + size)
+    x = rng.standard_normal((2 * n, n)) * np.exp(0.5 * rng.standard_normal(n))
+    gram = x.T @ x / (2 * n)
+    gram += 0.01 * np.mean(np.diag(gram)) * np.eye(n)
+    l = K.ldl_of_inverse(cuda(gram), size)
+    if n <= 1000:
+        assert np.abs(l.cpu().numpy() - oracle.ldl_of_inverse(gram, size)).max() < 1e-8
+    check_structure(l, size)
+    # G^{-1} = L Lambda L^T  <=>  L^T G L is block diagonal
+    d = l.T @ cuda(gram) @ l
+    block = torch.arange(n, device="cuda") // size
+    off = d[block[:, None] != block[None, :]]
+    assert off.abs().max().item() < 1e-9 * d.diagonal().abs().max().item()
+    # float32 stays close to the float64 factor
+    l32 = K.ldl_of_inverse(cuda(gram.astype(np.float32)), size)
+    assert (l32.double() - l).abs().max().item() < 2e-3
+    check_structure(l32, size)
+
+
+def test_feedback_factors_and_errors(K):
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    a = torch.randn(24, 24, generator=gen, device="cuda", dtype=torch.float64)
+    b = torch.randn(40, 40, generator=gen, device="cuda", dtype=torch.float64)
+    l, u = K.feedback_factors(a, b, (4, 8))
+    check_structure(l, 4)
+    check_structure(u.T, 8)
+    from gptq_2d_reference import ldl_of_inverse
+    assert torch.equal(ldl_of_inverse(a.T @ a, size=4), l)
+    with pytest.raises(torch.linalg.LinAlgError):
+        K.ldl_of_inverse(-torch.eye(70, device="cuda", dtype=torch.float64))
+    assert K.ldl_of_inverse(torch.empty(0, 0, device="cuda")).shape == (0, 0)
