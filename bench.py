@@ -2,9 +2,10 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--size 8192]
 
-One step = quantize one synthetic 8192 x 8192 fp32 layer to INT4 (symmetric, per-row fp16 abs-max scales) with the
-two-sided GPTQ-2D sweep, given its feedback factors L and U: the per-row scales are computed and the sweep is run
-through the package's public ``gptq_2d`` call (which reaches the kernels through the C ABI).  With N > 1 ranks (one
+One step = quantize one synthetic 8192 x 8192 fp32 layer to INT4 (symmetric, per-row fp16 abs-max scales) from its
+weights and its two Hessian factors G (output side) and H (input side): factor preparation ``ldl_of_inverse`` of both,
+the per-row scales, and the two-sided GPTQ-2D sweep, all through the package's public calls (which reach the kernels
+through the C ABI).  The sweep alone (the reference's own timing unit, demo.ipynb:157) is reported in ``config``.  With N > 1 ranks (one
 per GPU, launched by torchrun) every rank quantizes its own layer: the path shards by matrix and has no collective.
 Rank 0 prints one JSON line.  ``--impl reference`` times the CPU restatement of the reference's PyTorch path
 (``oracle/``) on the host cores instead, on a bounded sample scaled by the algorithmic work.
@@ -94,6 +95,33 @@ class ClockSampler:
         return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(sm_max), "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def cpu_prep_sample(size: int):
+    """Time the CPU oracle's ldl_of_inverse on one bounded sample; returns seconds."""
+    import numpy as np
+    from oracle import oracle
+
+    rng = np.random.default_rng(1)
+    x = (rng.standard_normal((2 * size, size)) * np.exp(rng.standard_normal(size))).astype(np.float32)
+    gram = x.T @ x / (2 * size)
+    gram += 0.01 * np.mean(np.diag(gram)) * np.eye(size, dtype=np.float32)
+    oracle.lib()
+    start = time.perf_counter()
+    oracle.ldl_of_inverse(gram.astype(np.float32))
+    return time.perf_counter() - start
+
+
+def cpu_layer_estimate(args):
+    """Seconds per full-size layer on the host: sweep sample and factor-preparation sample, each scaled by its work."""
+    sweep_s, cores = cpu_sweep_sample(args.cpu_sample)
+    sweep_factor = sweep_flops(args.size, args.size) / sweep_flops(args.cpu_sample, args.cpu_sample)
+    prep_size = max(256, args.cpu_sample // 2)
+    prep_s = cpu_prep_sample(prep_size)
+    prep_factor = 2 * (args.size / prep_size) ** 3
+    note = (f"oracle port (OpenMP): {args.cpu_sample}x{args.cpu_sample} INT4 sweep {sweep_s:.2f} s scaled x{sweep_factor:.1f} by m n (m + n - 2), "
+            f"plus ldl_of_inverse at n={prep_size} {prep_s:.2f} s scaled x{prep_factor:.0f} (two factors, n^3)")
+    return sweep_s * sweep_factor + prep_s * prep_factor, sweep_s + prep_s, cores, note
+
+
 def cpu_sweep_sample(size: int, threads_hint: int | None = None):
     """Time the CPU oracle's sweep (the restated reference PyTorch path) on a bounded sample; returns (seconds, cores)."""
     import numpy as np
@@ -116,20 +144,18 @@ def run_reference(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    sample = args.cpu_sample
-    factor = sweep_flops(args.size, args.size) / sweep_flops(sample, sample)
-    times = []
+    times, raw = [], []
     for step in range(args.warmup + args.steps):
-        seconds, cores = cpu_sweep_sample(sample)
+        per_layer, sample_seconds, cores, note = cpu_layer_estimate(args)
         if step >= args.warmup:
-            times.append(seconds)
-    per_layer = statistics.mean(times) * factor
-    note = f"{sample}x{sample} INT4 sweep of the oracle port (OpenMP), scaled by the algorithmic work x{factor:.1f}"
+            times.append(per_layer)
+            raw.append(sample_seconds)
+    per_layer = statistics.mean(times)
     line = {
         "impl": "reference", "metric": METRIC, "value": per_layer, "unit": "s", "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": 1e3 * statistics.mean(times), "higher_is_better": False, "scaling": "weak",
+        "warmup": args.warmup, "ms_per_step": 1e3 * statistics.mean(raw), "higher_is_better": False, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"{args.size}x{args.size} fp32 layer, INT4 symmetric per-row fp16 abs-max scales, two-sided sweep given L and U",
+        "config": {"workload": f"{args.size}x{args.size} fp32 layer from W, G, H: ldl_of_inverse x2, INT4 symmetric per-row fp16 abs-max scales, two-sided sweep",
                    "sample": note},
         "cpu_baseline": {"value": per_layer, "unit": "s", "cores": cores, "kind": "port", "sample": note},
         "e2e": {"value": per_layer, "unit": "s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -158,6 +184,7 @@ def main() -> None:
     import _abi
     import gptq_2d as G
     import quantizer_int as Q
+    import kron_factors as K
     import synthetic
 
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
@@ -171,23 +198,21 @@ def main() -> None:
     lib = _abi.library()
 
     m = n = args.size
-    # ---- untimed setup: one seeded layer per rank; its factors come from torch.linalg here ----
+    # ---- untimed setup: one seeded layer per rank (weights and the two Hessian factors) ----
     w, g, h = synthetic.make_layer(m, n, seed=1000 + rank, device=device, samples=m)
-
-    def factor(a):
-        um = torch.linalg.cholesky(a.flip(0, 1)).flip(0, 1)
-        inv = torch.linalg.solve_triangular(um, torch.eye(a.size(0), device=device, dtype=a.dtype), upper=True)
-        lower = inv.T
-        return (lower / lower.diagonal()).contiguous()
-
-    l, u = factor(g), factor(h).T.contiguous()
-    del g, h
     zero = torch.zeros(1, 1, device=device).expand(m, n)
     quantizer = functools.partial(Q.affine_quantizer_triton, qmin=-8, qmax=7)
 
-    def step(weights):
+    def sweep_only(weights, l, u):
         scale = Q.int_abs_max_scale_triton(weights, qmin=-8, qmax=7, dtype=torch.float16).expand(m, n)
         return G.gptq_2d(weights, l, u, quantizer=quantizer, quantizer_inputs=(scale, zero))
+
+    def step(weights, gram_out=g, gram_in=h):
+        l = K.ldl_of_inverse(gram_out, check=False)
+        u = K.ldl_of_inverse(gram_in, check=False).T
+        return sweep_only(weights, l, u)
+
+    l, u = K.ldl_of_inverse(g), K.ldl_of_inverse(h).T.contiguous()  # checked once: raises if a factor is not positive definite
 
     def barrier():
         if world > 1:
@@ -213,18 +238,28 @@ def main() -> None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         elapsed_ms = t.item()
     ms_per_step = elapsed_ms / args.steps
+    # the sweep alone and the preparation alone, same events, outside the headline region
+    parts = {}
+    for name, fn in (("sweep", lambda: sweep_only(w, l, u)), ("prep", lambda: (K.ldl_of_inverse(g, check=False), K.ldl_of_inverse(h, check=False)))):
+        fn()
+        torch.cuda.synchronize()
+        begin.record()
+        for _ in range(args.steps):
+            fn()
+        end.record()
+        torch.cuda.synchronize()
+        parts[name] = begin.elapsed_time(end) / args.steps
 
     # ---- end to end through the public call with HOST buffers: H2D of W, L, U and D2H of Z inside the timed region ----
-    host_w, host_l, host_u = (t.cpu().pin_memory() for t in (w, l, u))
+    host_w, host_l, host_u = (t.cpu().pin_memory() for t in (w, g, h))
     host_z = torch.empty_like(host_w).pin_memory()
-    dev_w, dev_l, dev_u = torch.empty_like(w), torch.empty_like(l), torch.empty_like(u)
+    dev_w, dev_l, dev_u = torch.empty_like(w), torch.empty_like(g), torch.empty_like(h)
 
     def e2e_step():
         dev_w.copy_(host_w, non_blocking=True)
         dev_l.copy_(host_l, non_blocking=True)
         dev_u.copy_(host_u, non_blocking=True)
-        scale = Q.int_abs_max_scale_triton(dev_w, qmin=-8, qmax=7, dtype=torch.float16).expand(m, n)
-        out = G.gptq_2d(dev_w, dev_l, dev_u, quantizer=quantizer, quantizer_inputs=(scale, zero))
+        out = step(dev_w, dev_l, dev_u)
         host_z.copy_(out, non_blocking=True)
 
     e2e_step()
@@ -277,7 +312,8 @@ def main() -> None:
         "algorithmic_flops_per_launch": far_flops / far_n if far_n else None,
         "kernel_ms": {"tile_sweep": tile_ms, "near_update": near_ms, "far_update": far_ms},
         "kernel_launches": {"tile_sweep": int(tile_n), "near_update": int(near_n), "far_update": int(far_n)},
-        "whole_sweep_tflops": sweep_flops(m, n) / (ms_per_step * 1e-3) / 1e12,
+        "whole_sweep_tflops": sweep_flops(m, n) / (parts["sweep"] * 1e-3) / 1e12,
+        "prep_tflops": 2 * (2 * float(n) ** 3 / 3) / (parts["prep"] * 1e-3) / 1e12,
         "timed_in": "separate profiled pass of the same step inside bench.py, one CUDA event pair per launch on the launching stream",
     }
 
@@ -286,10 +322,11 @@ def main() -> None:
         "ms_per_step": ms_per_step, "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
         "config": {
-            "workload": f"{m}x{n} fp32 layer, INT4 symmetric per-row fp16 abs-max scales, two-sided sweep given L and U (one layer per GPU per step)",
-            "step": "int_abs_max_scale + gptq_2d (fused engine) through the public API; factors L, U precomputed (untimed setup)",
-            "l2": "inputs larger than L2: W, L, U are 3 x %.0f MB" % (m * n * 4 / 1e6),
-            "stages": m + n - 1, "us_per_stage": ms_per_step * 1e3 / (m + n - 1),
+            "workload": f"{m}x{n} fp32 layer from W, G, H: ldl_of_inverse x2, INT4 symmetric per-row fp16 abs-max scales, two-sided sweep (one layer per GPU per step)",
+            "step": "kron_factors.ldl_of_inverse(G), ldl_of_inverse(H), int_abs_max_scale, gptq_2d (fused engine) through the public API",
+            "l2": "inputs larger than L2: W, G, H are 3 x %.0f MB" % (m * n * 4 / 1e6),
+            "sweep_ms": parts["sweep"], "prep_ms": parts["prep"],
+            "stages": m + n - 1, "sweep_us_per_stage": parts["sweep"] * 1e3 / (m + n - 1),
         },
         "clocks": clocks.summary(),
         "e2e": {"value": e2e_ms / 1e3 / world, "unit": "s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
@@ -297,13 +334,8 @@ def main() -> None:
         "roofline": roofline,
     }
     if world == 1 and not args.no_cpu_baseline:
-        sample = args.cpu_sample
-        seconds, cores = cpu_sweep_sample(sample)
-        factor_scale = sweep_flops(m, n) / sweep_flops(sample, sample)
-        line["cpu_baseline"] = {
-            "value": seconds * factor_scale, "unit": "s", "cores": cores, "kind": "port",
-            "sample": f"{sample}x{sample} INT4 sweep of the oracle port (OpenMP) took {seconds:.2f} s; scaled by the algorithmic work x{factor_scale:.1f}",
-        }
+        per_layer, _, cores, note = cpu_layer_estimate(args)
+        line["cpu_baseline"] = {"value": per_layer, "unit": "s", "cores": cores, "kind": "port", "sample": note}
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
