@@ -49,3 +49,32 @@ def feedback_factors(A: torch.Tensor, B: torch.Tensor, super_entry_shape: tuple[
     ``H = B B^T``, with ``p x p`` and ``q x q`` identity diagonal blocks for ``p x q`` super-entries."""
     p, q = super_entry_shape
     return ldl_of_inverse(A.t() @ A, size=p), ldl_of_inverse(B @ B.t(), size=q).t()
+
+
+@torch.no_grad()
+def gptq_d_sided(x: torch.Tensor, factors, *, quantizer=None, quantizer_inputs=(), **sweep_options) -> torch.Tensor:
+    """N-factor (D-sided) rounding of an ``n_1 x ... x n_D`` tensor under one unit lower triangular factor per mode
+    (Algorithm 4 of the paper; the reference's slow ``alg4``, gptq_2d_reference.py:269-294).
+
+    The D-sided sweep on ``[n_1, ..., n_D]`` equals the two-sided sweep on the row-major reshape
+    ``[n_1 ... n_{D-1}, n_D]`` with the row factor ``kron(L_1, ..., L_{D-1})`` and the column factor ``L_D^T``, so it
+    runs on the same fused engine.  The Kronecker row factor is formed explicitly here (``(n_1 ... n_{D-1})^2`` values);
+    ``quantizer`` and ``quantizer_inputs`` follow ``gptq_2d`` on the reshaped matrix.
+    """
+    import functools
+
+    import gptq_2d as engine
+
+    factors = list(factors)
+    assert x.dim() == len(factors) >= 1, "expected one factor per mode"
+    assert all(f.shape == (k, k) for f, k in zip(factors, x.shape)), "factor d must be n_d x n_d"
+    rows = x.numel() // x.size(-1) if x.numel() else 0
+    if x.numel() == 0:
+        return x.clone()
+    row_factor = functools.reduce(torch.kron, [f.contiguous() for f in factors[:-1]]) if len(factors) > 1 else torch.ones(1, 1, dtype=x.dtype, device=x.device)
+    options = dict(sweep_options)
+    if quantizer is not None:
+        options["quantizer"] = quantizer
+    z = engine.gptq_2d(x.reshape(rows, x.size(-1)), row_factor.contiguous(), factors[-1].t().contiguous(),
+                       quantizer_inputs=quantizer_inputs, **options)
+    return z.reshape(x.shape)

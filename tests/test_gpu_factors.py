@@ -77,3 +77,13 @@ def test_feedback_factors_and_errors(K):
     with pytest.raises(torch.linalg.LinAlgError):
         K.ldl_of_inverse(-torch.eye(70, device="cuda", dtype=torch.float64))
     assert K.ldl_of_inverse(torch.empty(0, 0, device="cuda")).shape == (0, 0)
+
+
+def test_d_sided_golden(K):
+    """gptq_2d_reference.py:450-478: N-factor rounding equals Algorithm 1 on the explicit Kronecker Gram (values from the reference's alg4)."""
+    g = load_golden("d_sided_fp64.npz")
+    for k in range(int(g["count"])):
+        x = cuda(g[f"x{k}"])
+        factors = [cuda(g[f"l{k}_{d}"]) for d in range(x.dim())]
+        z = K.gptq_d_sided(x, factors)
+        assert torch.equal(z.cpu(), torch.from_numpy(g[f"z{k}"])), k

@@ -1,0 +1,57 @@
+"""Host logic of the by-matrix sharding, including a two-rank run over gloo on the CPU (no GPU work: the per-matrix
+function is a stand-in)."""
+import os
+import tempfile
+
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+
+def test_layer_list_and_partition():
+    import layer_set
+
+    items = layer_set.layer_list(80)
+    assert len(items) == 560 and sum(i["m"] * i["n"] for i in items) == 80 * (2 * 8192 * 8192 + 2 * 1024 * 8192 + 3 * 28672 * 8192)
+    assert len({i["seed"] for i in items}) == 560
+    for world in (1, 2, 4, 8):
+        shares = layer_set.partition(items, world)
+        assert sorted((i["block"], i["name"]) for s in shares for i in s) == sorted((i["block"], i["name"]) for i in items)
+        loads = [sum(layer_set.work(i["m"], i["n"]) for i in s) for s in shares]
+        assert max(loads) / (sum(loads) / world) < 1.02  # longest-first dealing balances the algorithmic work
+    assert layer_set.partition(items[:3], 8)[3:] == [[]] * 5
+
+
+def _rank(rank, world, store_path, out_path):
+    import sys
+
+    from conftest import PACKAGE
+    sys.path.insert(0, PACKAGE)
+    import layer_set
+
+    dist.init_process_group("gloo", init_method=f"file://{store_path}", rank=rank, world_size=world)
+
+    def gather(obj):
+        out = [None] * world if rank == 0 else None
+        dist.gather_object(obj, out, dst=0)
+        return out
+
+    process = lambda item: {**item, "prep_ms": 1.0, "sweep_ms": float(item["m"]) / 1024, "finite": True, "codes_in_range": True, "rank": rank}
+    summary = layer_set.run(layer_set.layer_list(3, divide=64), process, rank=rank, world=world, gather=gather, barrier=dist.barrier)
+    if rank == 0:
+        import json
+        with open(out_path, "w") as f:
+            json.dump(summary, f)
+    else:
+        assert summary is None
+    dist.destroy_process_group()
+
+
+def test_two_ranks_over_gloo():
+    import json
+
+    with tempfile.TemporaryDirectory() as tmp:
+        store, out = os.path.join(tmp, "store"), os.path.join(tmp, "out.json")
+        mp.spawn(_rank, args=(2, store, out), nprocs=2, join=True)
+        summary = json.load(open(out))
+    assert summary["matrices"] == 21 and summary["n_gpus"] == 2 and len(summary["busy_s"]) == 2
+    assert summary["mean_ms_by_shape"]["448x128"]["count"] == 6 and summary["all_finite"]
