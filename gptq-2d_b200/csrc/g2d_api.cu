@@ -32,7 +32,8 @@ struct LaunchTimer {
 };
 
 // Algorithmic multiply-adds (x2 = flops) of one band update in tile mode: exact, no padding counted.
-double band_flops(int64_t m, int64_t n, int64_t s0, int64_t s1, int64_t s_end) {
+double band_flops(int64_t m, int64_t n, int64_t s0, int64_t s1, int64_t s_end, int64_t T = TILE) {
+    const int64_t TILE = T;
     const int64_t nI = ceil_div(m, TILE), nJ = ceil_div(n, TILE);
     double flops = 0;
     for (int64_t TI = 0; TI < nI; ++TI)
@@ -53,6 +54,15 @@ constexpr int kDefaultOuterTiles = 8;  // tile anti-diagonals gathered into one 
 
 inline size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 
+// The tensor-core macro updates serve one float matrix whose rows are 16-byte multiples (a TMA requirement).
+inline bool tc_eligible(const g2d_sweep_desc *d) {
+    return d->dtype == G2D_F32 && d->batch == 1 && d->m % 4 == 0 && d->n % 4 == 0 && d->reserved != 1;
+}
+inline size_t tc_extra_bytes(const g2d_sweep_desc *d) {
+    const size_t mn = align256(4 * (size_t)d->m * d->n), mm = align256(4 * (size_t)d->m * d->m), nn = align256(4 * (size_t)d->n * d->n);
+    return 256 + 4 * mn + 2 * mm + 2 * nn;
+}
+
 int check_sweep(const g2d_sweep_desc *d) {
     if (!d) return G2D_ERR_BAD_ARGUMENT;
     if (d->dtype != G2D_F32 && d->dtype != G2D_F64) return G2D_ERR_BAD_ARGUMENT;
@@ -62,11 +72,76 @@ int check_sweep(const g2d_sweep_desc *d) {
     return G2D_OK;
 }
 
+// Feedback between macro tiles: on the tensor cores when the operand planes exist, else the general FFMA update.
+template <typename F>
+int launch_macro_update(const BandArgs<F> &bm, const TcPlanes *planes, cudaStream_t stream) {
+    if (planes != nullptr) {
+        if constexpr (sizeof(F) == sizeof(float))
+            return launch_macro_update_tc(*planes, (float *)bm.y, (float *)bm.c, bm.m, bm.n, (int)bm.s0, (int)bm.s1, (int)bm.s_end, stream);
+    }
+    return launch_band_update<F>(bm, stream);
+}
+
+constexpr int MACRO = 2 * TILE;          // macro tile edge: 2 x 2 tiles
+constexpr int kDefaultOuterMacro = 4;    // macro anti-diagonals per far update (512 stages)
+
+// Macro schedule: the matrix is cut into 128 x 128 macro tiles of 2 x 2 tiles.  A macro anti-diagonal W is swept in
+// three tile launches (its even-even tiles, then the mixed ones, then the odd-odd ones) with the feedback inside each
+// macro tile applied by two small tile-level updates; feedback between macro tiles is rank-128 per macro anti-diagonal
+// (near update, into the rest of the group) and rank-512 per group (far update), so that every operand block of
+// those updates is a whole 128 x 128 block.
+template <typename F>
+int sweep_macro(const g2d_sweep_desc *d, SweepArgs<F> &a, BandArgs<F> &b64, cudaStream_t stream, LaunchTimer *timer, double *flops,
+                const TcPlanes *planes) {
+    const int nI2 = (int)ceil_div(d->m, MACRO), nJ2 = (int)ceil_div(d->n, MACRO);
+    const int waves = nI2 + nJ2 - 1;
+    const int outer = d->outer_tiles > 0 ? (d->outer_tiles + 1) / 2 : kDefaultOuterMacro;
+    BandArgs<F> bm = b64;
+    bm.P = MACRO; bm.Q = MACRO; bm.mode = BAND_GENERAL; bm.filter = 0;
+    auto timed = [&](int kind, auto &&launch) {
+        if (timer) timer->begin(kind);
+        const int status = launch();
+        if (timer) timer->end();
+        return status;
+    };
+    for (int W0 = 0; W0 < waves; W0 += outer) {
+        const int W1 = W0 + outer < waves ? W0 + outer : waves;
+        for (int W = W0; W < W1; ++W) {
+            int status = timed(0, [&] { return launch_tile_sweep<F>(a, 2 * W, stream, 1); });
+            if (status != G2D_OK) return status;
+            b64.s0 = 2 * W; b64.s1 = 2 * W + 1; b64.s_end = 2 * W + 2; b64.filter = 1;
+            status = timed(1, [&] { return launch_band_update<F>(b64, stream); });
+            if (status != G2D_OK) return status;
+            status = timed(0, [&] { return launch_tile_sweep<F>(a, 2 * W + 1, stream, 0); });
+            if (status != G2D_OK) return status;
+            b64.s0 = 2 * W + 1; b64.s1 = 2 * W + 2; b64.s_end = 2 * W + 3; b64.filter = 2;
+            status = timed(1, [&] { return launch_band_update<F>(b64, stream); });
+            if (status != G2D_OK) return status;
+            status = timed(0, [&] { return launch_tile_sweep<F>(a, 2 * W + 2, stream, 2); });
+            if (status != G2D_OK) return status;
+            if (W + 1 < W1) {
+                bm.s0 = W; bm.s1 = W + 1; bm.s_end = W1;
+                status = timed(1, [&] { return launch_macro_update<F>(bm, planes, stream); });
+                if (flops) flops[1] += band_flops(d->m, d->n, bm.s0, bm.s1, bm.s_end, MACRO) * (double)d->batch;
+                if (status != G2D_OK) return status;
+            }
+        }
+        if (W1 < waves) {
+            bm.s0 = W0; bm.s1 = W1; bm.s_end = waves;
+            const int status = timed(2, [&] { return launch_macro_update<F>(bm, planes, stream); });
+            if (flops) flops[2] += band_flops(d->m, d->n, bm.s0, bm.s1, bm.s_end, MACRO) * (double)d->batch;
+            if (status != G2D_OK) return status;
+        }
+    }
+    return G2D_OK;
+}
+
 template <typename F>
 int sweep_fused(const g2d_sweep_desc *d, cudaStream_t stream, LaunchTimer *timer = nullptr, double *flops = nullptr) {
     const int64_t count = d->batch * d->m * d->n;
     const size_t plane = align256(sizeof(F) * (size_t)count);
-    if (!d->workspace || d->workspace_bytes < 2 * plane) return G2D_ERR_WORKSPACE;
+    const bool tc = tc_eligible(d);
+    if (!d->workspace || d->workspace_bytes < 2 * plane + (tc ? tc_extra_bytes(d) : 0)) return G2D_ERR_WORKSPACE;
     if (((uintptr_t)d->workspace & 255) != 0) return G2D_ERR_WORKSPACE;
     SweepArgs<F> a;
     a.y = (F *)d->y;
@@ -87,7 +162,25 @@ int sweep_fused(const g2d_sweep_desc *d, cudaStream_t stream, LaunchTimer *timer
 
     BandArgs<F> b;
     b.y = a.y; b.c = a.c; b.e = a.e; b.l = a.l; b.u = a.u; b.l_off = a.l_off; b.u_off = a.u_off;
-    b.batch = a.batch; b.m = a.m; b.n = a.n; b.P = TILE; b.Q = TILE; b.down_into_y = 0; b.mode = BAND_TILE;
+    b.batch = a.batch; b.m = a.m; b.n = a.n; b.P = TILE; b.Q = TILE; b.down_into_y = 0; b.mode = BAND_TILE; b.filter = 0;
+    if (tc) {
+        // carve the operand planes behind C and E, prepare the static operands, run the macro schedule
+        char *p = (char *)d->workspace + 2 * plane;
+        const size_t mn = align256(4 * (size_t)d->m * d->n), mm = align256(4 * (size_t)d->m * d->m), nn = align256(4 * (size_t)d->n * d->n);
+        TcPlanes planes;
+        planes.error_flag = (int *)p; p += 256;
+        planes.et_hi = (float *)p; p += mn; planes.et_lo = (float *)p; p += mn;
+        planes.c_hi = (float *)p; p += mn; planes.c_lo = (float *)p; p += mn;
+        planes.l_hi = (float *)p; p += mm; planes.l_lo = (float *)p; p += mm;
+        planes.ut_hi = (float *)p; p += nn; planes.ut_lo = (float *)p; p += nn;
+        if (((uintptr_t)d->y & 15) != 0) return G2D_ERR_BAD_ARGUMENT;
+        if (cudaMemsetAsync(planes.error_flag, 0, sizeof(int), stream) != cudaSuccess) return G2D_ERR_CUDA;
+        const int status = tc_prepare_operands((const float *)d->l, (const float *)d->u, d->m, d->n, planes, stream);
+        if (status != G2D_OK) return status;
+        a.et_hi = planes.et_hi; a.et_lo = planes.et_lo; a.c_hi = planes.c_hi; a.c_lo = planes.c_lo;
+        return sweep_macro<F>(d, a, b, stream, timer, flops, &planes);
+    }
+    if (d->reserved == 2) return sweep_macro<F>(d, a, b, stream, timer, flops, nullptr);
 
     const int waves = a.nI + a.nJ - 1;
     const int outer = d->outer_tiles > 0 ? d->outer_tiles : kDefaultOuterTiles;
@@ -133,7 +226,7 @@ int stage_flush(const g2d_stage_desc *d, int64_t s0, int64_t s1, int64_t s_end, 
     b.y = (F *)d->y; b.c = (F *)d->c; b.e = (const F *)d->e;
     b.l = (const F *)d->l; b.u = (const F *)d->u; b.l_off = d->l_offsets; b.u_off = d->u_offsets;
     b.batch = d->batch; b.m = d->m; b.n = d->n; b.P = d->p; b.Q = d->q;
-    b.s0 = s0; b.s1 = s1; b.s_end = s_end; b.down_into_y = 1;
+    b.s0 = s0; b.s1 = s1; b.s_end = s_end; b.down_into_y = 1; b.filter = 0;
     b.mode = (d->p == 1 && d->q == 1) ? BAND_PLAIN : BAND_GENERAL;
     return launch_band_update<F>(b, stream);
 }
@@ -158,7 +251,7 @@ extern "C" int g2d_sweep_workspace_bytes(const g2d_sweep_desc *desc, size_t *byt
     const int status = check_sweep(desc);
     if (status != G2D_OK || !bytes) return status != G2D_OK ? status : G2D_ERR_BAD_ARGUMENT;
     const size_t elem = desc->dtype == G2D_F32 ? 4 : 8;
-    *bytes = 2 * align256(elem * (size_t)(desc->batch * desc->m * desc->n));
+    *bytes = 2 * align256(elem * (size_t)(desc->batch * desc->m * desc->n)) + (tc_eligible(desc) ? tc_extra_bytes(desc) : 0);
     return G2D_OK;
 }
 
@@ -189,6 +282,13 @@ extern "C" int g2d_sweep_fused_profile(const g2d_sweep_desc *desc, void *stream,
     double flops[3] = {0, 0, 0};
     status = desc->dtype == G2D_F32 ? sweep_fused<float>(desc, st, &timer, flops) : sweep_fused<double>(desc, st, &timer, flops);
     if (cudaStreamSynchronize(st) != cudaSuccess) status = status == G2D_OK ? G2D_ERR_CUDA : status;
+    if (status == G2D_OK && tc_eligible(desc)) {
+        // the tensor-core kernels report a bounded wait that ran out through a flag behind the C and E planes
+        const size_t elem = 4, plane = align256(elem * (size_t)(desc->batch * desc->m * desc->n));
+        int flag = 0;
+        if (cudaMemcpy(&flag, (const char *)desc->workspace + 2 * plane, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess || flag != 0)
+            status = G2D_ERR_CUDA;
+    }
     for (auto &it : timer.items) {
         float ms = 0;
         if (status == G2D_OK && timer.ok && cudaEventElapsedTime(&ms, it.begin, it.end) == cudaSuccess) {

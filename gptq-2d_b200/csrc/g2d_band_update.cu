@@ -191,6 +191,12 @@ __global__ void __launch_bounds__(BTH) band_update_kernel(BandArgs<F> P, int nTI
     int64_t rk_lo = (P.s0 - g.brow(i1)) * QQ, rk_hi = (P.s1 - g.brow(i0)) * QQ;
     rk_lo = max(rk_lo, (int64_t)0);
     rk_hi = min(min(rk_hi, n), g.bcol(j1) * QQ);
+    if (MODE == BAND_TILE && P.filter == 2 && !((TI & 1) && (TJ & 1))) return;
+    if (MODE == BAND_TILE && P.filter == 1) {
+        // single-stage use: the down source is tile (dk_lo / 64, TJ), the right source tile (TI, rk_lo / 64)
+        if ((TJ & 1) || ((dk_lo / TILE) & 1)) dk_hi = dk_lo;
+        if ((TI & 1) || ((rk_lo / TILE) & 1)) rk_hi = rk_lo;
+    }
     const int tid = threadIdx.x, ty = tid >> 3, tx = tid & 7;
 
     for (int64_t batch = blockIdx.z; batch < P.batch; batch += gridDim.z) {

@@ -77,10 +77,22 @@ struct SweepArgs {
     int kind;
     int64_t batch, m, n;
     int nI, nJ;  // tiles per column / per row
+    // float, single matrix, tensor-core updates only (else null): tf32 hi / lo copies of the finished tiles,
+    // E transposed ([n, m]) and the completed C ([m, n]), operands of the macro updates
+    float *et_hi = nullptr, *et_lo = nullptr, *c_hi = nullptr, *c_lo = nullptr;
 };
 
+// Operand planes of the tensor-core macro updates (all float; see g2d_macro_update_tc.cu).
+struct TcPlanes {
+    float *et_hi, *et_lo, *c_hi, *c_lo;  // written by the tile sweep
+    float *l_hi, *l_lo, *ut_hi, *ut_lo;  // written once per sweep from L and U
+    int *error_flag;                     // set when a bounded wait inside a kernel ran out
+};
+int tc_prepare_operands(const float *l, const float *u, int64_t m, int64_t n, const TcPlanes &planes, cudaStream_t stream);
+int launch_macro_update_tc(const TcPlanes &planes, float *y, float *c, int64_t m, int64_t n, int s0, int s1, int s_end, cudaStream_t stream);
+
 template <typename F>
-int launch_tile_sweep(const SweepArgs<F> &args, int S, cudaStream_t stream);
+int launch_tile_sweep(const SweepArgs<F> &args, int S, cudaStream_t stream, int parity = 0);
 
 enum BandMode { BAND_TILE = 0, BAND_PLAIN = 1, BAND_GENERAL = 2 };
 
@@ -94,6 +106,7 @@ struct BandArgs {
     int64_t s0, s1, s_end;    // sources s0..s1-1, targets s1..s_end-1
     int down_into_y;          // also add the down product into Y (the generic path keeps Y live)
     int mode;                 // BandMode
+    int filter;               // tile mode only: 0 none, 1 sources with even tile row and column only, 2 targets with odd tile row and column only
 };
 
 template <typename F>

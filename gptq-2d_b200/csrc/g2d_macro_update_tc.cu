@@ -1,0 +1,333 @@
+// Feedback between macro tiles on the tensor cores (float only): tcgen05.mma kind::tf32 with accumulators in
+// tensor memory, operands brought into shared memory by TMA (cp.async.bulk.tensor, 128-byte swizzle).
+//
+// One CTA owns one 128 x 128 target macro tile and forms both products of the band update
+//     down :  C[I, J] += sum_k L[I, k] E[k, J]      right:  Y[I, J] += sum_k C[I, k] U[k, J]
+// over the k ranges that hold the sources of the macro anti-diagonals s0..s1-1 (whole 128-blocks, no masks).
+// fp32 fidelity comes from the 3xTF32 split: every operand exists as hi = tf32(a) and lo = a - hi, and each
+// k step issues hi*hi + lo*hi + hi*lo into the same fp32 accumulator.  All four operand kinds are stored K-major
+// for the MMA: L and C as they are (rows x k), E and U transposed (columns x k); the split copies of L and U^T are
+// made once per sweep by the kernels at the end of this file, those of E^T and C by the tile sweep as it finishes
+// a tile.
+//
+// Warp roles (6 warps): warp 0 issues the TMA loads, warp 1 allocates tensor memory and issues the MMAs,
+// warps 2-5 read the accumulators (each its own 32 lanes) and add them into C / Y.  A three-stage ring of
+// 64 KB (A_hi, A_lo, B_hi, B_lo tiles of 128 x 32) is handed over with mbarriers; tcgen05.commit releases a stage
+// when its MMAs have read it.  Every wait is bounded: on time-out a flag is set and the CTA winds down.
+#include <cuda.h>
+
+#include "g2d_common.cuh"
+
+namespace g2d {
+
+constexpr int MT = 128;                    // macro tile edge
+constexpr int KC = 32;                     // k per chunk: 32 floats = one 128-byte swizzle row
+constexpr int TILE_BYTES = MT * KC * 4;    // 16 KB
+constexpr int STAGE_BYTES = 4 * TILE_BYTES;
+constexpr int STAGES = 3;
+constexpr int TC_THREADS = 192;
+constexpr uint32_t TMEM_COLS = 256;
+constexpr long long WAIT_CYCLES = 2000000000LL;  // about a second
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// false on time-out
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
+    const long long start = clock64();
+    while (!mbar_try_wait(bar, parity)) {
+        if (clock64() - start > WAIT_CYCLES) return false;
+    }
+    return true;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// K-major operand tile of 128-byte rows, 128-byte swizzle: 8-row groups 1024 bytes apart
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);   // start address
+    d |= (uint64_t)1 << 16;                       // leading byte offset (unused with swizzle)
+    d |= (uint64_t)(1024 >> 4) << 32;             // stride byte offset
+    d |= (uint64_t)1 << 46;                       // descriptor version
+    d |= (uint64_t)2 << 61;                       // SWIZZLE_128B
+    return d;
+}
+// D fp32, A and B tf32, both K-major, M = 128, N = 128
+constexpr uint32_t IDESC = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(MT >> 3) << 17) | ((uint32_t)(MT >> 4) << 24);
+
+struct TcMaps {
+    CUtensorMap l_hi, l_lo, c_hi, c_lo;      // A operands: [rows][k]
+    CUtensorMap et_hi, et_lo, ut_hi, ut_lo;  // B operands: [columns][k]
+};
+
+__global__ void __launch_bounds__(TC_THREADS) macro_update_tc_kernel(const __grid_constant__ TcMaps maps, float *y, float *c, int64_t m,
+                                                                     int64_t n, int nI2, int nJ2, int s0, int s1, int s_end,
+                                                                     int *error_flag) {
+    extern __shared__ unsigned char tc_smem_raw[];
+    __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], accum_bar;
+    __shared__ uint32_t tmem_slot;
+    __shared__ int failed;
+    // target macro tile: blockIdx.y selects the macro anti-diagonal, blockIdx.x the tile on it
+    const int W = s1 + (int)blockIdx.y;
+    const int ti_lo = max(0, W - nJ2 + 1), ti_hi = min(W + 1, nI2);
+    const int I2 = ti_lo + (int)blockIdx.x;
+    if (W >= s_end || I2 >= ti_hi) return;
+    const int J2 = W - I2;
+    // source macro rows (down) and macro columns (right) of the band
+    const int kd_lo = max(s0 - J2, 0), kd_hi = min(s1 - J2, I2);
+    const int kr_lo = max(s0 - I2, 0), kr_hi = min(s1 - I2, J2);
+    const int chunks_d = kd_hi > kd_lo ? (kd_hi - kd_lo) * (MT / KC) : 0;
+    const int chunks_r = kr_hi > kr_lo ? (kr_hi - kr_lo) * (MT / KC) : 0;
+    const int chunks = chunks_d + chunks_r;
+    if (chunks == 0) return;
+
+    const uint32_t smem_base = (smem_u32(tc_smem_raw) + 1023u) & ~1023u;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        mbar_init(&accum_bar, 1);
+        failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = tmem_slot;
+    const int i0 = I2 * MT, j0 = J2 * MT;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int ch = 0; ch < chunks; ++ch) {
+                const int stage = ch % STAGES, round = ch / STAGES;
+                if (round > 0 && !mbar_wait(&empty_bar[stage], (round - 1) & 1)) { failed = 1; break; }
+                const bool down = ch < chunks_d;
+                const int k = down ? kd_lo * MT + ch * KC : kr_lo * MT + (ch - chunks_d) * KC;
+                const uint32_t dst = smem_base + stage * STAGE_BYTES;
+                mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
+                tma_load_2d(dst, down ? &maps.l_hi : &maps.c_hi, k, i0, &full_bar[stage]);
+                tma_load_2d(dst + TILE_BYTES, down ? &maps.l_lo : &maps.c_lo, k, i0, &full_bar[stage]);
+                tma_load_2d(dst + 2 * TILE_BYTES, down ? &maps.et_hi : &maps.ut_hi, k, j0, &full_bar[stage]);
+                tma_load_2d(dst + 3 * TILE_BYTES, down ? &maps.et_lo : &maps.ut_lo, k, j0, &full_bar[stage]);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            bool ok = true;
+            for (int ch = 0; ch < chunks && ok; ++ch) {
+                const int stage = ch % STAGES, round = ch / STAGES;
+                if (!mbar_wait(&full_bar[stage], round & 1)) { failed = 1; ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const bool down = ch < chunks_d;
+                const uint32_t d_addr = tmem + (down ? 0u : (uint32_t)MT);
+                const bool first = down ? ch == 0 : ch == chunks_d;
+                const uint32_t a_hi = smem_base + stage * STAGE_BYTES, a_lo = a_hi + TILE_BYTES, b_hi = a_hi + 2 * TILE_BYTES,
+                               b_lo = a_hi + 3 * TILE_BYTES;
+#pragma unroll
+                for (int ks = 0; ks < KC / 8; ++ks) {
+                    const uint32_t off = ks * 32;  // 8 tf32 values = 32 bytes along the swizzled row
+                    umma_tf32(d_addr, umma_desc(a_hi + off), umma_desc(b_hi + off), IDESC, (first && ks == 0) ? 0u : 1u);
+                    umma_tf32(d_addr, umma_desc(a_lo + off), umma_desc(b_hi + off), IDESC, 1u);
+                    umma_tf32(d_addr, umma_desc(a_hi + off), umma_desc(b_lo + off), IDESC, 1u);
+                }
+                umma_commit(&empty_bar[stage]);  // arrives when the MMAs above have read the stage
+            }
+            umma_commit(&accum_bar);             // arrives when every MMA issued so far has completed
+        }
+    } else {
+        // epilogue warps: lanes 32 q .. 32 q + 31 of tensor memory, q = warp % 4
+        const int q = warp & 3;
+        const bool ok = mbar_wait(&accum_bar, 0);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (!ok) failed = 1;
+        const int64_t row = (int64_t)i0 + q * 32 + lane;
+        const bool go = __all_sync(0xffffffffu, ok && !failed);  // warp-uniform: the tensor-memory loads are warp-wide
+        if (go) {
+            for (int prod = 0; prod < 2; ++prod) {
+                if ((prod == 0 ? chunks_d : chunks_r) == 0) continue;
+                float *plane = prod == 0 ? c : y;
+                for (int cb = 0; cb < MT / 32; ++cb) {
+                    uint32_t v[32];
+                    const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(prod * MT + cb * 32);
+                    asm volatile(
+                        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+                          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+                          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+                          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                        : "r"(taddr)
+                        : "memory");
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if (row < m) {
+                        float *p = plane + row * n + j0 + cb * 32;
+#pragma unroll
+                        for (int x = 0; x < 32; x += 4) {
+                            if ((int64_t)j0 + cb * 32 + x < n) {  // n is a multiple of 4: a group is inside or outside as a whole
+                                float4 t = *reinterpret_cast<float4 *>(p + x);
+                                t.x += __uint_as_float(v[x]);
+                                t.y += __uint_as_float(v[x + 1]);
+                                t.z += __uint_as_float(v[x + 2]);
+                                t.w += __uint_as_float(v[x + 3]);
+                                *reinterpret_cast<float4 *>(p + x) = t;
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        if (failed) {
+            // give outstanding loads and MMAs a bounded chance to land before the memory they target is released
+            if (lane == 0) mbar_wait(&accum_bar, 0);
+            __syncwarp();
+        }
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    }
+    if (threadIdx.x == 0 && failed && error_flag) atomicExch(error_flag, 1);
+}
+
+// ---- one-time operand preparation ---------------------------------------------------------------------
+
+__device__ __forceinline__ void split_tf32(float a, float &hi, float &lo) {
+    uint32_t h;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(a));
+    hi = __uint_as_float(h);
+    lo = a - hi;
+}
+
+// L (row-major, read strictly below the diagonal) -> hi / lo copies with zeros elsewhere
+__global__ void split_lower_kernel(const float *__restrict__ l, int64_t m, float *__restrict__ hi, float *__restrict__ lo) {
+    const int64_t total = m * m;
+    for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = t / m, cidx = t % m;
+        float h = 0.f, o = 0.f;
+        if (cidx < r) split_tf32(l[t], h, o);
+        hi[t] = h;
+        lo[t] = o;
+    }
+}
+
+// U (row-major, read strictly above the diagonal) -> transposed hi / lo copies: out[j][k] = U[k][j] for k < j
+__global__ void split_upper_transposed_kernel(const float *__restrict__ u, int64_t n, float *__restrict__ hi, float *__restrict__ lo) {
+    __shared__ float tile[32][33];
+    const int64_t tiles = ceil_div(n, 32);
+    for (int64_t b = blockIdx.x; b < tiles * tiles; b += gridDim.x) {
+        const int64_t k0 = (b / tiles) * 32, j0 = (b % tiles) * 32;  // source block: rows k, columns j
+        for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+            const int64_t k = k0 + r, j = j0 + threadIdx.x;
+            tile[r][threadIdx.x] = (k < n && j < n && k < j) ? u[k * n + j] : 0.f;
+        }
+        __syncthreads();
+        for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+            const int64_t j = j0 + r, k = k0 + threadIdx.x;
+            if (j < n && k < n) {
+                float h, o;
+                split_tf32(tile[threadIdx.x][r], h, o);
+                hi[j * n + k] = h;
+                lo[j * n + k] = o;
+            }
+        }
+        __syncthreads();
+    }
+}
+
+// ---- host side ---------------------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void *ptr = nullptr;
+        cudaDriverEntryPointQueryResult result;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) == cudaSuccess &&
+            result == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    return fn;
+}
+
+// row-major fp32 matrix [rows][cols]; boxes of 128 rows x 32 columns, 128-byte swizzle, zero fill outside
+static bool make_map(CUtensorMap *map, const float *base, int64_t rows, int64_t cols) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)cols * sizeof(float)};
+    const cuuint32_t box[2] = {KC, MT};
+    const cuuint32_t elem[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+int tc_prepare_operands(const float *l, const float *u, int64_t m, int64_t n, const TcPlanes &pl, cudaStream_t stream) {
+    split_lower_kernel<<<148 * 8, 256, 0, stream>>>(l, m, pl.l_hi, pl.l_lo);
+    if (check_launch() != G2D_OK) return G2D_ERR_CUDA;
+    split_upper_transposed_kernel<<<148 * 8, dim3(32, 8), 0, stream>>>(u, n, pl.ut_hi, pl.ut_lo);
+    return check_launch();
+}
+
+int launch_macro_update_tc(const TcPlanes &pl, float *y, float *c, int64_t m, int64_t n, int s0, int s1, int s_end, cudaStream_t stream) {
+    static bool configured[64] = {};
+    const size_t smem = (size_t)STAGES * STAGE_BYTES + 1024;
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return G2D_ERR_CUDA;
+    if (!configured[device]) {
+        if (cudaFuncSetAttribute(macro_update_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return G2D_ERR_CUDA;
+        configured[device] = true;
+    }
+    TcMaps maps;
+    if (!make_map(&maps.l_hi, pl.l_hi, m, m) || !make_map(&maps.l_lo, pl.l_lo, m, m) || !make_map(&maps.c_hi, pl.c_hi, m, n) ||
+        !make_map(&maps.c_lo, pl.c_lo, m, n) || !make_map(&maps.et_hi, pl.et_hi, n, m) || !make_map(&maps.et_lo, pl.et_lo, n, m) ||
+        !make_map(&maps.ut_hi, pl.ut_hi, n, n) || !make_map(&maps.ut_lo, pl.ut_lo, n, n))
+        return G2D_ERR_CUDA;
+    const int nI2 = (int)ceil_div(m, MT), nJ2 = (int)ceil_div(n, MT);
+    if (s_end <= s1) return G2D_OK;
+    dim3 grid((unsigned)(nI2 < nJ2 ? nI2 : nJ2), (unsigned)(s_end - s1));
+    macro_update_tc_kernel<<<grid, TC_THREADS, smem, stream>>>(maps, y, c, m, n, nI2, nJ2, s0, s1, s_end, pl.error_flag);
+    return check_launch();
+}
+
+}  // namespace g2d

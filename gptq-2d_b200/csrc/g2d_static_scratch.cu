@@ -44,6 +44,7 @@ extern "C" int g2d_sweep_fused_static(const g2d_sweep_desc *desc, void *stream) 
     g2d_sweep_desc local = *desc;
     local.workspace = nullptr;
     local.workspace_bytes = 0;
+    local.reserved = 1;  // the tile schedule: its scratch is the two planes this array is sized for
     size_t need = 0;
     const int status = g2d_sweep_workspace_bytes(&local, &need);
     if (status != G2D_OK) return status;

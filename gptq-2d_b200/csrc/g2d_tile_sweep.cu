@@ -78,7 +78,7 @@ __device__ __forceinline__ void mm16(F *__restrict__ D, const F *__restrict__ A,
 }
 
 template <typename F, int KIND>
-__global__ void __launch_bounds__(TTH) tile_sweep_kernel(SweepArgs<F> P, int S) {
+__global__ void __launch_bounds__(TTH) tile_sweep_kernel(SweepArgs<F> P, int S, int i_first, int i_step) {
     extern __shared__ __align__(16) unsigned char g2d_smem[];
     F *Ys = reinterpret_cast<F *>(g2d_smem);  // X + right feedback; the errors E once a sub-tile is swept
     F *Cs = Ys + TILE * LD;                   // down feedback; the completed C once a sub-tile is swept
@@ -87,7 +87,7 @@ __global__ void __launch_bounds__(TTH) tile_sweep_kernel(SweepArgs<F> P, int S) 
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int k = lane & 15, half = lane >> 4;
-    const int I = max(0, S - P.nJ + 1) + (int)blockIdx.x, J = S - I;
+    const int I = i_first + i_step * (int)blockIdx.x, J = S - I;  // tiles of the anti-diagonal S, every one or every second
     const int64_t i0 = (int64_t)I * TILE, j0 = (int64_t)J * TILE;
     const int64_t m = P.m, n = P.n;
     const bool full = i0 + TILE <= m && j0 + TILE <= n;
@@ -276,6 +276,35 @@ __global__ void __launch_bounds__(TTH) tile_sweep_kernel(SweepArgs<F> P, int S) 
             }
         }
 
+        // ---- operands of the tensor-core macro updates: tf32 hi / lo of E (transposed) and of the completed C ----
+        if (P.c_hi != nullptr) {
+            if constexpr (sizeof(F) == sizeof(float)) {
+                for (int idx = tid; idx < TILE * TILE; idx += TTH) {
+                    {   // C[i][j], consecutive threads along j
+                        const int r = idx / TILE, c = idx % TILE;
+                        const int64_t gi = i0 + r, gj = j0 + c;
+                        if (gi < m && gj < n) {
+                            const float v = (float)Cs[r * LD + c];
+                            uint32_t h;
+                            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(v));
+                            P.c_hi[gi * n + gj] = __uint_as_float(h);
+                            P.c_lo[gi * n + gj] = v - __uint_as_float(h);
+                        }
+                    }
+                    {   // E^T[j][i], consecutive threads along i
+                        const int c = idx / TILE, r = idx % TILE;
+                        const int64_t gi = i0 + r, gj = j0 + c;
+                        if (gi < m && gj < n) {
+                            const float v = (float)Ys[r * LD + c];
+                            uint32_t h;
+                            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(v));
+                            P.et_hi[gj * m + gi] = __uint_as_float(h);
+                            P.et_lo[gj * m + gi] = v - __uint_as_float(h);
+                        }
+                    }
+                }
+            }
+        }
         // ---- store the errors and the completed C of the tile; Z went out entry by entry ----
         if (vec) {
             constexpr int PER = TILE * TILE / 4 / TTH;
@@ -303,7 +332,7 @@ __global__ void __launch_bounds__(TTH) tile_sweep_kernel(SweepArgs<F> P, int S) 
 }
 
 template <typename F, int KIND>
-static int launch_kind(const SweepArgs<F> &args, int S, cudaStream_t stream) {
+static int launch_kind(const SweepArgs<F> &args, int S, int parity, cudaStream_t stream) {
     // the opt-in to more than 48 KB of dynamic shared memory is per device
     static bool configured[64] = {};
     const size_t smem = sizeof(F) * (3 * TILE * LD + 2 * NSUB * DBLK + 2 * DBLK);
@@ -316,22 +345,32 @@ static int launch_kind(const SweepArgs<F> &args, int S, cudaStream_t stream) {
     }
     const int i_lo = S - args.nJ + 1 > 0 ? S - args.nJ + 1 : 0;
     const int i_hi = S + 1 < args.nI ? S + 1 : args.nI;
-    dim3 grid((unsigned)(i_hi - i_lo), (unsigned)(args.batch < 65535 ? args.batch : 65535));
-    tile_sweep_kernel<F, KIND><<<grid, TTH, smem, stream>>>(args, S);
+    // parity 0: every tile of the anti-diagonal; 1: tiles with even row and column index; 2: odd row and column index
+    int first = i_lo, step = 1, count = i_hi - i_lo;
+    if (parity != 0) {
+        const int want = parity == 1 ? 0 : 1;
+        if ((S & 1) != 0) return G2D_OK;  // row + column parity is even for both selections
+        first = i_lo + (((i_lo & 1) != want) ? 1 : 0);
+        step = 2;
+        count = first < i_hi ? (i_hi - first + 1) / 2 : 0;
+    }
+    if (count <= 0) return G2D_OK;
+    dim3 grid((unsigned)count, (unsigned)(args.batch < 65535 ? args.batch : 65535));
+    tile_sweep_kernel<F, KIND><<<grid, TTH, smem, stream>>>(args, S, first, step);
     return check_launch();
 }
 
 template <typename F>
-int launch_tile_sweep(const SweepArgs<F> &args, int S, cudaStream_t stream) {
+int launch_tile_sweep(const SweepArgs<F> &args, int S, cudaStream_t stream, int parity) {
     switch (args.kind) {
-    case G2D_Q_ROUND: return launch_kind<F, G2D_Q_ROUND>(args, S, stream);
-    case G2D_Q_AFFINE: return launch_kind<F, G2D_Q_AFFINE>(args, S, stream);
-    case G2D_Q_FORCED: return launch_kind<F, G2D_Q_FORCED>(args, S, stream);
+    case G2D_Q_ROUND: return launch_kind<F, G2D_Q_ROUND>(args, S, parity, stream);
+    case G2D_Q_AFFINE: return launch_kind<F, G2D_Q_AFFINE>(args, S, parity, stream);
+    case G2D_Q_FORCED: return launch_kind<F, G2D_Q_FORCED>(args, S, parity, stream);
     default: return G2D_ERR_UNSUPPORTED;
     }
 }
 
-template int launch_tile_sweep<float>(const SweepArgs<float> &, int, cudaStream_t);
-template int launch_tile_sweep<double>(const SweepArgs<double> &, int, cudaStream_t);
+template int launch_tile_sweep<float>(const SweepArgs<float> &, int, cudaStream_t, int);
+template int launch_tile_sweep<double>(const SweepArgs<double> &, int, cudaStream_t, int);
 
 }  // namespace g2d

@@ -86,6 +86,10 @@ def _row_major(t: torch.Tensor) -> torch.Tensor:
 # fused engine
 # --------------------------------------------------------------------------------------------------------
 
+# Launch schedule of the fused engine: 0 lets the library choose, 1 forces the tile schedule (64 x 64 tiles, FFMA
+# updates), 2 forces the macro schedule (128 x 128 macro tiles; tensor-core updates where the library has them).
+SWEEP_SCHEDULE = 0
+
 _AFFINE_PLAIN = (quantizer_int.affine_quantizer_cuda,)
 _AFFINE_SUPER = (quantizer_int.affine_quantizer_super_entry_cuda,)
 
@@ -139,6 +143,7 @@ def _sweep_fused(y, l, u, batch_shape, options: dict, quantizer_inputs, *, force
     if y_pre is not None:
         desc.y_pre = y_pre.data_ptr()
     desc.outer_tiles = outer_tiles
+    desc.reserved = SWEEP_SCHEDULE
     size = ctypes.c_size_t()
     _abi.check(lib.g2d_sweep_workspace_bytes(ctypes.byref(desc), ctypes.byref(size)), "g2d_sweep_workspace_bytes")
     workspace = torch.empty(size.value, dtype=torch.uint8, device=y.device)

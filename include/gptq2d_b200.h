@@ -62,7 +62,7 @@ typedef struct g2d_sweep_desc {
     void *workspace;             /* g2d_sweep_workspace_bytes() bytes, 256-byte aligned */
     size_t workspace_bytes;
     int32_t outer_tiles;         /* tile anti-diagonals per far update; 0 selects the default */
-    int32_t reserved;
+    int32_t reserved;            /* launch schedule: 0 library default, 1 tile schedule, 2 macro schedule */
 } g2d_sweep_desc;
 
 const char *g2d_status_string(int status);
@@ -110,7 +110,7 @@ unsigned long long g2d_launch_count(void);
 typedef struct g2d_stage_desc {
     int32_t dtype;
     int32_t p, q;                /* super-entry shape; 1, 1 for plain entries */
-    int32_t reserved;
+    int32_t reserved;            /* must be 0 */
     int64_t batch, m, n;
     void *y;                     /* live Y (X plus every push so far; quantized where done) */
     void *c;                     /* running buffer C = L E (gptq_2d.py:1324) */

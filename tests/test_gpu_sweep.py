@@ -35,7 +35,17 @@ def python_round(y_flat, selection, *, out):
     torch.round(selected, out=out)
 
 
-def test_fused_round_fp64_golden(api):
+@pytest.fixture(params=[1, 2], ids=["tile-schedule", "macro-schedule"])
+def schedule(request, api):
+    """Run a test under both launch schedules of the fused engine."""
+    G, _ = api
+    before = G.SWEEP_SCHEDULE
+    G.SWEEP_SCHEDULE = request.param
+    yield request.param
+    G.SWEEP_SCHEDULE = before
+
+
+def test_fused_round_fp64_golden(api, schedule):
     G, _ = api
     g = load_golden("sweep_fp64.npz")
     for k, (m, n, p, q) in enumerate(g["cases"]):
@@ -71,7 +81,7 @@ def test_generic_engine_fp64_golden(api):
         assert torch.equal(z.cpu(), expected)
 
 
-def test_default_blocks_medium_fp64(api, oracle):
+def test_default_blocks_medium_fp64(api, oracle, schedule):
     """Default block sizes (32 / 512 and 8 / 64) on a size that flushes at both levels."""
     G, _ = api
     rng = np.random.default_rng(5)
@@ -87,7 +97,7 @@ def test_default_blocks_medium_fp64(api, oracle):
     assert torch.equal(z.cpu(), expected)
 
 
-def test_batches_inplace_and_quantizer_inputs(api):
+def test_batches_inplace_and_quantizer_inputs(api, schedule):
     """test_gptq_2d.py:129-147: broadcast batches, per-entry scales, in and out of place, both engines."""
     G, Q = api
     g = load_golden("sweep_batched_fp64.npz")
@@ -125,7 +135,7 @@ def _objective(z, x, g, h):
     return ((g.double() @ r) * (r @ h.double())).sum().item()
 
 
-def test_config0_fp32(api):
+def test_config0_fp32(api, schedule):
     """BASELINE config 0 (256 x 256 fp32 INT4, fp16 row scales) and its 64 x 64 companion."""
     G, Q = api
     for n in (64, 256):
@@ -147,7 +157,7 @@ def test_config0_fp32(api):
 
 
 @pytest.mark.parametrize("m,n", [(256, 256), (1024, 1024), (320, 1100)])
-def test_teacher_forced_fp32(api, oracle, m, n):
+def test_teacher_forced_fp32(api, oracle, m, n, schedule):
     """Appendix-C style parity at fp32: with the rounding decisions imposed from the oracle's run, the engine's
     pre-rounding values must lead to the same codes except within 1e-5 code units of a tie."""
     G, Q = api
@@ -174,7 +184,7 @@ def test_teacher_forced_fp32(api, oracle, m, n):
     assert (distance_to_tie[mismatch] <= 2e-5).all()
 
 
-def test_self_consistency_large_fp32(api):
+def test_self_consistency_large_fp32(api, schedule):
     """Size-independent properties on a larger free run: Z is the quantizer applied to the engine's own
     pre-rounding values, and Z - X = L E U with E = Z - Y_pre (the defining identity of the sweep)."""
     import _abi
