@@ -28,6 +28,7 @@ constexpr int STAGES = 3;
 constexpr int TC_THREADS = 192;
 constexpr uint32_t TMEM_COLS = 256;
 constexpr long long WAIT_CYCLES = 2000000000LL;  // about a second
+constexpr int RB_I = 8, RB_J = 16;               // rasterisation block of the far updates: 128 macro tiles, about one wave of CTAs
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -92,17 +93,28 @@ struct TcMaps {
 
 __global__ void __launch_bounds__(TC_THREADS) macro_update_tc_kernel(const __grid_constant__ TcMaps maps, float *y, float *c, int64_t m,
                                                                      int64_t n, int nI2, int nJ2, int s0, int s1, int s_end,
-                                                                     int *error_flag) {
+                                                                     int raster, int *error_flag) {
     extern __shared__ unsigned char tc_smem_raw[];
     __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], accum_bar;
     __shared__ uint32_t tmem_slot;
     __shared__ int failed;
-    // target macro tile: blockIdx.y selects the macro anti-diagonal, blockIdx.x the tile on it
-    const int W = s1 + (int)blockIdx.y;
-    const int ti_lo = max(0, W - nJ2 + 1), ti_hi = min(W + 1, nI2);
-    const int I2 = ti_lo + (int)blockIdx.x;
-    if (W >= s_end || I2 >= ti_hi) return;
-    const int J2 = W - I2;
+    // Target macro tile.  With gridDim.y > 1, blockIdx.y selects the macro anti-diagonal and blockIdx.x the tile on it
+    // (few anti-diagonals: near updates).  Otherwise the whole macro grid is walked in RB_I x RB_J blocks, so that the
+    // CTAs resident at one time cover a compact patch and share their L / C row strips and E^T / U^T column strips in L2.
+    int I2, J2;
+    if (raster == 0) {
+        const int W = s1 + (int)blockIdx.y;
+        const int ti_lo = max(0, W - nJ2 + 1), ti_hi = min(W + 1, nI2);
+        I2 = ti_lo + (int)blockIdx.x;
+        if (W >= s_end || I2 >= ti_hi) return;
+        J2 = W - I2;
+    } else {
+        const int blocks_j = (nJ2 + RB_J - 1) / RB_J;
+        const int blk = (int)blockIdx.x / (RB_I * RB_J), within = (int)blockIdx.x % (RB_I * RB_J);
+        I2 = (blk / blocks_j) * RB_I + within / RB_J;
+        J2 = (blk % blocks_j) * RB_J + within % RB_J;
+        if (I2 >= nI2 || J2 >= nJ2 || I2 + J2 < s1 || I2 + J2 >= s_end) return;
+    }
     // source macro rows (down) and macro columns (right) of the band
     const int kd_lo = max(s0 - J2, 0), kd_hi = min(s1 - J2, I2);
     const int kr_lo = max(s0 - I2, 0), kr_hi = min(s1 - I2, J2);
@@ -201,12 +213,10 @@ __global__ void __launch_bounds__(TC_THREADS) macro_update_tc_kernel(const __gri
 #pragma unroll
                         for (int x = 0; x < 32; x += 4) {
                             if ((int64_t)j0 + cb * 32 + x < n) {  // n is a multiple of 4: a group is inside or outside as a whole
-                                float4 t = *reinterpret_cast<float4 *>(p + x);
-                                t.x += __uint_as_float(v[x]);
-                                t.y += __uint_as_float(v[x + 1]);
-                                t.z += __uint_as_float(v[x + 2]);
-                                t.w += __uint_as_float(v[x + 3]);
-                                *reinterpret_cast<float4 *>(p + x) = t;
+                                // one CTA owns each target entry, so the reduction needs no read-back and stays deterministic
+                                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p + x), "f"(__uint_as_float(v[x])),
+                                             "f"(__uint_as_float(v[x + 1])), "f"(__uint_as_float(v[x + 2])), "f"(__uint_as_float(v[x + 3]))
+                                             : "memory");
                             }
                         }
                     }
@@ -325,8 +335,13 @@ int launch_macro_update_tc(const TcPlanes &pl, float *y, float *c, int64_t m, in
         return G2D_ERR_CUDA;
     const int nI2 = (int)ceil_div(m, MT), nJ2 = (int)ceil_div(n, MT);
     if (s_end <= s1) return G2D_OK;
+    const int raster = s_end - s1 > 8 ? 1 : 0;
     dim3 grid((unsigned)(nI2 < nJ2 ? nI2 : nJ2), (unsigned)(s_end - s1));
-    macro_update_tc_kernel<<<grid, TC_THREADS, smem, stream>>>(maps, y, c, m, n, nI2, nJ2, s0, s1, s_end, pl.error_flag);
+    if (raster) {
+        const int64_t blocks = ceil_div(nI2, RB_I) * ceil_div(nJ2, RB_J);
+        grid = dim3((unsigned)(blocks * RB_I * RB_J), 1);
+    }
+    macro_update_tc_kernel<<<grid, TC_THREADS, smem, stream>>>(maps, y, c, m, n, nI2, nJ2, s0, s1, s_end, raster, pl.error_flag);
     return check_launch();
 }
 
