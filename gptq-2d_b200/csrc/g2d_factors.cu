@@ -174,47 +174,55 @@ __global__ void __launch_bounds__(FTH) ldl_syrk_kernel(F *a, int64_t n, int kb) 
     }
 }
 
-// ---- step 2: block row i of Lf = T^{-1}; CTA j < i computes Lf[i, j], CTA i copies T_ii^{-1} ----
+// ---- step 2: Lf = T^{-1} by doubling.  The 64 x 64 diagonal blocks of Lf are the inverted diagonal blocks of T.
+// At level b (64, 128, ...) every aligned pair of finished b x b diagonal blocks [A^{-1} 0; . B^{-1}] is completed by
+//     X = -B^{-1} (C A^{-1}),   C = T[second half rows, first half columns],
+// as two batched tile products over all pairs: W = C A^{-1} into scratch, then X = -B^{-1} W into Lf.  Both inverses
+// are lower triangular, which bounds the k range of every output tile. ----
 template <typename F>
-__global__ void __launch_bounds__(FTH) ldl_trinv_kernel(const F *a, int64_t n, int i, const F *tinv, F *out) {
+__global__ void __launch_bounds__(FTH) ldl_copy_diag_inverse_kernel(const F *tinv, int64_t n, F *out) {
+    const int i = blockIdx.x;
+    const int64_t r0 = (int64_t)i * FB;
+    const int bs = (int)min((int64_t)FB, n - r0);
+    for (int idx = threadIdx.x; idx < FB * FB; idx += FTH) {
+        const int r = idx / FB, c = idx % FB;
+        if (r < bs && c < bs) out[(r0 + r) * n + r0 + c] = tinv[(int64_t)i * FB * FB + idx];
+    }
+}
+
+// second == false: W[pair block] = C A^{-1};  second == true: Lf[pair block] = -B^{-1} W
+template <typename F>
+__global__ void __launch_bounds__(FTH) ldl_trinv_level_kernel(const F *a, int64_t n, int64_t b, F *w, F *out, bool second) {
     __shared__ __align__(16) F As[FK * FLD];
     __shared__ __align__(16) F Bs[FK * FLD];
-    const int j = blockIdx.x;
-    const int64_t r0 = (int64_t)i * FB, c0 = (int64_t)j * FB;
-    const int bs = (int)min((int64_t)FB, n - r0);
-    const F *ti = tinv + (int64_t)i * FB * FB;
-    const int tid = threadIdx.x, ty = tid >> 3, tx = tid & 7;
-    if (j == i) {
-        for (int idx = tid; idx < FB * FB; idx += FTH) {
-            const int r = idx / FB, c = idx % FB;
-            if (r < bs && c < bs) out[(r0 + r) * n + c0 + c] = ti[idx];
-        }
-        return;
-    }
+    const int64_t r0 = (int64_t)blockIdx.x * 2 * b, r1 = r0 + b;  // first half rows [r0, r1), second half rows [r1, r2)
+    if (r1 >= n) return;
+    const int64_t r2 = min(r0 + 2 * b, n);
+    const int64_t ti = blockIdx.y, tj = blockIdx.z;  // output tile inside the b x b off-diagonal block
+    const int64_t row0 = r1 + ti * FB, col0 = r0 + tj * FB;
+    if (row0 >= r2) return;
+    const int64_t rows = min((int64_t)FB, r2 - row0);
     F acc[8][8];
     zero_acc(acc);
-    // R = sum_{k in [j*64, i*64)} T[i rows, k] Lf[k, j cols]
-    const int64_t k_lo = c0, K = r0 - c0;
-    tile_product<F>(acc, K, [&](int r, int64_t k) { return r < bs ? a[(r0 + r) * n + k_lo + k] : (F)0; },
-                    [&](int64_t k, int c) { return out[(k_lo + k) * n + c0 + c]; }, As, Bs, true);
-    // park R in the output block (this CTA owns it), then Lf[i, j] = -T_ii^{-1} R
-    F *rblk = out + r0 * n + c0;
-#pragma unroll
-    for (int x = 0; x < 8; ++x) {
-        const int r = own8(ty, x);
-#pragma unroll
-        for (int y = 0; y < 8; ++y)
-            if (r < bs) rblk[(int64_t)r * n + own8(tx, y)] = acc[x][y];
+    if (!second) {
+        // W[i][j] = sum_{k >= j} C[i][k] A^{-1}[k][j]: k from the output tile's first column to the end of the first half
+        const int64_t k_lo = col0, K = r1 - col0;
+        tile_product<F>(acc, K, [&](int r, int64_t k) { return r < rows ? a[(row0 + r) * n + k_lo + k] : (F)0; },
+                        [&](int64_t k, int c) { return out[(k_lo + k) * n + col0 + c]; }, As, Bs, true);
+    } else {
+        // X[i][j] = -sum_{k <= i} B^{-1}[i][k] W[k][j]: k from the start of the second half through the output tile's rows
+        const int64_t k_lo = r1, K = min(row0 + FB, r2) - r1;
+        tile_product<F>(acc, K, [&](int r, int64_t k) { return r < rows ? out[(row0 + r) * n + k_lo + k] : (F)0; },
+                        [&](int64_t k, int c) { return w[(k_lo + k) * n + col0 + c]; }, As, Bs, true);
     }
-    __syncthreads();
-    zero_acc(acc);
-    tile_product<F>(acc, bs, [&](int r, int64_t k) { return ti[r * FB + k]; }, [&](int64_t k, int c) { return rblk[k * n + c]; }, As, Bs, true);
+    const int tid = threadIdx.x, ty = tid >> 3, tx = tid & 7;
+    F *dst = second ? out : w;
 #pragma unroll
     for (int x = 0; x < 8; ++x) {
         const int r = own8(ty, x);
 #pragma unroll
         for (int y = 0; y < 8; ++y)
-            if (r < bs) out[(r0 + r) * n + c0 + own8(tx, y)] = -acc[x][y];
+            if (r < rows) dst[(row0 + r) * n + col0 + own8(tx, y)] = second ? -acc[x][y] : acc[x][y];
     }
 }
 
@@ -283,8 +291,16 @@ int ldl_run(int64_t n, F *a, int size, F *out, int *flag, void *workspace, cudaS
             if (check_launch() != G2D_OK) return G2D_ERR_CUDA;
         }
     }
-    for (int i = 0; i < nb; ++i) {
-        ldl_trinv_kernel<F><<<i + 1, FTH, 0, st>>>(a, n, i, tinv, out);
+    ldl_copy_diag_inverse_kernel<F><<<nb, FTH, 0, st>>>(tinv, n, out);
+    if (check_launch() != G2D_OK) return G2D_ERR_CUDA;
+    F *w = dblk + n * (int64_t)FB;  // [n][n] scratch of the doubling steps
+    for (int64_t b = FB; b < n; b *= 2) {
+        const int64_t pairs = ceil_div(n, 2 * b), tiles = b / FB;
+        if (tiles > 65535) return G2D_ERR_TOO_LARGE;
+        dim3 grid((unsigned)pairs, (unsigned)tiles, (unsigned)tiles);
+        ldl_trinv_level_kernel<F><<<grid, FTH, 0, st>>>(a, n, b, w, out, false);
+        if (check_launch() != G2D_OK) return G2D_ERR_CUDA;
+        ldl_trinv_level_kernel<F><<<grid, FTH, 0, st>>>(a, n, b, w, out, true);
         if (check_launch() != G2D_OK) return G2D_ERR_CUDA;
     }
     const int64_t work = n * (n / size);
@@ -305,7 +321,7 @@ using namespace g2d;
 static size_t ldl_bytes(int dtype, int64_t n) {
     const size_t elem = dtype == G2D_F32 ? 4 : 8;
     const size_t nb = (size_t)ceil_div(n, FB);
-    return ((nb * FB * FB + (size_t)n * FB) * elem + 255) & ~(size_t)255;
+    return ((nb * FB * FB + (size_t)n * FB + (size_t)n * n) * elem + 255) & ~(size_t)255;
 }
 
 extern "C" int g2d_ldl_workspace_bytes(int dtype, int64_t n, size_t *bytes) {
