@@ -42,6 +42,22 @@ __device__ __forceinline__ F affine_value(F y, F scale, F zp, F qmin, F qmax) {
     return mul_rn(sub_rn(t, zp), scale);
 }
 
+// The same value with the division done as a product with a precomputed reciprocal `rc` of the scale plus one
+// residual correction: q = y rc, q += (y - q s) rc.  With rc within half an ulp of 1 / scale this is the IEEE
+// quotient except, rarely, in its last bit, which can change the result only within one ulp of a rounding tie.
+// Used inside the fused float sweep, where the exact division sits on the critical path of every stage.
+__device__ __forceinline__ float affine_value_rcp(float y, float scale, float zp, float rc, float qmin, float qmax) {
+    const float q0 = y * rc;
+    const float q = fmaf(fmaf(-q0, scale, y), rc, q0);
+    float t = rintf(__fadd_rn(q, zp));
+    t = t < qmin ? qmin : t;
+    t = t > qmax ? qmax : t;
+    return __fmul_rn(__fsub_rn(t, zp), scale);
+}
+__device__ __forceinline__ double affine_value_rcp(double y, double scale, double zp, double, double qmin, double qmax) {
+    return affine_value(y, scale, zp, qmin, qmax);
+}
+
 // float -> fp16 / bf16 -> float, round to nearest even (denormals kept).
 __device__ __forceinline__ float round_to_half(float f, int half_kind) {
     return half_kind == G2D_BF16 ? __bfloat162float(__float2bfloat16_rn(f)) : __half2float(__float2half_rn(f));

@@ -17,6 +17,8 @@
 //     stage loop is fully unrolled and indexes registers statically.  The feedback coefficients
 //     of a sub-tile come from zero-padded copies of the diagonal blocks of L and U^T, so the
 //     pushes need no bounds predicates: out-of-range pushes multiply by zero.
+#include <type_traits>
+
 #include "g2d_common.cuh"
 
 namespace g2d {
@@ -84,6 +86,7 @@ __global__ void __launch_bounds__(TTH) tile_sweep_kernel(SweepArgs<F> P, int S, 
     F *Cs = Ys + TILE * LD;                   // down feedback; the completed C once a sub-tile is swept
     F *LUs = Cs + TILE * LD;                  // strict lower part: L[I, I]; strict upper part: U[J, J]
     F *Dg = LUs + TILE * LD;                  // [2][NSUB] zero-padded diagonal blocks: L[a, a] and U[b, b]^T, strictly lower
+    F *Zs = Dg + 2 * NSUB * DBLK + 2 * DBLK;  // the rounded values, written out in one coalesced pass at the end
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int k = lane & 15, half = lane >> 4;
@@ -172,6 +175,8 @@ __global__ void __launch_bounds__(TTH) tile_sweep_kernel(SweepArgs<F> P, int S, 
         __syncthreads();
 
         F sc[SUB], zp[SUB];  // quantizer parameters of this lane's entries, skewed like acc
+        F rc[SUB];           // float affine only: refined reciprocals of the scales, see affine_value_rcp
+        bool fast_division = false;
         bool have_params = false;
         unsigned valid = 0xFFFFu;  // bit r: the entry held in register r lies inside the matrix
 
@@ -193,6 +198,18 @@ __global__ void __launch_bounds__(TTH) tile_sweep_kernel(SweepArgs<F> P, int S, 
                 }
             }
             valid = bits;
+            if (KIND == G2D_Q_AFFINE && sizeof(F) == sizeof(float)) {
+                bool normal = true;
+#pragma unroll
+                for (int r = 0; r < SUB; ++r) {
+                    const float sv = (float)sc[r], av = fabsf(sv);
+                    normal = normal && av > 1e-18f && av < 1e18f;
+                    float x = __frcp_rn(sv);
+                    x = fmaf(fmaf(-sv, x, 1.f), x, x);  // one Newton step: the reciprocal to within half an ulp
+                    rc[r] = (F)x;
+                }
+                fast_division = __all_sync(0xffffffffu, normal);
+            }
         };
 
         for (int w = 0; w < 2 * NSUB - 1; ++w) {
@@ -209,9 +226,11 @@ __global__ void __launch_bounds__(TTH) tile_sweep_kernel(SweepArgs<F> P, int S, 
                 // lane-constant addresses; stage s adds a compile-time offset
                 F *const cs_ptr = Cs + (r0 + k) * LD + c0 - k;          // row owner: completed C of (k, s - k)
                 F *const ys_ptr = Ys + (r0 - k) * LD + c0 + k;          // column owner: error of (s - k, k)
-                F *const z_ptr = yg + (i0 + r0 + k) * n + j0 + c0 - k;  // row owner: Z of (k, s - k)
                 F *const pre_ptr = pre ? pre + (i0 + r0 + k) * n + j0 + c0 - k : nullptr;
                 const F *const dg = Dg + (half * NSUB + (half ? b : a)) * DBLK;
+                F *const zs_ptr = Zs + (r0 + k) * LD + c0 - k;          // row owner: Z of (k, s - k)
+                auto stages = [&](auto fast_tag) {
+                constexpr bool FASTDIV = decltype(fast_tag)::value;
 #pragma unroll
                 for (int s = 0; s < 2 * SUB - 1; ++s) {
                     const int r = s & (SUB - 1);
@@ -224,15 +243,15 @@ __global__ void __launch_bounds__(TTH) tile_sweep_kernel(SweepArgs<F> P, int S, 
                     const F yv = yacc + cacc;
                     const bool ok = active && ((valid >> r) & 1u);
                     F z;
-                    if (KIND == G2D_Q_AFFINE) z = affine_value(yv, sc[r], zp[r], P.qmin, P.qmax);
+                    if (KIND == G2D_Q_AFFINE) z = FASTDIV ? affine_value_rcp(yv, sc[r], zp[r], rc[r], P.qmin, P.qmax) : affine_value(yv, sc[r], zp[r], P.qmin, P.qmax);
                     else if (KIND == G2D_Q_FORCED) z = sc[r];
                     else z = rint_even(yv);
                     const F ev = ok ? z - yv : (F)0;
                     const F cc = cacc + ev;
                     if (active && half) cs_ptr[s] = cc;
                     if (active && !half) ys_ptr[s * LD] = ev;
+                    if (active && half) zs_ptr[s] = z;
                     if (ok && half) {
-                        z_ptr[s] = z;
                         if (pre_ptr) pre_ptr[s] = yv;
                     }
                     // push: the column owner sends its error down through L, the row owner its completed C right
@@ -245,6 +264,9 @@ __global__ void __launch_bounds__(TTH) tile_sweep_kernel(SweepArgs<F> P, int S, 
                     for (int dd = 1; dd <= kMaxPush; ++dd)
                         if (dd <= dd_hi) acc[(r + dd) & (SUB - 1)] += cp[dd * DLD] * val;
                 }
+                };
+                if (fast_division) stages(std::true_type{});
+                else stages(std::false_type{});
             }
             // fetch the parameters of the next sub-tile of this warp while the updates run
             {
@@ -305,17 +327,19 @@ __global__ void __launch_bounds__(TTH) tile_sweep_kernel(SweepArgs<F> P, int S, 
                 }
             }
         }
-        // ---- store the errors and the completed C of the tile; Z went out entry by entry ----
+        // ---- store the rounded values, the errors and the completed C of the tile ----
         if (vec) {
             constexpr int PER = TILE * TILE / 4 / TTH;
 #pragma unroll
             for (int t = 0; t < PER; ++t) {
                 const int idx = t * TTH + tid, r = idx / (TILE / 4), c = (idx % (TILE / 4)) * 4;
-                F ve[4], vc[4];
+                F ve[4], vc[4], vz[4];
                 load4(Ys + r * LD + c, ve);
                 load4(Cs + r * LD + c, vc);
+                load4(Zs + r * LD + c, vz);
                 store4(eg + (i0 + r) * n + j0 + c, ve);
                 store4(cg + (i0 + r) * n + j0 + c, vc);
+                store4(yg + (i0 + r) * n + j0 + c, vz);
             }
         } else {
             for (int idx = tid; idx < TILE * TILE; idx += TTH) {
@@ -324,6 +348,7 @@ __global__ void __launch_bounds__(TTH) tile_sweep_kernel(SweepArgs<F> P, int S, 
                 if (gi < m && gj < n) {
                     eg[gi * n + gj] = Ys[r * LD + c];
                     cg[gi * n + gj] = Cs[r * LD + c];
+                    yg[gi * n + gj] = Zs[r * LD + c];
                 }
             }
         }
@@ -335,7 +360,7 @@ template <typename F, int KIND>
 static int launch_kind(const SweepArgs<F> &args, int S, int parity, cudaStream_t stream) {
     // the opt-in to more than 48 KB of dynamic shared memory is per device
     static bool configured[64] = {};
-    const size_t smem = sizeof(F) * (3 * TILE * LD + 2 * NSUB * DBLK + 2 * DBLK);
+    const size_t smem = sizeof(F) * (4 * TILE * LD + 2 * NSUB * DBLK + 2 * DBLK);
     int device = 0;
     if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return G2D_ERR_CUDA;
     if (!configured[device]) {

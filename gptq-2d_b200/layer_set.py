@@ -150,6 +150,9 @@ def main() -> None:
         def barrier():
             dist.barrier()
             torch.cuda.synchronize()
+    # one small matrix through every kernel first: the CUDA module loads on first use and would otherwise be charged
+    # to the first (largest) matrix of every rank
+    quantize_matrix({"block": -1, "name": "warm-up", "m": 384, "n": 512, "seed": 1}, device)
     summary = run(layer_list(args.blocks, args.divide), functools.partial(quantize_matrix, device=device), rank=rank, world=world,
                   gather=gather, barrier=barrier)
     if summary is not None:
