@@ -69,17 +69,19 @@ __device__ __forceinline__ void zero_acc(F (&acc)[8][8]) {
 }
 
 // ---- step 1a: factor the diagonal block kb (bs x bs), M_kk = T_kk^T T_kk, and invert T_kk ----
+// One CTA of 16 x 16 threads; thread (ty, tx) owns the entries (ty + 16 a, tx + 16 b).  Step j (last row first)
+// subtracts row j's outer product, scaled by 1 / pivot, from the leading j x j block and emits row j of T; the
+// unscaled row j is never written again, so one barrier per step is enough.
 template <typename F>
 __global__ void __launch_bounds__(256) ldl_diag_kernel(F *a, int64_t n, int kb, F *tinv, int *flag) {
-    __shared__ F S[FB][FB + 1];   // working block, becomes T_kk (lower)
+    __shared__ F S[FB][FB + 1];   // working block (kept symmetric); row j is final, unscaled, after step j
     __shared__ int bad;
-    const int tid = threadIdx.x;
+    const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
     const int64_t o = (int64_t)kb * FB;
     const int bs = (int)min((int64_t)FB, n - o);
     if (tid == 0) bad = 0;
     for (int idx = tid; idx < FB * FB; idx += 256) {
         const int r = idx / FB, c = idx % FB;
-        // the working copy is kept symmetric from the stored lower triangle
         F v = (F)0;
         if (r < bs && c < bs) v = r >= c ? a[(o + r) * n + o + c] : a[(o + c) * n + o + r];
         S[r][c] = v;
@@ -88,31 +90,54 @@ __global__ void __launch_bounds__(256) ldl_diag_kernel(F *a, int64_t n, int kb, 
     __syncthreads();
     for (int j = bs - 1; j >= 0; --j) {
         const F d2 = S[j][j];
-        __syncthreads();
-        if (!(d2 > (F)0)) {
-            if (tid == 0) bad = j + 1;
-        }
-        const F d = sqrt(d2);
-        // row j of T: T[j][i] = M'[j][i] / d for i <= j
-        if (tid <= j) S[j][tid] = tid == j ? d : S[j][tid] / d;
-        __syncthreads();
-        // M'[i1][i2] -= T[j][i1] T[j][i2] for i1, i2 < j
-        for (int idx = tid; idx < j * j; idx += 256) {
-            const int i1 = idx / j, i2 = idx % j;
-            S[i1][i2] -= S[j][i1] * S[j][i2];
+        if (tid == 0 && !(d2 > (F)0)) bad = j + 1;
+        const F inv_d2 = (F)1 / d2;
+#pragma unroll
+        for (int aa = 0; aa < FB / 16; ++aa) {
+            const int i1 = ty + 16 * aa;
+            if (i1 < j) {
+                const F f = S[j][i1] * inv_d2;
+#pragma unroll
+                for (int bb = 0; bb < FB / 16; ++bb) {
+                    const int i2 = tx + 16 * bb;
+                    if (i2 < j) S[i1][i2] -= f * S[j][i2];
+                }
+            }
         }
         __syncthreads();
     }
-    // inverse of the lower triangular T_kk: thread c solves T x = e_c by forward substitution; it keeps its
-    // column in the (zeroed) global block and reads back only what it wrote itself
+    // rows scaled by 1 / sqrt(pivot) are the factor: T[j][i] = S[j][i] / sqrt(S[j][j]), T[j][j] = sqrt(S[j][j])
+    {
+        F vals[FB * FB / 256];
+#pragma unroll
+        for (int t = 0; t < FB * FB / 256; ++t) {
+            const int idx = t * 256 + tid, r = idx / FB, c = idx % FB;
+            const F root = sqrt(S[r][r]);
+            vals[t] = r == c ? root : (c < r ? S[r][c] / root : (F)0);
+        }
+        __syncthreads();
+#pragma unroll
+        for (int t = 0; t < FB * FB / 256; ++t) {
+            const int idx = t * 256 + tid;
+            S[idx / FB][idx % FB] = vals[t];
+        }
+        __syncthreads();
+    }
+    // inverse V of the lower triangular T_kk: thread c solves T x = e_c by forward substitution.  The strict upper
+    // triangle of S is free, so column c of V is kept as row c there: V[r][c] = S[c][r] for r > c.
     if (tid < bs) {
         const int c = tid;
-        F *v = tinv + (int64_t)kb * FB * FB;
-        for (int r = c; r < bs; ++r) {
-            F acc = r == c ? (F)1 : (F)0;
-            for (int k = c; k < r; ++k) acc -= S[r][k] * v[k * FB + c];
-            v[r * FB + c] = acc / S[r][r];
+        const F vcc = (F)1 / S[c][c];
+        for (int r = c + 1; r < bs; ++r) {
+            F acc = -S[r][c] * vcc;
+            for (int k = c + 1; k < r; ++k) acc -= S[r][k] * S[c][k];
+            S[c][r] = acc / S[r][r];
         }
+    }
+    __syncthreads();
+    for (int idx = tid; idx < FB * FB; idx += 256) {
+        const int r = idx / FB, c = idx % FB;
+        if (r < bs && c < bs && r >= c) tinv[(int64_t)kb * FB * FB + idx] = r == c ? (F)1 / S[r][r] : S[c][r];
     }
     for (int idx = tid; idx < FB * FB; idx += 256) {
         const int r = idx / FB, c = idx % FB;
