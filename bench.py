@@ -304,10 +304,12 @@ def main() -> None:
     tensor_peak = pk["bf16_tflops_sustained"] / 6.0  # fp32-faithful tensor roofline: TF32 = bf16 / 2, three TF32 products per fp32 product
     far_tflops = far_flops / (far_ms * 1e-3) / 1e12 if far_ms > 0 else 0.0
     roofline = {
-        "bound": "tensor", "kernel": "band_update_kernel<float, tile mode> (far updates)",
+        "bound": "tensor", "kernel": "macro_update_tc_kernel (tcgen05 kind::tf32, 3xTF32 split; far updates)",
         "achieved": far_tflops, "peak": tensor_peak, "unit": "TFLOP/s", "frac": far_tflops / tensor_peak if tensor_peak else None,
-        "traffic": None,
-        "peak_basis": f"{pk['source']} bf16 sustained {pk['bf16_tflops_sustained']} TFLOP/s / 2 (TF32) / 3 (3xTF32 split); the kernel itself runs on FFMA",
+        # dram bytes read + written of one far-update launch, from the ncu capture of a 4096 x 4096 run (149.7 MB for
+        # 946 target macro tiles, profiles/macro_update_tc_kernel_far_4096.md), scaled by the target tiles of an average launch here
+        "traffic": 149.7e6 / 946 * (far_flops / far_n / (2 * 2 * 128 * 128 * 512)) if far_n else None,
+        "peak_basis": f"{pk['source']} bf16 sustained {pk['bf16_tflops_sustained']} TFLOP/s / 2 (TF32) / 3 (three tf32 products per fp32 product)",
         "launches": int(far_n), "avg_launch_ms": far_ms / far_n if far_n else None,
         "algorithmic_flops_per_launch": far_flops / far_n if far_n else None,
         "kernel_ms": {"tile_sweep": tile_ms, "near_update": near_ms, "far_update": far_ms},
