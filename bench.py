@@ -208,8 +208,7 @@ def main() -> None:
         return G.gptq_2d(weights, l, u, quantizer=quantizer, quantizer_inputs=(scale, zero))
 
     def step(weights, gram_out=g, gram_in=h):
-        l = K.ldl_of_inverse(gram_out, check=False)
-        u = K.ldl_of_inverse(gram_in, check=False).T
+        l, u = K.feedback_factors_from_grams(gram_out, gram_in)
         return sweep_only(weights, l, u)
 
     l, u = K.ldl_of_inverse(g), K.ldl_of_inverse(h).T.contiguous()  # checked once: raises if a factor is not positive definite
@@ -240,7 +239,7 @@ def main() -> None:
     ms_per_step = elapsed_ms / args.steps
     # the sweep alone and the preparation alone, same events, outside the headline region
     parts = {}
-    for name, fn in (("sweep", lambda: sweep_only(w, l, u)), ("prep", lambda: (K.ldl_of_inverse(g, check=False), K.ldl_of_inverse(h, check=False)))):
+    for name, fn in (("sweep", lambda: sweep_only(w, l, u)), ("prep", lambda: K.feedback_factors_from_grams(g, h))):
         fn()
         torch.cuda.synchronize()
         begin.record()
@@ -325,7 +324,7 @@ def main() -> None:
         "data": "synthetic",
         "config": {
             "workload": f"{m}x{n} fp32 layer from W, G, H: ldl_of_inverse x2, INT4 symmetric per-row fp16 abs-max scales, two-sided sweep (one layer per GPU per step)",
-            "step": "kron_factors.ldl_of_inverse(G), ldl_of_inverse(H), int_abs_max_scale, gptq_2d (fused engine) through the public API",
+            "step": "kron_factors.feedback_factors_from_grams(G, H) (two ldl_of_inverse on two streams), int_abs_max_scale, gptq_2d (fused engine) through the public API",
             "l2": "inputs larger than L2: W, G, H are 3 x %.0f MB" % (m * n * 4 / 1e6),
             "sweep_ms": parts["sweep"], "prep_ms": parts["prep"],
             "stages": m + n - 1, "sweep_us_per_stage": parts["sweep"] * 1e3 / (m + n - 1),

@@ -23,9 +23,11 @@
 
 namespace g2d {
 
-constexpr int DLD = SUB + 1;            // row stride of a padded diagonal block
-constexpr int DROWS = 2 * SUB;          // rows of a padded diagonal block (the lower half is zero)
-constexpr int DBLK = DROWS * DLD;       // elements per padded block
+// Push coefficients of a 16 x 16 diagonal block, one row per source p: entry [p][dd] is the coefficient that carries
+// the value of source p to the receiver dd places further (L[p + dd][p] or U[p][p + dd]), zero for dd = 0 and past the
+// block's end.  A lane fetches its row with four 16-byte loads; a row stride of 20 keeps eight lanes on distinct banks.
+constexpr int DLD = SUB + 4;            // row stride
+constexpr int DBLK = SUB * DLD;         // elements per block
 constexpr int TTH = NSUB * 32;          // threads per CTA
 
 template <typename F>
@@ -86,7 +88,7 @@ __global__ void __launch_bounds__(TTH) tile_sweep_kernel(SweepArgs<F> P, int S, 
     F *Cs = Ys + TILE * LD;                   // down feedback; the completed C once a sub-tile is swept
     F *LUs = Cs + TILE * LD;                  // strict lower part: L[I, I]; strict upper part: U[J, J]
     F *Dg = LUs + TILE * LD;                  // [2][NSUB] zero-padded diagonal blocks: L[a, a] and U[b, b]^T, strictly lower
-    F *Zs = Dg + 2 * NSUB * DBLK + 2 * DBLK;  // the rounded values, written out in one coalesced pass at the end
+    F *Zs = Dg + 2 * NSUB * DBLK;             // the rounded values, written out in one coalesced pass at the end
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int k = lane & 15, half = lane >> 4;
@@ -167,27 +169,34 @@ __global__ void __launch_bounds__(TTH) tile_sweep_kernel(SweepArgs<F> P, int S, 
         }
         __syncthreads();
         for (int idx = tid; idx < 2 * NSUB * DBLK; idx += TTH) {
-            const int which = idx / (NSUB * DBLK), blk = idx / DBLK % NSUB, r = idx % DBLK / DLD, c = idx % DLD;
+            const int which = idx / (NSUB * DBLK), blk = idx / DBLK % NSUB, p = idx % DBLK / DLD, dd = idx % DLD;
             F v = (F)0;
-            if (r < SUB && c < r) v = which == 0 ? LUs[(blk * SUB + r) * LD + blk * SUB + c] : LUs[(blk * SUB + c) * LD + blk * SUB + r];
+            if (dd >= 1 && dd < SUB && p + dd < SUB)
+                v = which == 0 ? LUs[(blk * SUB + p + dd) * LD + blk * SUB + p] : LUs[(blk * SUB + p) * LD + blk * SUB + p + dd];
             Dg[idx] = v;
         }
         __syncthreads();
 
-        F sc[SUB], zp[SUB];  // quantizer parameters of this lane's entries, skewed like acc
+        // Sweep of the sub-tiles.  A half-warp (16 lanes) sweeps one sub-tile, so warps 0 and 1 hold the up to four
+        // sub-tiles of a sub-tile anti-diagonal: half-warp h of warp w2 takes sub-tile row a = 2 w2 + h.  Lane k owns
+        // column k (down feedback, "C") and row k (right feedback, "Y") of its sub-tile, both skewed so that the entries of
+        // anti-diagonal s sit in register s mod 16.  At stage s lane k rounds its column's entry (p, k), p = s - k; the
+        // lane that owns row p is lane p, and lane p in turn rounds (k, p), the entry of this lane's row: the two lanes
+        // exchange the row accumulator before rounding and the completed C after it.
+        F sc[SUB], zp[SUB];  // quantizer parameters of this lane's column entries, register r holds entry ((r - k) mod 16, k)
         F rc[SUB];           // float affine only: refined reciprocals of the scales, see affine_value_rcp
         bool fast_division = false;
         bool have_params = false;
         unsigned valid = 0xFFFFu;  // bit r: the entry held in register r lies inside the matrix
+        const int sub_a = 2 * warp + half;  // sub-tile row of this half-warp (warps 0 and 1 only)
 
-        // parameters (and the in-range mask) of sub-tile (warp, b) for this lane
         auto fetch_params = [&](int b) {
-            const int r0 = warp * SUB, c0 = b * SUB;
+            const int r0 = sub_a * SUB, c0 = b * SUB;
             unsigned bits = 0;
 #pragma unroll
             for (int r = 0; r < SUB; ++r) {
                 const int o = (r - k) & (SUB - 1);
-                const int64_t gi = i0 + r0 + (half ? k : o), gj = j0 + c0 + (half ? o : k);
+                const int64_t gi = i0 + r0 + o, gj = j0 + c0 + k;
                 const bool in = full || (gi < m && gj < n);
                 bits |= in ? (1u << r) : 0u;
                 if (KIND == G2D_Q_AFFINE) {
@@ -198,6 +207,10 @@ __global__ void __launch_bounds__(TTH) tile_sweep_kernel(SweepArgs<F> P, int S, 
                 }
             }
             valid = bits;
+        };
+        // second half of the fetch, run when the loads above have had an update phase to land: reciprocals and the
+        // warp-wide decision whether every scale is in the range where the reciprocal form of the division is safe
+        auto finish_params = [&]() {
             if (KIND == G2D_Q_AFFINE && sizeof(F) == sizeof(float)) {
                 bool normal = true;
 #pragma unroll
@@ -213,69 +226,80 @@ __global__ void __launch_bounds__(TTH) tile_sweep_kernel(SweepArgs<F> P, int S, 
         };
 
         for (int w = 0; w < 2 * NSUB - 1; ++w) {
-            const int a = warp, b = w - warp;
-            if (b >= 0 && b < NSUB) {
-                const int r0 = a * SUB, c0 = b * SUB;
+            if (warp < 2) {
+                const int b_raw = w - sub_a;
+                const bool tile_ok = b_raw >= 0 && b_raw < NSUB;  // a half-warp without a sub-tile runs along with everything masked
+                const int b = tile_ok ? b_raw : 0;
+                const int r0 = sub_a * SUB, c0 = b * SUB;
                 if (!have_params) fetch_params(b);
-                F acc[SUB];
+                finish_params();
+                F cacc[SUB], yacc[SUB];
 #pragma unroll
                 for (int r = 0; r < SUB; ++r) {
                     const int o = (r - k) & (SUB - 1);
-                    acc[r] = half ? Ys[(r0 + k) * LD + c0 + o] : Cs[(r0 + o) * LD + c0 + k];
+                    cacc[r] = Cs[(r0 + o) * LD + c0 + k];
+                    yacc[r] = Ys[(r0 + k) * LD + c0 + o];
                 }
-                // lane-constant addresses; stage s adds a compile-time offset
-                F *const cs_ptr = Cs + (r0 + k) * LD + c0 - k;          // row owner: completed C of (k, s - k)
-                F *const ys_ptr = Ys + (r0 - k) * LD + c0 + k;          // column owner: error of (s - k, k)
-                F *const pre_ptr = pre ? pre + (i0 + r0 + k) * n + j0 + c0 - k : nullptr;
-                const F *const dg = Dg + (half * NSUB + (half ? b : a)) * DBLK;
-                F *const zs_ptr = Zs + (r0 + k) * LD + c0 - k;          // row owner: Z of (k, s - k)
+                // entry (s - k, k) of the sub-tile: a lane-constant address plus s rows
+                const int entry0 = (r0 - k) * LD + c0 + k;
+                F *pre_ptr = pre ? pre + (i0 + r0 - k) * n + j0 + c0 + k : nullptr;
+                const F *const dgl = Dg + sub_a * DBLK, *const dgu = Dg + (NSUB + b) * DBLK;
                 auto stages = [&](auto fast_tag) {
-                constexpr bool FASTDIV = decltype(fast_tag)::value;
+                    constexpr bool FASTDIV = decltype(fast_tag)::value;
+#pragma unroll 1
+                    for (int pass = 0; pass < 2; ++pass) {
+                        const int s0 = pass * SUB;
+                        F *const e_ptr = Ys + entry0 + s0 * LD, *const c_ptr = Cs + entry0 + s0 * LD, *const z_ptr = Zs + entry0 + s0 * LD;
 #pragma unroll
-                for (int s = 0; s < 2 * SUB - 1; ++s) {
-                    const int r = s & (SUB - 1);
-                    const int src = s - k;
-                    const bool active = src >= 0 && src < SUB;
-                    const int srcw = src & (SUB - 1);
-                    // column owner j = k needs the Y accumulator of row src; row owner i = k the C accumulator of column src
-                    const F other = __shfl_sync(0xffffffffu, acc[r], half ? srcw : SUB + srcw);
-                    const F yacc = half ? acc[r] : other, cacc = half ? other : acc[r];
-                    const F yv = yacc + cacc;
-                    const bool ok = active && ((valid >> r) & 1u);
-                    F z;
-                    if (KIND == G2D_Q_AFFINE) z = FASTDIV ? affine_value_rcp(yv, sc[r], zp[r], rc[r], P.qmin, P.qmax) : affine_value(yv, sc[r], zp[r], P.qmin, P.qmax);
-                    else if (KIND == G2D_Q_FORCED) z = sc[r];
-                    else z = rint_even(yv);
-                    const F ev = ok ? z - yv : (F)0;
-                    const F cc = cacc + ev;
-                    if (active && half) cs_ptr[s] = cc;
-                    if (active && !half) ys_ptr[s * LD] = ev;
-                    if (active && half) zs_ptr[s] = z;
-                    if (ok && half) {
-                        if (pre_ptr) pre_ptr[s] = yv;
+                        for (int r = 0; r < SUB; ++r) {
+                            const int p = s0 + r - k;  // row of this lane's column entry = column of its row entry = partner lane
+                            const bool active = tile_ok && p >= 0 && p < SUB;
+                            const int pw = p & (SUB - 1);
+                            const F yrow = __shfl_sync(0xffffffffu, yacc[r], pw, SUB);  // Y accumulator of (p, k) from the owner of row p
+                            const F yv = yrow + cacc[r];
+                            const bool ok = active && ((valid >> r) & 1u);
+                            F z;
+                            if (KIND == G2D_Q_AFFINE) z = FASTDIV ? affine_value_rcp(yv, sc[r], zp[r], rc[r], P.qmin, P.qmax) : affine_value(yv, sc[r], zp[r], P.qmin, P.qmax);
+                            else if (KIND == G2D_Q_FORCED) z = sc[r];
+                            else z = rint_even(yv);
+                            const F ev = ok ? z - yv : (F)0;
+                            const F cc = cacc[r] + ev;
+                            const F ccrow = __shfl_sync(0xffffffffu, cc, pw, SUB);  // completed C of (k, p), rounded by lane p
+                            if (active) {
+                                e_ptr[r * LD] = ev;
+                                c_ptr[r * LD] = cc;
+                                z_ptr[r * LD] = z;
+                            }
+                            if (ok && pre_ptr) pre_ptr[(int64_t)(s0 + r) * n] = yv;
+                            // pushes: the error down column k through L, the completed C of (k, p) right along row k through U;
+                            // rows past the block's end read the zero padding, inactive lanes push zero
+                            const F vcol = active ? ev : (F)0, vrow = active ? ccrow : (F)0;
+                            F kl[SUB], ku[SUB];
+#pragma unroll
+                            for (int v4 = 0; v4 < SUB; v4 += 4) {
+                                F t[4];
+                                load4(dgl + pw * DLD + v4, t);
+#pragma unroll
+                                for (int x = 0; x < 4; ++x) kl[v4 + x] = t[x];
+                                load4(dgu + pw * DLD + v4, t);
+#pragma unroll
+                                for (int x = 0; x < 4; ++x) ku[v4 + x] = t[x];
+                            }
+#pragma unroll
+                            for (int dd = 1; dd < SUB; ++dd) {
+                                cacc[(r + dd) & (SUB - 1)] += kl[dd] * vcol;
+                                yacc[(r + dd) & (SUB - 1)] += ku[dd] * vrow;
+                            }
+                        }
                     }
-                    // push: the column owner sends its error down through L, the row owner its completed C right
-                    // through U; rows past the block's end and inactive lanes multiply by zero
-                    const F val = active ? (half ? cc : ev) : (F)0;
-                    const F *cp = dg + srcw * (DLD + 1);
-                    constexpr int kMaxPush = SUB - 1;
-                    const int dd_hi = s < SUB ? kMaxPush : 2 * SUB - 2 - s;  // static bound: src >= s - (SUB - 1)
-#pragma unroll
-                    for (int dd = 1; dd <= kMaxPush; ++dd)
-                        if (dd <= dd_hi) acc[(r + dd) & (SUB - 1)] += cp[dd * DLD] * val;
-                }
                 };
                 if (fast_division) stages(std::true_type{});
                 else stages(std::false_type{});
-            }
-            // fetch the parameters of the next sub-tile of this warp while the updates run
-            {
-                const int bn = w + 1 - warp;
-                have_params = false;
-                if (bn >= 0 && bn < NSUB) {
-                    fetch_params(bn);
-                    have_params = true;
-                }
+                // fetch the parameters of this half-warp's next sub-tile while the updates run.  Both half-warps make the
+                // call (it ends in a warp-wide vote); one without a next sub-tile fetches a valid dummy and stays masked
+                const int bn = w + 1 - sub_a;
+                fetch_params(bn >= 0 && bn < NSUB ? bn : 0);
+                have_params = true;
             }
             __syncthreads();
             // ---- apply the finished sub-tiles to the rest of the tile ----
@@ -360,7 +384,7 @@ template <typename F, int KIND>
 static int launch_kind(const SweepArgs<F> &args, int S, int parity, cudaStream_t stream) {
     // the opt-in to more than 48 KB of dynamic shared memory is per device
     static bool configured[64] = {};
-    const size_t smem = sizeof(F) * (4 * TILE * LD + 2 * NSUB * DBLK + 2 * DBLK);
+    const size_t smem = sizeof(F) * (4 * TILE * LD + 2 * NSUB * DBLK);
     int device = 0;
     if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return G2D_ERR_CUDA;
     if (!configured[device]) {

@@ -78,3 +78,30 @@ def gptq_d_sided(x: torch.Tensor, factors, *, quantizer=None, quantizer_inputs=(
     z = engine.gptq_2d(x.reshape(rows, x.size(-1)), row_factor.contiguous(), factors[-1].t().contiguous(),
                        quantizer_inputs=quantizer_inputs, **options)
     return z.reshape(x.shape)
+
+
+_SIDE_STREAMS: dict = {}
+
+
+@torch.no_grad()
+def feedback_factors_from_grams(g: torch.Tensor, h: torch.Tensor, super_entry_shape: tuple[int, int] = (1, 1),
+                                check: bool = False) -> tuple[torch.Tensor, torch.Tensor]:
+    """L from the output-side Gram ``g [m, m]`` and U from the input-side Gram ``h [n, n]`` (``U = ldl_of_inverse(h).T``),
+    prepared concurrently: both factorizations are chains of small dependent launches, so the second one runs on a side
+    stream that forks from and joins the current stream (capturable in a CUDA graph)."""
+    p, q = super_entry_shape
+    current = torch.cuda.current_stream(g.device)
+    side = _SIDE_STREAMS.get(g.device)
+    if side is None:
+        side = _SIDE_STREAMS[g.device] = torch.cuda.Stream(device=g.device)
+    side.wait_stream(current)
+    with torch.cuda.stream(side):
+        lower_of_h = ldl_of_inverse(h, size=q, check=False)
+    l = ldl_of_inverse(g, size=p, check=False)
+    current.wait_stream(side)
+    lower_of_h.record_stream(current)
+    if check:
+        for name, factor in (("G", l), ("H", lower_of_h)):
+            if not bool(torch.isfinite(factor).all()):
+                raise torch.linalg.LinAlgError(f"feedback_factors_from_grams: the factor of {name} is not finite (is the matrix positive definite?)")
+    return l, lower_of_h.t()

@@ -66,8 +66,7 @@ def quantize_matrix(item: dict, device) -> dict:
     w, g, h = synthetic.make_layer(m, n, seed=item["seed"], device=device, samples=min(8192, max(m, n)))
     events = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
     events[0].record()
-    l = K.ldl_of_inverse(g, check=False)
-    u = K.ldl_of_inverse(h, check=False).T
+    l, u = K.feedback_factors_from_grams(g, h)
     events[1].record()
     scale = Q.int_abs_max_scale_triton(w, qmin=-8, qmax=7, dtype=torch.float16).expand(m, n)
     zero = torch.zeros(1, 1, device=device, dtype=w.dtype).expand(m, n)
