@@ -10,6 +10,8 @@
 //   3. out = Lf D^{-1} with D the size x size diagonal blocks of Lf: identity diagonal blocks, zeros above.
 //
 // M is overwritten (its lower triangle becomes T).  A non-positive pivot stores its 1-based index in *flag.
+#include <mutex>
+
 #include "g2d_common.cuh"
 
 namespace g2d {
@@ -172,11 +174,11 @@ __global__ void __launch_bounds__(FTH) ldl_trsm_kernel(F *a, int64_t n, int kb, 
 
 // ---- step 1c: M'[TI, TJ] -= T[kb, TI]^T T[kb, TJ] for TJ <= TI < kb (lower triangle of tiles) ----
 template <typename F>
-__global__ void __launch_bounds__(FTH) ldl_syrk_kernel(F *a, int64_t n, int kb) {
+__global__ void __launch_bounds__(FTH) ldl_syrk_kernel(F *a, int64_t n, int kb, int64_t first) {
     __shared__ __align__(16) F As[FK * FLD];
     __shared__ __align__(16) F Bs[FK * FLD];
     // linear index -> (TI, TJ) with TJ <= TI
-    const int64_t lin = blockIdx.x;
+    const int64_t lin = first + blockIdx.x;
     int TI = (int)((sqrt(8.0 * (double)lin + 1.0) - 1.0) / 2.0);
     while ((int64_t)(TI + 1) * (TI + 2) / 2 <= lin) ++TI;
     while ((int64_t)TI * (TI + 1) / 2 > lin) --TI;
@@ -298,6 +300,30 @@ __global__ void ldl_scale_kernel(F *out, int64_t n, int size, const F *dblk) {
     }
 }
 
+// Side streams for the look-ahead of the trailing updates.  Calls take lanes round robin, so two factorizations that
+// a caller runs concurrently on two streams do not share one.  Created on first use per device and kept.
+struct SideLane {
+    cudaStream_t stream = nullptr;
+    cudaEvent_t panel[4] = {}, rest[4] = {};
+};
+static SideLane *acquire_side_lane() {
+    static std::mutex mutex;
+    static SideLane lanes[64][4];
+    static unsigned next[64] = {};
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return nullptr;
+    std::lock_guard<std::mutex> lock(mutex);
+    SideLane *lane = &lanes[device][next[device]++ & 3];
+    if (!lane->stream) {
+        if (cudaStreamCreateWithFlags(&lane->stream, cudaStreamNonBlocking) != cudaSuccess) return nullptr;
+        for (int k = 0; k < 4; ++k)
+            if (cudaEventCreateWithFlags(&lane->panel[k], cudaEventDisableTiming) != cudaSuccess ||
+                cudaEventCreateWithFlags(&lane->rest[k], cudaEventDisableTiming) != cudaSuccess)
+                return nullptr;
+    }
+    return lane;
+}
+
 template <typename F>
 int ldl_run(int64_t n, F *a, int size, F *out, int *flag, void *workspace, cudaStream_t st) {
     const int nb = (int)ceil_div(n, FB);
@@ -305,17 +331,42 @@ int ldl_run(int64_t n, F *a, int size, F *out, int *flag, void *workspace, cudaS
     F *dblk = tinv + (int64_t)nb * FB * FB;                     // [n / size][size][size]
     if (flag && cudaMemsetAsync(flag, 0, sizeof(int), st) != cudaSuccess) return G2D_ERR_CUDA;
     if (cudaMemsetAsync(out, 0, sizeof(F) * (size_t)n * n, st) != cudaSuccess) return G2D_ERR_CUDA;
+    // Look-ahead: step kb's trailing update is split into the block row that the next step factors (kept on the
+    // caller's stream) and the rest (a side stream), so that the latency-bound diagonal and panel kernels of step kb - 1
+    // overlap the bulk of step kb's update.  rest(kb) touches block rows <= kb - 2: the next diagonal block needs
+    // rest(kb + 2) and older, the next row update must follow rest(kb + 1).
+    SideLane *lane = acquire_side_lane();
+    if (!lane) return G2D_ERR_CUDA;
+    bool rest_recorded[4] = {false, false, false, false};
+    auto wait_rest = [&](int step) {
+        if (step <= nb - 1 && rest_recorded[step & 3]) return cudaStreamWaitEvent(st, lane->rest[step & 3], 0) == cudaSuccess;
+        return true;
+    };
     for (int kb = nb - 1; kb >= 0; --kb) {
+        if (!wait_rest(kb + 2)) return G2D_ERR_CUDA;
         ldl_diag_kernel<F><<<1, 256, 0, st>>>(a, n, kb, tinv, flag);
         if (check_launch() != G2D_OK) return G2D_ERR_CUDA;
         if (kb > 0) {
             ldl_trsm_kernel<F><<<kb, FTH, 0, st>>>(a, n, kb, tinv);
             if (check_launch() != G2D_OK) return G2D_ERR_CUDA;
-            const int64_t pairs = (int64_t)kb * (kb + 1) / 2;
-            ldl_syrk_kernel<F><<<(unsigned)pairs, FTH, 0, st>>>(a, n, kb);
+            const int64_t rest = (int64_t)(kb - 1) * kb / 2;  // tile pairs of the block rows above kb - 1
+            rest_recorded[kb & 3] = false;
+            if (rest > 0) {  // the panel is final: the side stream may start on the block rows <= kb - 2
+                if (cudaEventRecord(lane->panel[kb & 3], st) != cudaSuccess || cudaStreamWaitEvent(lane->stream, lane->panel[kb & 3], 0) != cudaSuccess)
+                    return G2D_ERR_CUDA;
+                ldl_syrk_kernel<F><<<(unsigned)rest, FTH, 0, lane->stream>>>(a, n, kb, 0);
+                if (check_launch() != G2D_OK) return G2D_ERR_CUDA;
+                if (cudaEventRecord(lane->rest[kb & 3], lane->stream) != cudaSuccess) return G2D_ERR_CUDA;
+            }
+            if (!wait_rest(kb + 1)) return G2D_ERR_CUDA;
+            ldl_syrk_kernel<F><<<(unsigned)kb, FTH, 0, st>>>(a, n, kb, rest);  // block row kb - 1, which the next step factors
             if (check_launch() != G2D_OK) return G2D_ERR_CUDA;
+            rest_recorded[kb & 3] = rest > 0;
         }
     }
+    // everything the side stream did joins the caller's stream before the inverse starts
+    for (int k = 0; k < 4; ++k)
+        if (rest_recorded[k] && cudaStreamWaitEvent(st, lane->rest[k], 0) != cudaSuccess) return G2D_ERR_CUDA;
     ldl_copy_diag_inverse_kernel<F><<<nb, FTH, 0, st>>>(tinv, n, out);
     if (check_launch() != G2D_OK) return G2D_ERR_CUDA;
     F *w = dblk + n * (int64_t)FB;  // [n][n] scratch of the doubling steps
