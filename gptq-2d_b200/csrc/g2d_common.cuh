@@ -107,6 +107,18 @@ struct TcPlanes {
 int tc_prepare_operands(const float *l, const float *u, int64_t m, int64_t n, const TcPlanes &planes, cudaStream_t stream);
 int launch_macro_update_tc(const TcPlanes &planes, float *y, float *c, int64_t m, int64_t n, int s0, int s1, int s_end, cudaStream_t stream);
 
+// One problem of the tensor-core triangular inverse of the factor preparation (all [n][n] float; see g2d_factors_tc.cu).
+struct FactorPlanes {
+    const float *a;            // Cholesky factor T in its lower triangle
+    float *out;                // the inverse being built
+    float *out_hi, *out_lo;    // its tf32 split, and the split of its transpose
+    float *outt_hi, *outt_lo;
+    float *tw_hi, *tw_lo;      // lower triangle: split of T; upper triangle: split of the transposed intermediate product
+    int64_t n;
+    int *flag;                 // receives -1 when a bounded wait inside a kernel ran out (may be null)
+};
+int launch_trinv_tc(int count, const FactorPlanes *problems, cudaStream_t stream);
+
 template <typename F>
 int launch_tile_sweep(const SweepArgs<F> &args, int S, cudaStream_t stream, int parity = 0);
 

@@ -12,6 +12,8 @@
 // M is overwritten (its lower triangle becomes T).  A non-positive pivot stores its 1-based index in *flag.
 #include <mutex>
 
+#include <type_traits>
+
 #include "g2d_common.cuh"
 
 namespace g2d {
@@ -62,6 +64,28 @@ __device__ __forceinline__ void tile_product(F (&acc)[8][8], int64_t K, LA la, L
     __syncthreads();
 }
 
+// Up to two factorizations advance together, block step by block step, in the same launches (the steps are chains of
+// short dependent kernels, so a second matrix rides along almost for free).  Problem z of a launch is blockIdx.y, or
+// folded into blockIdx.x where the grid is three-dimensional already; a problem with fewer block rows starts later.
+template <typename F>
+struct LdlProblem {
+    F *a, *out, *tinv, *w;
+    int64_t n;
+    int *flag;
+};
+template <typename F>
+struct LdlBatch {
+    LdlProblem<F> p[2];
+    int count;
+    int steps;  // block rows of the largest problem
+};
+#define LDL_PROBLEM(z)                                        \
+    const LdlProblem<F> Q = (z) ? B.p[1] : B.p[0];            \
+    F *const a = Q.a;                                         \
+    const int64_t n = Q.n;                                    \
+    const int kb = (int)ceil_div(n, FB) - 1 - (B.steps - 1 - step_down); \
+    if (kb < 0) return;
+
 template <typename F>
 __device__ __forceinline__ void zero_acc(F (&acc)[8][8]) {
 #pragma unroll
@@ -75,7 +99,10 @@ __device__ __forceinline__ void zero_acc(F (&acc)[8][8]) {
 // subtracts row j's outer product, scaled by 1 / pivot, from the leading j x j block and emits row j of T; the
 // unscaled row j is never written again, so one barrier per step is enough.
 template <typename F>
-__global__ void __launch_bounds__(256) ldl_diag_kernel(F *a, int64_t n, int kb, F *tinv, int *flag) {
+__global__ void __launch_bounds__(256) ldl_diag_kernel(LdlBatch<F> B, int step_down) {
+    LDL_PROBLEM(blockIdx.y)
+    F *const tinv = Q.tinv;
+    int *const flag = Q.flag;
     __shared__ F S[FB][FB + 1];   // working block (kept symmetric); row j is final, unscaled, after step j
     __shared__ int bad;
     const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
@@ -150,7 +177,10 @@ __global__ void __launch_bounds__(256) ldl_diag_kernel(F *a, int64_t n, int kb, 
 
 // ---- step 1b: block row to the left of the diagonal block: T[kb, j] = T_kk^{-T} M'[kb, j] ----
 template <typename F>
-__global__ void __launch_bounds__(FTH) ldl_trsm_kernel(F *a, int64_t n, int kb, const F *tinv) {
+__global__ void __launch_bounds__(FTH) ldl_trsm_kernel(LdlBatch<F> B, int step_down) {
+    LDL_PROBLEM(blockIdx.y)
+    const F *const tinv = Q.tinv;
+    if ((int)blockIdx.x >= kb) return;
     __shared__ __align__(16) F As[FK * FLD];
     __shared__ __align__(16) F Bs[FK * FLD];
     const int j = blockIdx.x;  // column tile, j < kb
@@ -174,7 +204,12 @@ __global__ void __launch_bounds__(FTH) ldl_trsm_kernel(F *a, int64_t n, int kb, 
 
 // ---- step 1c: M'[TI, TJ] -= T[kb, TI]^T T[kb, TJ] for TJ <= TI < kb (lower triangle of tiles) ----
 template <typename F>
-__global__ void __launch_bounds__(FTH) ldl_syrk_kernel(F *a, int64_t n, int kb, int64_t first) {
+__global__ void __launch_bounds__(FTH) ldl_syrk_kernel(LdlBatch<F> B, int step_down, bool row) {
+    LDL_PROBLEM(blockIdx.y)
+    // tile pairs (TI, TJ), TJ <= TI < kb, in row order: the last block row (TI = kb - 1) or everything above it
+    const int64_t above = (int64_t)(kb - 1) * kb / 2;
+    if (row ? (int64_t)blockIdx.x >= kb : (int64_t)blockIdx.x >= above) return;
+    const int64_t first = row ? above : 0;
     __shared__ __align__(16) F As[FK * FLD];
     __shared__ __align__(16) F Bs[FK * FLD];
     // linear index -> (TI, TJ) with TJ <= TI
@@ -207,8 +242,13 @@ __global__ void __launch_bounds__(FTH) ldl_syrk_kernel(F *a, int64_t n, int kb, 
 // as two batched tile products over all pairs: W = C A^{-1} into scratch, then X = -B^{-1} W into Lf.  Both inverses
 // are lower triangular, which bounds the k range of every output tile. ----
 template <typename F>
-__global__ void __launch_bounds__(FTH) ldl_copy_diag_inverse_kernel(const F *tinv, int64_t n, F *out) {
+__global__ void __launch_bounds__(FTH) ldl_copy_diag_inverse_kernel(LdlBatch<F> B) {
+    const LdlProblem<F> Q = blockIdx.y ? B.p[1] : B.p[0];
+    const F *const tinv = Q.tinv;
+    F *const out = Q.out;
+    const int64_t n = Q.n;
     const int i = blockIdx.x;
+    if ((int64_t)i * FB >= n) return;
     const int64_t r0 = (int64_t)i * FB;
     const int bs = (int)min((int64_t)FB, n - r0);
     for (int idx = threadIdx.x; idx < FB * FB; idx += FTH) {
@@ -219,10 +259,14 @@ __global__ void __launch_bounds__(FTH) ldl_copy_diag_inverse_kernel(const F *tin
 
 // second == false: W[pair block] = C A^{-1};  second == true: Lf[pair block] = -B^{-1} W
 template <typename F>
-__global__ void __launch_bounds__(FTH) ldl_trinv_level_kernel(const F *a, int64_t n, int64_t b, F *w, F *out, bool second) {
+__global__ void __launch_bounds__(FTH) ldl_trinv_level_kernel(LdlBatch<F> B, int64_t b, int pairs, bool second) {
+    const LdlProblem<F> Q = (int)blockIdx.x >= pairs ? B.p[1] : B.p[0];
+    const F *const a = Q.a;
+    F *const w = Q.w, *const out = Q.out;
+    const int64_t n = Q.n;
     __shared__ __align__(16) F As[FK * FLD];
     __shared__ __align__(16) F Bs[FK * FLD];
-    const int64_t r0 = (int64_t)blockIdx.x * 2 * b, r1 = r0 + b;  // first half rows [r0, r1), second half rows [r1, r2)
+    const int64_t r0 = (int64_t)(blockIdx.x % pairs) * 2 * b, r1 = r0 + b;  // first half rows [r0, r1), second half rows [r1, r2)
     if (r1 >= n) return;
     const int64_t r2 = min(r0 + 2 * b, n);
     const int64_t ti = blockIdx.y, tj = blockIdx.z;  // output tile inside the b x b off-diagonal block
@@ -325,41 +369,54 @@ static SideLane *acquire_side_lane() {
 }
 
 template <typename F>
-int ldl_run(int64_t n, F *a, int size, F *out, int *flag, void *workspace, cudaStream_t st) {
-    const int nb = (int)ceil_div(n, FB);
-    F *tinv = (F *)workspace;                                   // [nb][64][64]
-    F *dblk = tinv + (int64_t)nb * FB * FB;                     // [n / size][size][size]
-    if (flag && cudaMemsetAsync(flag, 0, sizeof(int), st) != cudaSuccess) return G2D_ERR_CUDA;
-    if (cudaMemsetAsync(out, 0, sizeof(F) * (size_t)n * n, st) != cudaSuccess) return G2D_ERR_CUDA;
-    // Look-ahead: step kb's trailing update is split into the block row that the next step factors (kept on the
-    // caller's stream) and the rest (a side stream), so that the latency-bound diagonal and panel kernels of step kb - 1
-    // overlap the bulk of step kb's update.  rest(kb) touches block rows <= kb - 2: the next diagonal block needs
-    // rest(kb + 2) and older, the next row update must follow rest(kb + 1).
+int ldl_run(int count, const int64_t *ns, F *const *as, const int *sizes, F *const *outs, int *flags, void *const *workspaces, cudaStream_t st) {
+    LdlBatch<F> B;
+    B.count = count;
+    B.steps = 0;
+    F *dblks[2] = {nullptr, nullptr};
+    int64_t n_max = 0;
+    for (int z = 0; z < count; ++z) {
+        const int64_t n = ns[z];
+        const int nb = (int)ceil_div(n, FB);
+        F *tinv = (F *)workspaces[z];                             // [nb][64][64]
+        dblks[z] = tinv + (int64_t)nb * FB * FB;                  // [n / size][size][size]
+        B.p[z] = LdlProblem<F>{as[z], outs[z], tinv, dblks[z] + n * (int64_t)FB /* [n][n] scratch of the doubling steps */, n,
+                               flags ? flags + z : nullptr};
+        B.steps = nb > B.steps ? nb : B.steps;
+        n_max = n > n_max ? n : n_max;
+        if (cudaMemsetAsync(outs[z], 0, sizeof(F) * (size_t)n * n, st) != cudaSuccess) return G2D_ERR_CUDA;
+    }
+    if (count == 1) B.p[1] = B.p[0];
+    if (flags && cudaMemsetAsync(flags, 0, sizeof(int) * count, st) != cudaSuccess) return G2D_ERR_CUDA;
+    // Look-ahead: a step's trailing update is split into the block row that the next step factors (kept on the
+    // caller's stream) and the rest (a side stream), so that the latency-bound diagonal and panel kernels of the next
+    // step overlap the bulk of this step's update.  With kb the block row of a step, rest(kb) touches block rows
+    // <= kb - 2: the next diagonal block needs rest(kb + 2) and older, the next row update must follow rest(kb + 1).
     SideLane *lane = acquire_side_lane();
     if (!lane) return G2D_ERR_CUDA;
     bool rest_recorded[4] = {false, false, false, false};
     auto wait_rest = [&](int step) {
-        if (step <= nb - 1 && rest_recorded[step & 3]) return cudaStreamWaitEvent(st, lane->rest[step & 3], 0) == cudaSuccess;
+        if (step <= B.steps - 1 && rest_recorded[step & 3]) return cudaStreamWaitEvent(st, lane->rest[step & 3], 0) == cudaSuccess;
         return true;
     };
-    for (int kb = nb - 1; kb >= 0; --kb) {
+    for (int kb = B.steps - 1; kb >= 0; --kb) {  // block row of the largest problem; smaller problems join when it reaches theirs
         if (!wait_rest(kb + 2)) return G2D_ERR_CUDA;
-        ldl_diag_kernel<F><<<1, 256, 0, st>>>(a, n, kb, tinv, flag);
+        ldl_diag_kernel<F><<<dim3(1, count), 256, 0, st>>>(B, kb);
         if (check_launch() != G2D_OK) return G2D_ERR_CUDA;
         if (kb > 0) {
-            ldl_trsm_kernel<F><<<kb, FTH, 0, st>>>(a, n, kb, tinv);
+            ldl_trsm_kernel<F><<<dim3(kb, count), FTH, 0, st>>>(B, kb);
             if (check_launch() != G2D_OK) return G2D_ERR_CUDA;
             const int64_t rest = (int64_t)(kb - 1) * kb / 2;  // tile pairs of the block rows above kb - 1
             rest_recorded[kb & 3] = false;
             if (rest > 0) {  // the panel is final: the side stream may start on the block rows <= kb - 2
                 if (cudaEventRecord(lane->panel[kb & 3], st) != cudaSuccess || cudaStreamWaitEvent(lane->stream, lane->panel[kb & 3], 0) != cudaSuccess)
                     return G2D_ERR_CUDA;
-                ldl_syrk_kernel<F><<<(unsigned)rest, FTH, 0, lane->stream>>>(a, n, kb, 0);
+                ldl_syrk_kernel<F><<<dim3((unsigned)rest, count), FTH, 0, lane->stream>>>(B, kb, false);
                 if (check_launch() != G2D_OK) return G2D_ERR_CUDA;
                 if (cudaEventRecord(lane->rest[kb & 3], lane->stream) != cudaSuccess) return G2D_ERR_CUDA;
             }
             if (!wait_rest(kb + 1)) return G2D_ERR_CUDA;
-            ldl_syrk_kernel<F><<<(unsigned)kb, FTH, 0, st>>>(a, n, kb, rest);  // block row kb - 1, which the next step factors
+            ldl_syrk_kernel<F><<<dim3(kb, count), FTH, 0, st>>>(B, kb, true);  // block row kb - 1, which the next step factors
             if (check_launch() != G2D_OK) return G2D_ERR_CUDA;
             rest_recorded[kb & 3] = rest > 0;
         }
@@ -367,27 +424,63 @@ int ldl_run(int64_t n, F *a, int size, F *out, int *flag, void *workspace, cudaS
     // everything the side stream did joins the caller's stream before the inverse starts
     for (int k = 0; k < 4; ++k)
         if (rest_recorded[k] && cudaStreamWaitEvent(st, lane->rest[k], 0) != cudaSuccess) return G2D_ERR_CUDA;
-    ldl_copy_diag_inverse_kernel<F><<<nb, FTH, 0, st>>>(tinv, n, out);
+    ldl_copy_diag_inverse_kernel<F><<<dim3(B.steps, count), FTH, 0, st>>>(B);
     if (check_launch() != G2D_OK) return G2D_ERR_CUDA;
-    F *w = dblk + n * (int64_t)FB;  // [n][n] scratch of the doubling steps
-    for (int64_t b = FB; b < n; b *= 2) {
-        const int64_t pairs = ceil_div(n, 2 * b), tiles = b / FB;
-        if (tiles > 65535) return G2D_ERR_TOO_LARGE;
-        dim3 grid((unsigned)pairs, (unsigned)tiles, (unsigned)tiles);
-        ldl_trinv_level_kernel<F><<<grid, FTH, 0, st>>>(a, n, b, w, out, false);
+    // The 64-level for everyone; from the 128-level on, float problems whose rows are 16-byte multiples continue on the
+    // tensor cores and the others here.  The choice depends on the problem alone, never on its partner in the batch.
+    auto ffma_levels = [&](const LdlBatch<F> &batch, int problems, int64_t n_top, int64_t b_first, int64_t b_end) {
+        for (int64_t b = b_first; b < n_top && b < b_end; b *= 2) {
+            const int64_t pairs = ceil_div(n_top, 2 * b), tiles = b / FB;
+            if (tiles > 65535) return (int)G2D_ERR_TOO_LARGE;
+            dim3 grid((unsigned)(pairs * problems), (unsigned)tiles, (unsigned)tiles);
+            ldl_trinv_level_kernel<F><<<grid, FTH, 0, st>>>(batch, b, (int)pairs, false);
+            if (check_launch() != G2D_OK) return (int)G2D_ERR_CUDA;
+            ldl_trinv_level_kernel<F><<<grid, FTH, 0, st>>>(batch, b, (int)pairs, true);
+            if (check_launch() != G2D_OK) return (int)G2D_ERR_CUDA;
+        }
+        return (int)G2D_OK;
+    };
+    int status = ffma_levels(B, count, n_max, FB, 2 * FB);
+    if (status != G2D_OK) return status;
+    FactorPlanes planes[2];
+    int tensor_count = 0;
+    LdlBatch<F> rest = B;
+    int rest_count = 0;
+    int64_t rest_max = 0;
+    for (int z = 0; z < count; ++z) {
+        const int64_t n = ns[z];
+        if (std::is_same<F, float>::value && n % 4 == 0) {
+            float *base = (float *)B.p[z].w + n * n;  // six [n][n] planes behind the scratch of the 64-level
+            planes[tensor_count++] = FactorPlanes{(const float *)as[z], (float *)outs[z], base, base + n * n, base + 2 * n * n,
+                                                  base + 3 * n * n, base + 4 * n * n, base + 5 * n * n, n, flags ? flags + z : nullptr};
+        } else {
+            rest.p[rest_count++] = B.p[z];
+            rest_max = n > rest_max ? n : rest_max;
+        }
+    }
+    if (rest_count == 1) rest.p[1] = rest.p[0];
+    if (rest_count > 0) {
+        status = ffma_levels(rest, rest_count, rest_max, 2 * FB, INT64_MAX);
+        if (status != G2D_OK) return status;
+    }
+    if (tensor_count > 0) {
+        status = launch_trinv_tc(tensor_count, planes, st);
+        if (status != G2D_OK) return status;
+    }
+    for (int z = 0; z < count; ++z) {
+        const int64_t n = ns[z];
+        const int size = sizes[z];
+        const int64_t work = n * (n / size);
+        int64_t blocks = ceil_div(work, 256);
+        if (blocks > 148 * 64) blocks = 148 * 64;
+        ldl_copy_diag_kernel<F><<<(unsigned)(ceil_div(n * size, 256) < 148 * 64 ? ceil_div(n * size, 256) : 148 * 64), 256, 0, st>>>(outs[z], n, size, dblks[z]);
         if (check_launch() != G2D_OK) return G2D_ERR_CUDA;
-        ldl_trinv_level_kernel<F><<<grid, FTH, 0, st>>>(a, n, b, w, out, true);
+        ldl_scale_kernel<F><<<(unsigned)blocks, 256, 0, st>>>(outs[z], n, size, dblks[z]);
+        if (check_launch() != G2D_OK) return G2D_ERR_CUDA;
+        ldl_normalize_kernel<F><<<(unsigned)blocks, 256, 0, st>>>(outs[z], n, size);
         if (check_launch() != G2D_OK) return G2D_ERR_CUDA;
     }
-    const int64_t work = n * (n / size);
-    int64_t blocks = ceil_div(work, 256);
-    if (blocks > 148 * 64) blocks = 148 * 64;
-    ldl_copy_diag_kernel<F><<<(unsigned)(ceil_div(n * size, 256) < 148 * 64 ? ceil_div(n * size, 256) : 148 * 64), 256, 0, st>>>(out, n, size, dblk);
-    if (check_launch() != G2D_OK) return G2D_ERR_CUDA;
-    ldl_scale_kernel<F><<<(unsigned)blocks, 256, 0, st>>>(out, n, size, dblk);
-    if (check_launch() != G2D_OK) return G2D_ERR_CUDA;
-    ldl_normalize_kernel<F><<<(unsigned)blocks, 256, 0, st>>>(out, n, size);
-    return check_launch();
+    return G2D_OK;
 }
 
 }  // namespace g2d
@@ -397,7 +490,8 @@ using namespace g2d;
 static size_t ldl_bytes(int dtype, int64_t n) {
     const size_t elem = dtype == G2D_F32 ? 4 : 8;
     const size_t nb = (size_t)ceil_div(n, FB);
-    return ((nb * FB * FB + (size_t)n * FB + (size_t)n * n) * elem + 255) & ~(size_t)255;
+    const size_t planes = dtype == G2D_F32 ? 6 * (size_t)n * n : 0;  // operand planes of the tensor-core triangular inverse
+    return ((nb * FB * FB + (size_t)n * FB + (size_t)n * n + planes) * elem + 255) & ~(size_t)255;
 }
 
 extern "C" int g2d_ldl_workspace_bytes(int dtype, int64_t n, size_t *bytes) {
@@ -406,15 +500,46 @@ extern "C" int g2d_ldl_workspace_bytes(int dtype, int64_t n, size_t *bytes) {
     return G2D_OK;
 }
 
-extern "C" int g2d_ldl_of_inverse(int dtype, int64_t n, void *a, int32_t size, void *out, int32_t *status_flag, void *workspace,
-                                  size_t workspace_bytes, void *stream) {
-    if ((dtype != G2D_F32 && dtype != G2D_F64) || n < 0 || size <= 0) return G2D_ERR_BAD_ARGUMENT;
-    if (n == 0) return G2D_OK;
+static int ldl_check(int dtype, int64_t n, int32_t size, const void *a, const void *out, const void *workspace, size_t workspace_bytes) {
+    if ((dtype != G2D_F32 && dtype != G2D_F64) || n <= 0 || size <= 0) return G2D_ERR_BAD_ARGUMENT;
     if (n % size != 0 || size > FB) return size > FB ? G2D_ERR_TOO_LARGE : G2D_ERR_BAD_ARGUMENT;
     if (!a || !out) return G2D_ERR_BAD_ARGUMENT;
     if (!workspace || workspace_bytes < ldl_bytes(dtype, n)) return G2D_ERR_WORKSPACE;
     if (ceil_div(n, FB) > 46000) return G2D_ERR_TOO_LARGE;  // tile pairs of one launch must fit a 1-D grid
+    return G2D_OK;
+}
+
+extern "C" int g2d_ldl_of_inverse(int dtype, int64_t n, void *a, int32_t size, void *out, int32_t *status_flag, void *workspace,
+                                  size_t workspace_bytes, void *stream) {
+    if (n == 0 && (dtype == G2D_F32 || dtype == G2D_F64) && size > 0) return G2D_OK;
+    const int status = ldl_check(dtype, n, size, a, out, workspace, workspace_bytes);
+    if (status != G2D_OK) return status;
     cudaStream_t st = (cudaStream_t)stream;
-    return dtype == G2D_F32 ? ldl_run<float>(n, (float *)a, size, (float *)out, status_flag, workspace, st)
-                            : ldl_run<double>(n, (double *)a, size, (double *)out, status_flag, workspace, st);
+    const int sizes[1] = {size};
+    void *const ws[1] = {workspace};
+    if (dtype == G2D_F32) {
+        float *as[1] = {(float *)a}, *outs[1] = {(float *)out};
+        return ldl_run<float>(1, &n, as, sizes, outs, status_flag, ws, st);
+    }
+    double *as[1] = {(double *)a}, *outs[1] = {(double *)out};
+    return ldl_run<double>(1, &n, as, sizes, outs, status_flag, ws, st);
+}
+
+extern "C" int g2d_ldl_of_inverse_pair(int dtype, int64_t n0, void *a0, int32_t size0, void *out0, void *workspace0, size_t workspace0_bytes,
+                                       int64_t n1, void *a1, int32_t size1, void *out1, void *workspace1, size_t workspace1_bytes,
+                                       int32_t *status_flags, void *stream) {
+    int status = ldl_check(dtype, n0, size0, a0, out0, workspace0, workspace0_bytes);
+    if (status != G2D_OK) return status;
+    status = ldl_check(dtype, n1, size1, a1, out1, workspace1, workspace1_bytes);
+    if (status != G2D_OK) return status;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int64_t ns[2] = {n0, n1};
+    const int sizes[2] = {size0, size1};
+    void *const ws[2] = {workspace0, workspace1};
+    if (dtype == G2D_F32) {
+        float *as[2] = {(float *)a0, (float *)a1}, *outs[2] = {(float *)out0, (float *)out1};
+        return ldl_run<float>(2, ns, as, sizes, outs, status_flags, ws, st);
+    }
+    double *as[2] = {(double *)a0, (double *)a1}, *outs[2] = {(double *)out0, (double *)out1};
+    return ldl_run<double>(2, ns, as, sizes, outs, status_flags, ws, st);
 }

@@ -1,0 +1,253 @@
+// Triangular inverse of the factor preparation on the tensor cores (float only).
+//
+// The inverse Lf = T^{-1} of the lower triangular Cholesky factor is built by doubling: at level b every aligned pair
+// of finished b x b diagonal blocks [A^{-1} 0; . B^{-1}] of Lf is completed by X = -B^{-1} (C A^{-1}) with
+// C = T[second half rows, first half columns].  From b = 128 on, both products of a level run here as tcgen05.mma
+// kind::tf32 GEMMs over 128 x 128 output tiles with the 3xTF32 split (hi*hi + lo*hi + hi*lo into one fp32 accumulator
+// in tensor memory).  The MMA wants both operands K-major, so the first product is formed transposed,
+//     W^T[j][i] = sum_k Lf^T[j][k] T[i][k]        (k from the tile's first row j0 to the end of the first half)
+//     X[i][j]   = -sum_k Lf[i][k] W^T[j][k]       (k from the start of the second half through the tile's rows)
+// and every operand is kept as ready-made hi / lo planes: Lf and its transpose (both written by the second product's
+// epilogue), and one plane pair whose lower triangle holds T and whose upper triangle receives W^T.
+// Same pipeline as the macro updates of the sweep: one warp issues TMA loads into a three-stage ring, one warp
+// issues the MMAs, four warps read the accumulator and store; every wait is bounded.
+#include "g2d_tc.cuh"
+
+namespace g2d {
+
+struct FactorMaps {
+    CUtensorMap out_hi, out_lo, outt_hi, outt_lo, tw_hi, tw_lo;
+};
+struct TrinvJob {
+    FactorMaps maps[2];
+    FactorPlanes p[2];
+    int pairs;   // pairs of diagonal blocks of the largest problem; blockIdx.x = problem * pairs + pair
+    int tiles;   // b / 128
+    int64_t b;
+    int second;  // 0: W^T, 1: X
+};
+
+constexpr uint32_t TRINV_TMEM_COLS = 128;
+
+__global__ void __launch_bounds__(TC_THREADS) trinv_tc_kernel(const __grid_constant__ TrinvJob job) {
+    extern __shared__ unsigned char tc_smem_raw[];
+    __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], accum_bar;
+    __shared__ uint32_t tmem_slot;
+    __shared__ int failed;
+    const int z = (int)blockIdx.x >= job.pairs ? 1 : 0;
+    const int64_t pair = (int64_t)blockIdx.x - (int64_t)z * job.pairs;
+    const FactorPlanes P = z ? job.p[1] : job.p[0];
+    const FactorMaps *maps = z ? &job.maps[1] : &job.maps[0];
+    const int64_t n = P.n, b = job.b;
+    const int64_t r0 = pair * 2 * b, r1 = r0 + b;  // first half rows [r0, r1), second half rows [r1, r2)
+    if (r1 >= n) return;
+    const int64_t r2 = min(r0 + 2 * b, n);
+    // output tile: rows m0.. of the A operand's matrix, columns n0.. of the B operand's
+    int64_t m0, n0, k_lo, k_hi;
+    const CUtensorMap *a_hi, *a_lo;
+    if (!job.second) {
+        m0 = r0 + (int64_t)blockIdx.z * MT;  // j: long k ranges (small j) are scheduled first
+        n0 = r1 + (int64_t)blockIdx.y * MT;  // i
+        if (n0 >= r2) return;
+        k_lo = m0;
+        k_hi = r1;
+        a_hi = &maps->outt_hi;
+        a_lo = &maps->outt_lo;
+    } else {
+        m0 = r1 + (int64_t)(job.tiles - 1 - (int)blockIdx.y) * MT;  // i: long k ranges (large i) first
+        if (m0 >= r2) return;
+        n0 = r0 + (int64_t)blockIdx.z * MT;  // j
+        k_lo = r1;
+        k_hi = min(m0 + MT, r2);
+        a_hi = &maps->out_hi;
+        a_lo = &maps->out_lo;
+    }
+    const int chunks = (int)ceil_div(k_hi - k_lo, (int64_t)KC);  // a ragged tail reads zeros beyond the matrix
+
+    const uint32_t smem_base = (smem_u32(tc_smem_raw) + 1023u) & ~1023u;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        mbar_init(&accum_bar, 1);
+        failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(TRINV_TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int ch = 0; ch < chunks; ++ch) {
+                const int stage = ch % STAGES, round = ch / STAGES;
+                if (round > 0 && !mbar_wait(&empty_bar[stage], (round - 1) & 1)) { failed = 1; break; }
+                const int k = (int)(k_lo + (int64_t)ch * KC);
+                const uint32_t dst = smem_base + stage * STAGE_BYTES;
+                mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
+                tma_load_2d(dst, a_hi, k, (int)m0, &full_bar[stage]);
+                tma_load_2d(dst + TILE_BYTES, a_lo, k, (int)m0, &full_bar[stage]);
+                tma_load_2d(dst + 2 * TILE_BYTES, &maps->tw_hi, k, (int)n0, &full_bar[stage]);
+                tma_load_2d(dst + 3 * TILE_BYTES, &maps->tw_lo, k, (int)n0, &full_bar[stage]);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            for (int ch = 0; ch < chunks; ++ch) {
+                const int stage = ch % STAGES, round = ch / STAGES;
+                if (!mbar_wait(&full_bar[stage], round & 1)) { failed = 1; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t s_a_hi = smem_base + stage * STAGE_BYTES, s_a_lo = s_a_hi + TILE_BYTES, s_b_hi = s_a_hi + 2 * TILE_BYTES,
+                               s_b_lo = s_a_hi + 3 * TILE_BYTES;
+#pragma unroll
+                for (int ks = 0; ks < KC / 8; ++ks) {
+                    const uint32_t off = ks * 32;  // 8 tf32 values = 32 bytes along the swizzled row
+                    umma_tf32(tmem, umma_desc(s_a_hi + off), umma_desc(s_b_hi + off), IDESC, (ch == 0 && ks == 0) ? 0u : 1u);
+                    umma_tf32(tmem, umma_desc(s_a_lo + off), umma_desc(s_b_hi + off), IDESC, 1u);
+                    umma_tf32(tmem, umma_desc(s_a_hi + off), umma_desc(s_b_lo + off), IDESC, 1u);
+                }
+                umma_commit(&empty_bar[stage]);  // arrives when the MMAs above have read the stage
+            }
+            umma_commit(&accum_bar);             // arrives when every MMA issued so far has completed
+        }
+    } else {
+        // epilogue warps: lanes 32 q .. 32 q + 31 of tensor memory, q = warp % 4; one accumulator row per thread
+        const int q = warp & 3;
+        const bool ok = mbar_wait(&accum_bar, 0);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (!ok) failed = 1;
+        const bool go = __all_sync(0xffffffffu, ok && !failed);  // warp-uniform: the tensor-memory loads are warp-wide
+        if (go) {
+            const int64_t gi = m0 + q * 32 + lane;
+            for (int cb = 0; cb < MT / 32; ++cb) {
+                uint32_t v[32];
+                tmem_load_32(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(cb * 32), v);
+                const int64_t gj0 = n0 + cb * 32;
+                if (!job.second) {
+                    // W^T[gi][gj]: gi is inside the first half (always a row of the matrix), gj is cut at r2
+                    float *hi = P.tw_hi + gi * n + gj0, *lo = P.tw_lo + gi * n + gj0;
+#pragma unroll
+                    for (int x = 0; x < 32; x += 4) {
+                        if (gj0 + x < r2) {  // r2 is a multiple of 4: a group is inside or outside as a whole
+                            float4 h, l;
+                            split_tf32(__uint_as_float(v[x]), h.x, l.x);
+                            split_tf32(__uint_as_float(v[x + 1]), h.y, l.y);
+                            split_tf32(__uint_as_float(v[x + 2]), h.z, l.z);
+                            split_tf32(__uint_as_float(v[x + 3]), h.w, l.w);
+                            *reinterpret_cast<float4 *>(hi + x) = h;
+                            *reinterpret_cast<float4 *>(lo + x) = l;
+                        }
+                    }
+                } else if (gi < r2) {
+                    // X[gi][gj] = -acc: the inverse itself, its split, and the split of its transpose (coalesced across the lanes)
+                    float *dst = P.out + gi * n + gj0, *hi = P.out_hi + gi * n + gj0, *lo = P.out_lo + gi * n + gj0;
+#pragma unroll
+                    for (int x = 0; x < 32; x += 4) {
+                        float4 val = make_float4(-__uint_as_float(v[x]), -__uint_as_float(v[x + 1]), -__uint_as_float(v[x + 2]), -__uint_as_float(v[x + 3]));
+                        float4 h, l;
+                        split_tf32(val.x, h.x, l.x);
+                        split_tf32(val.y, h.y, l.y);
+                        split_tf32(val.z, h.z, l.z);
+                        split_tf32(val.w, h.w, l.w);
+                        *reinterpret_cast<float4 *>(dst + x) = val;
+                        *reinterpret_cast<float4 *>(hi + x) = h;
+                        *reinterpret_cast<float4 *>(lo + x) = l;
+                        P.outt_hi[(gj0 + x) * n + gi] = h.x;
+                        P.outt_hi[(gj0 + x + 1) * n + gi] = h.y;
+                        P.outt_hi[(gj0 + x + 2) * n + gi] = h.z;
+                        P.outt_hi[(gj0 + x + 3) * n + gi] = h.w;
+                        P.outt_lo[(gj0 + x) * n + gi] = l.x;
+                        P.outt_lo[(gj0 + x + 1) * n + gi] = l.y;
+                        P.outt_lo[(gj0 + x + 2) * n + gi] = l.z;
+                        P.outt_lo[(gj0 + x + 3) * n + gi] = l.w;
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        if (failed) {
+            // give outstanding loads and MMAs a bounded chance to land before the memory they target is released
+            if (lane == 0) mbar_wait(&accum_bar, 0);
+            __syncwarp();
+        }
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TRINV_TMEM_COLS) : "memory");
+    }
+    if (threadIdx.x == 0 && failed && P.flag) atomicExch(P.flag, -1);
+}
+
+// Operand planes after the 64-level of the doubling: T strictly below the diagonal into the lower triangle of tw, and the
+// finished 128 x 128 diagonal blocks of Lf (lower triangular) into out / outt with explicit zeros in their other halves.
+__global__ void trinv_split_kernel(FactorPlanes p0, FactorPlanes p1) {
+    const FactorPlanes P = blockIdx.y ? p1 : p0;
+    const int64_t n = P.n, total = n * n;
+    for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = t / n, c = t % n;
+        if (c < r) {
+            float h, l;
+            split_tf32(P.a[t], h, l);
+            P.tw_hi[t] = h;
+            P.tw_lo[t] = l;
+        }
+        if (r / MT == c / MT) {
+            float h, l;
+            split_tf32(c <= r ? P.out[t] : 0.f, h, l);
+            P.out_hi[t] = h;
+            P.out_lo[t] = l;
+            split_tf32(c >= r ? P.out[c * n + r] : 0.f, h, l);
+            P.outt_hi[t] = h;
+            P.outt_lo[t] = l;
+        }
+    }
+}
+
+static bool factor_maps(FactorMaps *maps, const FactorPlanes &p) {
+    return make_map(&maps->out_hi, p.out_hi, p.n, p.n) && make_map(&maps->out_lo, p.out_lo, p.n, p.n) &&
+           make_map(&maps->outt_hi, p.outt_hi, p.n, p.n) && make_map(&maps->outt_lo, p.outt_lo, p.n, p.n) &&
+           make_map(&maps->tw_hi, p.tw_hi, p.n, p.n) && make_map(&maps->tw_lo, p.tw_lo, p.n, p.n);
+}
+
+// Levels b = 128, 256, ... of the doubling for one or two problems whose 128 x 128 diagonal blocks are finished.
+int launch_trinv_tc(int count, const FactorPlanes *problems, cudaStream_t stream) {
+    static bool configured[64] = {};
+    const size_t smem = (size_t)STAGES * STAGE_BYTES + 1024;
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return G2D_ERR_CUDA;
+    if (!configured[device]) {
+        if (cudaFuncSetAttribute(trinv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return G2D_ERR_CUDA;
+        configured[device] = true;
+    }
+    TrinvJob job;
+    int64_t n_max = 0;
+    for (int z = 0; z < 2; ++z) {
+        job.p[z] = problems[z < count ? z : 0];
+        if (!factor_maps(&job.maps[z], job.p[z])) return G2D_ERR_CUDA;
+        n_max = job.p[z].n > n_max ? job.p[z].n : n_max;
+    }
+    trinv_split_kernel<<<dim3(148 * 8, count), 256, 0, stream>>>(job.p[0], job.p[1]);
+    if (check_launch() != G2D_OK) return G2D_ERR_CUDA;
+    for (int64_t b = MT; b < n_max; b *= 2) {
+        const int64_t pairs = ceil_div(n_max, 2 * b), tiles = b / MT;
+        if (tiles > 65535 || pairs * count > 0x7fffffff) return G2D_ERR_TOO_LARGE;
+        job.pairs = (int)pairs;
+        job.tiles = (int)tiles;
+        job.b = b;
+        for (int second = 0; second < 2; ++second) {
+            job.second = second;
+            trinv_tc_kernel<<<dim3((unsigned)(pairs * count), (unsigned)tiles, (unsigned)tiles), TC_THREADS, smem, stream>>>(job);
+            if (check_launch() != G2D_OK) return G2D_ERR_CUDA;
+        }
+    }
+    return G2D_OK;
+}
+
+}  // namespace g2d

@@ -14,77 +14,11 @@
 // warps 2-5 read the accumulators (each its own 32 lanes) and add them into C / Y.  A three-stage ring of
 // 64 KB (A_hi, A_lo, B_hi, B_lo tiles of 128 x 32) is handed over with mbarriers; tcgen05.commit releases a stage
 // when its MMAs have read it.  Every wait is bounded: on time-out a flag is set and the CTA winds down.
-#include <cuda.h>
-
-#include "g2d_common.cuh"
+#include "g2d_tc.cuh"
 
 namespace g2d {
 
-constexpr int MT = 128;                    // macro tile edge
-constexpr int KC = 32;                     // k per chunk: 32 floats = one 128-byte swizzle row
-constexpr int TILE_BYTES = MT * KC * 4;    // 16 KB
-constexpr int STAGE_BYTES = 4 * TILE_BYTES;
-constexpr int STAGES = 3;
-constexpr int TC_THREADS = 192;
-constexpr uint32_t TMEM_COLS = 256;
-constexpr long long WAIT_CYCLES = 2000000000LL;  // about a second
-constexpr int RB_I = 8, RB_J = 16;               // rasterisation block of the far updates: 128 macro tiles, about one wave of CTAs
-
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// false on time-out
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
-    const long long start = clock64();
-    while (!mbar_try_wait(bar, parity)) {
-        if (clock64() - start > WAIT_CYCLES) return false;
-    }
-    return true;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                 ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
-                 : "memory");
-}
-__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t *bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-// K-major operand tile of 128-byte rows, 128-byte swizzle: 8-row groups 1024 bytes apart
-__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);   // start address
-    d |= (uint64_t)1 << 16;                       // leading byte offset (unused with swizzle)
-    d |= (uint64_t)(1024 >> 4) << 32;             // stride byte offset
-    d |= (uint64_t)1 << 46;                       // descriptor version
-    d |= (uint64_t)2 << 61;                       // SWIZZLE_128B
-    return d;
-}
-// D fp32, A and B tf32, both K-major, M = 128, N = 128
-constexpr uint32_t IDESC = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(MT >> 3) << 17) | ((uint32_t)(MT >> 4) << 24);
+constexpr int RB_I = 8, RB_J = 16;  // rasterisation block of the far updates: 128 macro tiles, about one wave of CTAs
 
 struct TcMaps {
     CUtensorMap l_hi, l_lo, c_hi, c_lo;      // A operands: [rows][k]
@@ -239,13 +173,6 @@ __global__ void __launch_bounds__(TC_THREADS) macro_update_tc_kernel(const __gri
 
 // ---- one-time operand preparation ---------------------------------------------------------------------
 
-__device__ __forceinline__ void split_tf32(float a, float &hi, float &lo) {
-    uint32_t h;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(a));
-    hi = __uint_as_float(h);
-    lo = a - hi;
-}
-
 // L (row-major, read strictly below the diagonal) -> hi / lo copies with zeros elsewhere
 __global__ void split_lower_kernel(const float *__restrict__ l, int64_t m, float *__restrict__ hi, float *__restrict__ lo) {
     const int64_t total = m * m;
@@ -283,34 +210,6 @@ __global__ void split_upper_transposed_kernel(const float *__restrict__ u, int64
 }
 
 // ---- host side ---------------------------------------------------------------------------------------
-
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
-                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_tiled_fn() {
-    static EncodeTiledFn fn = nullptr;
-    if (!fn) {
-        void *ptr = nullptr;
-        cudaDriverEntryPointQueryResult result;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) == cudaSuccess &&
-            result == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(ptr);
-    }
-    return fn;
-}
-
-// row-major fp32 matrix [rows][cols]; boxes of 128 rows x 32 columns, 128-byte swizzle, zero fill outside
-static bool make_map(CUtensorMap *map, const float *base, int64_t rows, int64_t cols) {
-    EncodeTiledFn fn = encode_tiled_fn();
-    if (!fn) return false;
-    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)cols * sizeof(float)};
-    const cuuint32_t box[2] = {KC, MT};
-    const cuuint32_t elem[2] = {1, 1};
-    return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
-              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
 
 int tc_prepare_operands(const float *l, const float *u, int64_t m, int64_t n, const TcPlanes &pl, cudaStream_t stream) {
     split_lower_kernel<<<148 * 8, 256, 0, stream>>>(l, m, pl.l_hi, pl.l_lo);

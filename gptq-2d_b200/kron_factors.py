@@ -39,6 +39,8 @@ def ldl_of_inverse(M: torch.Tensor, size: int = 1, check: bool = True) -> torch.
                                           need.value, _abi.stream_of(M)), "g2d_ldl_of_inverse")
     if check:
         pivot = int(flag.item())
+        if pivot < 0:
+            raise RuntimeError("ldl_of_inverse: a bounded wait inside a tensor-core kernel ran out; the result is not valid")
         if pivot:
             raise torch.linalg.LinAlgError(f"ldl_of_inverse: the matrix is not positive definite (pivot {pivot} is not positive)")
     return out
@@ -80,28 +82,39 @@ def gptq_d_sided(x: torch.Tensor, factors, *, quantizer=None, quantizer_inputs=(
     return z.reshape(x.shape)
 
 
-_SIDE_STREAMS: dict = {}
-
-
 @torch.no_grad()
 def feedback_factors_from_grams(g: torch.Tensor, h: torch.Tensor, super_entry_shape: tuple[int, int] = (1, 1),
                                 check: bool = False) -> tuple[torch.Tensor, torch.Tensor]:
     """L from the output-side Gram ``g [m, m]`` and U from the input-side Gram ``h [n, n]`` (``U = ldl_of_inverse(h).T``),
-    prepared concurrently: both factorizations are chains of small dependent launches, so the second one runs on a side
-    stream that forks from and joins the current stream (capturable in a CUDA graph)."""
+    prepared together: both factorizations are chains of short dependent launches, so they advance block step by block
+    step in the same launches (``g2d_ldl_of_inverse_pair``) and the pair costs little more than the larger one."""
     p, q = super_entry_shape
-    current = torch.cuda.current_stream(g.device)
-    side = _SIDE_STREAMS.get(g.device)
-    if side is None:
-        side = _SIDE_STREAMS[g.device] = torch.cuda.Stream(device=g.device)
-    side.wait_stream(current)
-    with torch.cuda.stream(side):
-        lower_of_h = ldl_of_inverse(h, size=q, check=False)
-    l = ldl_of_inverse(g, size=p, check=False)
-    current.wait_stream(side)
-    lower_of_h.record_stream(current)
+    assert g.dim() == 2 and g.size(0) == g.size(1) and h.dim() == 2 and h.size(0) == h.size(1), "expected square matrices"
+    assert g.is_cuda and h.is_cuda and g.device == h.device, "the CUDA factor preparation requires CUDA tensors on one device"
+    assert g.dtype == h.dtype, "both Grams must have the same dtype"
+    m, n = g.size(0), h.size(0)
+    assert p > 0 and q > 0 and m % p == 0 and n % q == 0, "the block sizes must divide the matrix sizes"
+    if m == 0 or n == 0:
+        return ldl_of_inverse(g, size=p, check=check), ldl_of_inverse(h, size=q, check=check).t()
+    lib = _abi.library()
+    code = _abi.dtype_code(g.dtype)
+    works = [x.clone(memory_format=torch.contiguous_format) for x in (g, h)]  # the kernels factor in place
+    outs = [torch.empty_like(w) for w in works]
+    spaces = []
+    for k in (m, n):
+        need = ctypes.c_size_t()
+        _abi.check(lib.g2d_ldl_workspace_bytes(code, k, ctypes.byref(need)), "g2d_ldl_workspace_bytes")
+        spaces.append(torch.empty(need.value, dtype=torch.uint8, device=g.device))
+    flags = torch.zeros(2, dtype=torch.int32, device=g.device)
+    with torch.cuda.device(g.device):
+        _abi.check(lib.g2d_ldl_of_inverse_pair(code, m, works[0].data_ptr(), p, outs[0].data_ptr(), spaces[0].data_ptr(), spaces[0].numel(),
+                                               n, works[1].data_ptr(), q, outs[1].data_ptr(), spaces[1].data_ptr(), spaces[1].numel(),
+                                               flags.data_ptr(), _abi.stream_of(g)), "g2d_ldl_of_inverse_pair")
     if check:
-        for name, factor in (("G", l), ("H", lower_of_h)):
-            if not bool(torch.isfinite(factor).all()):
-                raise torch.linalg.LinAlgError(f"feedback_factors_from_grams: the factor of {name} is not finite (is the matrix positive definite?)")
-    return l, lower_of_h.t()
+        pivots = flags.tolist()
+        for name, pivot in zip(("G", "H"), pivots):
+            if pivot < 0:
+                raise RuntimeError("feedback_factors_from_grams: a bounded wait inside a tensor-core kernel ran out; the result is not valid")
+            if pivot:
+                raise torch.linalg.LinAlgError(f"feedback_factors_from_grams: {name} is not positive definite (pivot {pivot} is not positive)")
+    return outs[0], outs[1].t()

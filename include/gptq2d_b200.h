@@ -177,6 +177,15 @@ int g2d_ldl_workspace_bytes(int dtype, int64_t n, size_t *bytes);
 int g2d_ldl_of_inverse(int dtype, int64_t n, void *a, int32_t size, void *out, int32_t *status_flag, void *workspace,
                        size_t workspace_bytes, void *stream);
 
+/* Two factorizations of g2d_ldl_of_inverse advanced together in the same launches (both are chains of short
+ * dependent kernels, so the pair costs little more than the larger one): the L and U of one layer, i.e. both
+ * calls of feedback_factors (gptq_2d_reference.py:52-66).  Each problem has its own workspace
+ * (g2d_ldl_workspace_bytes of its n); status_flags is int32[2] on the device or NULL.  Results are identical
+ * to two single calls. */
+int g2d_ldl_of_inverse_pair(int dtype, int64_t n0, void *a0, int32_t size0, void *out0, void *workspace0,
+                            size_t workspace0_bytes, int64_t n1, void *a1, int32_t size1, void *out1,
+                            void *workspace1, size_t workspace1_bytes, int32_t *status_flags, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

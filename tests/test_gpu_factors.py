@@ -79,6 +79,30 @@ def test_feedback_factors_and_errors(K):
     assert K.ldl_of_inverse(torch.empty(0, 0, device="cuda")).shape == (0, 0)
 
 
+@pytest.mark.parametrize("dtype", [torch.float64, torch.float32])
+@pytest.mark.parametrize("m, n, p, q", [(200, 330, 1, 1), (1100, 256, 2, 4), (64, 1345, 1, 5), (640, 640, 1, 1)])
+def test_pair_equals_two_single_calls(K, dtype, m, n, p, q):
+    """Both factors of a layer prepared in shared launches are bit-identical to one call per factor, whatever the sizes."""
+    gen = torch.Generator(device="cuda").manual_seed(m + n)
+    grams = []
+    for k in (m, n):
+        a = torch.randn(k + 32, k, generator=gen, device="cuda", dtype=dtype)
+        grams.append(a.T @ a / k + 0.01 * torch.eye(k, device="cuda", dtype=dtype))
+    l, u = K.feedback_factors_from_grams(grams[0], grams[1], (p, q), check=True)
+    assert torch.equal(l, K.ldl_of_inverse(grams[0], p))
+    assert torch.equal(u, K.ldl_of_inverse(grams[1], q).T)
+    check_structure(l, p)
+    check_structure(u.T, q)
+
+
+def test_pair_reports_the_failing_factor(K):
+    good = torch.eye(130, device="cuda", dtype=torch.float64)
+    with pytest.raises(torch.linalg.LinAlgError, match="H is not positive definite"):
+        K.feedback_factors_from_grams(good, -torch.eye(70, device="cuda", dtype=torch.float64), check=True)
+    with pytest.raises(torch.linalg.LinAlgError, match="G is not positive definite"):
+        K.feedback_factors_from_grams(-good, torch.eye(70, device="cuda", dtype=torch.float64), check=True)
+
+
 def test_d_sided_golden(K):
     """gptq_2d_reference.py:450-478: N-factor rounding equals Algorithm 1 on the explicit Kronecker Gram (values from the reference's alg4)."""
     g = load_golden("d_sided_fp64.npz")

@@ -300,3 +300,28 @@ def test_quantizer_sees_quantized_values(api):
 
         run(x, l, u, quantizer=quantizer)
         assert len(earlier) > 0
+
+
+def test_unused_triangles_are_never_read_fp32(api):
+    """gptq_2d.py:1393-1395: only the entries of L below and of U above the diagonal are read; NaN elsewhere must not
+    reach the result on any schedule (the tensor-core operands are sanitised copies)."""
+    G, Q = api
+    gen = torch.Generator(device="cuda").manual_seed(11)
+    m, n = 520, 392
+    w = 0.02 * torch.randn(m, n, generator=gen, device="cuda")
+    l = torch.tril(torch.randn(m, m, generator=gen, device="cuda") * (0.3 / m ** .5), -1)
+    u = torch.triu(torch.randn(n, n, generator=gen, device="cuda") * (0.3 / n ** .5), 1)
+    scale = Q.int_abs_max_scale_triton(w, qmin=-8, qmax=7, dtype=torch.float16).expand(m, n)
+    zero = torch.zeros(1, 1, device="cuda").expand(m, n)
+    quantizer = functools.partial(Q.affine_quantizer_triton, qmin=-8, qmax=7)
+    poisoned_l = torch.where(torch.ones_like(l).tril(-1) > 0, l, torch.nan)
+    poisoned_u = torch.where(torch.ones_like(u).triu(1) > 0, u, torch.nan)
+    before = G.SWEEP_SCHEDULE
+    try:
+        for schedule in (0, 1, 2):
+            G.SWEEP_SCHEDULE = schedule
+            clean = G.gptq_2d(w, l, u, quantizer=quantizer, quantizer_inputs=(scale, zero))
+            dirty = G.gptq_2d(w, poisoned_l, poisoned_u, quantizer=quantizer, quantizer_inputs=(scale, zero))
+            assert torch.isfinite(dirty).all() and torch.equal(clean, dirty)
+    finally:
+        G.SWEEP_SCHEDULE = before
