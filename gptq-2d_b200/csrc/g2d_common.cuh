@@ -98,6 +98,15 @@ struct SweepArgs {
     float *et_hi = nullptr, *et_lo = nullptr, *c_hi = nullptr, *c_lo = nullptr;
 };
 
+// fp32 -> tf32 hi (round to nearest) and the fp32 remainder: a = hi + lo exactly, and hi*hi' + lo*hi' + hi*lo' recovers
+// the fp32 product to about 2^-21 relative
+__device__ __forceinline__ void split_tf32(float a, float &hi, float &lo) {
+    uint32_t h;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(a));
+    hi = __uint_as_float(h);
+    lo = a - hi;
+}
+
 // Operand planes of the tensor-core macro updates (all float; see g2d_macro_update_tc.cu).
 struct TcPlanes {
     float *et_hi, *et_lo, *c_hi, *c_lo;  // written by the tile sweep
@@ -118,6 +127,23 @@ struct FactorPlanes {
     int *flag;                 // receives -1 when a bounded wait inside a kernel ran out (may be null)
 };
 int launch_trinv_tc(int count, const FactorPlanes *problems, cudaStream_t stream);
+
+// Tensor-core trailing update of the blocked Cholesky factorization (see g2d_factors_tc.cu).  pt planes are
+// [n][SYRK_TC_K] float: pt[r][k] = a[o + k][r] for the group of block rows that starts at row o.
+constexpr int SYRK_TC_K = 256;
+struct SyrkTcMaps {
+    alignas(64) unsigned char hi[128], lo[128];  // tensor maps of the hi and lo planes (opaque here)
+};
+struct SyrkTcTarget {
+    const SyrkTcMaps *maps;
+    float *a;
+    int64_t n;
+    int t_lo, t_hi;  // target 128-row tile rows [t_lo, t_hi), tile columns up to the diagonal
+    int kw;          // rows of the group (<= SYRK_TC_K)
+    int *flag;
+};
+bool syrk_tc_maps(SyrkTcMaps *maps, const float *pt_hi, const float *pt_lo, int64_t n);
+int launch_syrk_tc(int count, const SyrkTcTarget *targets, cudaStream_t stream);
 
 template <typename F>
 int launch_tile_sweep(const SweepArgs<F> &args, int S, cudaStream_t stream, int parity = 0);

@@ -66,25 +66,32 @@ __device__ __forceinline__ void tile_product(F (&acc)[8][8], int64_t K, LA la, L
 
 // Up to two factorizations advance together, block step by block step, in the same launches (the steps are chains of
 // short dependent kernels, so a second matrix rides along almost for free).  Problem z of a launch is blockIdx.y, or
-// folded into blockIdx.x where the grid is three-dimensional already; a problem with fewer block rows starts later.
+// folded into blockIdx.x where the grid is three-dimensional already.  Block rows are taken in groups of GROUP
+// (the trailing update of a tensor-core problem is applied once per group), and the problems are lined up so that
+// their groups end at the same steps: with block-row counts rounded up to a multiple of GROUP, the launch for block
+// row s of the largest problem serves block row s - (steps - rounded count) of a smaller one.
+constexpr int GROUP = 4;
 template <typename F>
 struct LdlProblem {
     F *a, *out, *tinv, *w;
     int64_t n;
     int *flag;
+    int tc;                       // trailing updates of whole groups run on the tensor cores (float, n % 4 == 0)
+    float *pt_hi[2], *pt_lo[2];   // [n][GROUP * 64] transposed split panels of the even and odd groups
 };
 template <typename F>
 struct LdlBatch {
     LdlProblem<F> p[2];
     int count;
-    int steps;  // block rows of the largest problem
+    int steps;  // block rows of the largest problem, rounded up to a multiple of GROUP
 };
+__host__ __device__ inline int padded_block_rows(int64_t n) { return (int)(ceil_div(ceil_div(n, (int64_t)64), (int64_t)GROUP) * GROUP); }
 #define LDL_PROBLEM(z)                                        \
     const LdlProblem<F> Q = (z) ? B.p[1] : B.p[0];            \
     F *const a = Q.a;                                         \
     const int64_t n = Q.n;                                    \
-    const int kb = (int)ceil_div(n, FB) - 1 - (B.steps - 1 - step_down); \
-    if (kb < 0) return;
+    const int kb = step_down - (B.steps - padded_block_rows(n)); \
+    if (kb < 0 || (int64_t)kb * FB >= n) return;
 
 template <typename F>
 __device__ __forceinline__ void zero_acc(F (&acc)[8][8]) {
@@ -200,16 +207,41 @@ __global__ void __launch_bounds__(FTH) ldl_trsm_kernel(LdlBatch<F> B, int step_d
         for (int y = 0; y < 8; ++y)
             if (r < bs) a[(o + r) * n + c0 + own8(tx, y)] = acc[x][y];
     }
+    if constexpr (std::is_same<F, float>::value) {
+        // tensor-core problems: the finished block row, transposed and split, is an operand of the group's trailing
+        // update (columns left of the group only); rows beyond a ragged block are zero in acc already
+        const int kb_lo = kb / GROUP * GROUP;
+        if (Q.tc && j < kb_lo) {
+            float *hi = Q.pt_hi[(kb / GROUP) & 1], *lo = Q.pt_lo[(kb / GROUP) & 1];
+            const int k0 = (kb - kb_lo) * FB;
+#pragma unroll
+            for (int y = 0; y < 8; ++y) {
+                const int64_t c = c0 + own8(tx, y);
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    float4 h, l;
+                    split_tf32(acc[4 * half][y], h.x, l.x);
+                    split_tf32(acc[4 * half + 1][y], h.y, l.y);
+                    split_tf32(acc[4 * half + 2][y], h.z, l.z);
+                    split_tf32(acc[4 * half + 3][y], h.w, l.w);
+                    const int64_t at = c * (GROUP * FB) + k0 + own8(ty, 4 * half);
+                    *reinterpret_cast<float4 *>(hi + at) = h;
+                    *reinterpret_cast<float4 *>(lo + at) = l;
+                }
+            }
+        }
+    }
 }
 
 // ---- step 1c: M'[TI, TJ] -= T[kb, TI]^T T[kb, TJ] for TJ <= TI < kb (lower triangle of tiles) ----
 template <typename F>
-__global__ void __launch_bounds__(FTH) ldl_syrk_kernel(LdlBatch<F> B, int step_down, bool row) {
+__global__ void __launch_bounds__(FTH) ldl_syrk_kernel(LdlBatch<F> B, int step_down) {
     LDL_PROBLEM(blockIdx.y)
-    // tile pairs (TI, TJ), TJ <= TI < kb, in row order: the last block row (TI = kb - 1) or everything above it
-    const int64_t above = (int64_t)(kb - 1) * kb / 2;
-    if (row ? (int64_t)blockIdx.x >= kb : (int64_t)blockIdx.x >= above) return;
-    const int64_t first = row ? above : 0;
+    // tile pairs (TI, TJ), TJ <= TI < kb, in row order.  A tensor-core problem updates only the block rows of its own
+    // group here (TI >= first block row of the group); the rows above wait for the group's update.
+    const int kb_lo = Q.tc ? kb / GROUP * GROUP : 0;
+    const int64_t first = (int64_t)kb_lo * (kb_lo + 1) / 2;
+    if ((int64_t)blockIdx.x >= (int64_t)kb * (kb + 1) / 2 - first) return;
     __shared__ __align__(16) F As[FK * FLD];
     __shared__ __align__(16) F Bs[FK * FLD];
     // linear index -> (TI, TJ) with TJ <= TI
@@ -374,52 +406,107 @@ int ldl_run(int count, const int64_t *ns, F *const *as, const int *sizes, F *con
     B.count = count;
     B.steps = 0;
     F *dblks[2] = {nullptr, nullptr};
+    SyrkTcMaps pt_maps[2][2];
     int64_t n_max = 0;
+    bool any_tc = false;
     for (int z = 0; z < count; ++z) {
         const int64_t n = ns[z];
         const int nb = (int)ceil_div(n, FB);
         F *tinv = (F *)workspaces[z];                             // [nb][64][64]
         dblks[z] = tinv + (int64_t)nb * FB * FB;                  // [n / size][size][size]
-        B.p[z] = LdlProblem<F>{as[z], outs[z], tinv, dblks[z] + n * (int64_t)FB /* [n][n] scratch of the doubling steps */, n,
-                               flags ? flags + z : nullptr};
-        B.steps = nb > B.steps ? nb : B.steps;
+        LdlProblem<F> &P = B.p[z];
+        P = LdlProblem<F>{as[z], outs[z], tinv, dblks[z] + n * (int64_t)FB /* [n][n] scratch of the doubling steps */, n,
+                          flags ? flags + z : nullptr, 0, {nullptr, nullptr}, {nullptr, nullptr}};
+        // float problems whose rows are 16-byte multiples use the tensor cores; the choice depends on the problem alone,
+        // never on its partner in the batch, so that a pair gives the results of two single calls
+        if (std::is_same<F, float>::value && n % 4 == 0) {
+            float *base = (float *)P.w + 7 * n * n;  // behind the scratch and the six planes of the triangular inverse
+            for (int k = 0; k < 2; ++k) {
+                P.pt_hi[k] = base + (2 * k) * n * (GROUP * FB);
+                P.pt_lo[k] = base + (2 * k + 1) * n * (GROUP * FB);
+                if (!syrk_tc_maps(&pt_maps[z][k], P.pt_hi[k], P.pt_lo[k], n)) return G2D_ERR_CUDA;
+            }
+            P.tc = 1;
+            any_tc = true;
+        }
+        const int padded = padded_block_rows(n);
+        B.steps = padded > B.steps ? padded : B.steps;
         n_max = n > n_max ? n : n_max;
         if (cudaMemsetAsync(outs[z], 0, sizeof(F) * (size_t)n * n, st) != cudaSuccess) return G2D_ERR_CUDA;
     }
     if (count == 1) B.p[1] = B.p[0];
     if (flags && cudaMemsetAsync(flags, 0, sizeof(int) * count, st) != cudaSuccess) return G2D_ERR_CUDA;
-    // Look-ahead: a step's trailing update is split into the block row that the next step factors (kept on the
-    // caller's stream) and the rest (a side stream), so that the latency-bound diagonal and panel kernels of the next
-    // step overlap the bulk of this step's update.  With kb the block row of a step, rest(kb) touches block rows
-    // <= kb - 2: the next diagonal block needs rest(kb + 2) and older, the next row update must follow rest(kb + 1).
+    // Each step factors one 64-row block row (last first): diagonal block, panel to its left, trailing update.  The
+    // update of a step reaches every row above for an ordinary problem, but only the rows of the step's own group of
+    // GROUP block rows for a tensor-core problem; the rows above the group get the whole group's update at once
+    // (K = 256) from the tensor cores.  Look-ahead: that update is split into the rows of the next group (kept on the
+    // caller's stream) and the rest (a side stream), so that the latency-bound kernels of the next group overlap the
+    // bulk of the update.  rest(g) touches the groups <= g - 2: group g needs rest(g + 2) and older before its first
+    // kernel (which also frees the panel planes that it reuses), and next(g) must follow rest(g + 1), whose targets
+    // it shares (the order of the additions is fixed, hence the result).
     SideLane *lane = acquire_side_lane();
     if (!lane) return G2D_ERR_CUDA;
     bool rest_recorded[4] = {false, false, false, false};
-    auto wait_rest = [&](int step) {
-        if (step <= B.steps - 1 && rest_recorded[step & 3]) return cudaStreamWaitEvent(st, lane->rest[step & 3], 0) == cudaSuccess;
+    const int groups = B.steps / GROUP;
+    auto wait_rest = [&](int g) {
+        if (g < groups && rest_recorded[g & 3]) return cudaStreamWaitEvent(st, lane->rest[g & 3], 0) == cudaSuccess;
         return true;
     };
-    for (int kb = B.steps - 1; kb >= 0; --kb) {  // block row of the largest problem; smaller problems join when it reaches theirs
-        if (!wait_rest(kb + 2)) return G2D_ERR_CUDA;
-        ldl_diag_kernel<F><<<dim3(1, count), 256, 0, st>>>(B, kb);
+    for (int s = B.steps - 1; s >= 0; --s) {  // block row of the largest problem; smaller problems are lined up by groups
+        const int g = s / GROUP;
+        if (s % GROUP == GROUP - 1 && !wait_rest(g + 2)) return G2D_ERR_CUDA;
+        ldl_diag_kernel<F><<<dim3(1, count), 256, 0, st>>>(B, s);
         if (check_launch() != G2D_OK) return G2D_ERR_CUDA;
-        if (kb > 0) {
-            ldl_trsm_kernel<F><<<dim3(kb, count), FTH, 0, st>>>(B, kb);
-            if (check_launch() != G2D_OK) return G2D_ERR_CUDA;
-            const int64_t rest = (int64_t)(kb - 1) * kb / 2;  // tile pairs of the block rows above kb - 1
-            rest_recorded[kb & 3] = false;
-            if (rest > 0) {  // the panel is final: the side stream may start on the block rows <= kb - 2
-                if (cudaEventRecord(lane->panel[kb & 3], st) != cudaSuccess || cudaStreamWaitEvent(lane->stream, lane->panel[kb & 3], 0) != cudaSuccess)
-                    return G2D_ERR_CUDA;
-                ldl_syrk_kernel<F><<<dim3((unsigned)rest, count), FTH, 0, lane->stream>>>(B, kb, false);
-                if (check_launch() != G2D_OK) return G2D_ERR_CUDA;
-                if (cudaEventRecord(lane->rest[kb & 3], lane->stream) != cudaSuccess) return G2D_ERR_CUDA;
-            }
-            if (!wait_rest(kb + 1)) return G2D_ERR_CUDA;
-            ldl_syrk_kernel<F><<<dim3(kb, count), FTH, 0, st>>>(B, kb, true);  // block row kb - 1, which the next step factors
-            if (check_launch() != G2D_OK) return G2D_ERR_CUDA;
-            rest_recorded[kb & 3] = rest > 0;
+        if (s == 0) break;
+        int64_t panel_tiles = 0, update_tiles = 0;
+        for (int z = 0; z < count; ++z) {
+            const int kb = s - (B.steps - padded_block_rows(ns[z]));
+            if (kb <= 0 || (int64_t)kb * FB >= ns[z]) continue;
+            const int kb_lo = B.p[z].tc ? kb / GROUP * GROUP : 0;
+            const int64_t tiles = (int64_t)kb * (kb + 1) / 2 - (int64_t)kb_lo * (kb_lo + 1) / 2;
+            panel_tiles = kb > panel_tiles ? kb : panel_tiles;
+            update_tiles = tiles > update_tiles ? tiles : update_tiles;
         }
+        if (panel_tiles > 0) {
+            ldl_trsm_kernel<F><<<dim3((unsigned)panel_tiles, count), FTH, 0, st>>>(B, s);
+            if (check_launch() != G2D_OK) return G2D_ERR_CUDA;
+        }
+        if (update_tiles > 0) {
+            ldl_syrk_kernel<F><<<dim3((unsigned)update_tiles, count), FTH, 0, st>>>(B, s);
+            if (check_launch() != G2D_OK) return G2D_ERR_CUDA;
+        }
+        if (s % GROUP != 0 || !any_tc) continue;
+        // the group g is complete: its update of everything above, for the tensor-core problems
+        SyrkTcTarget next[2], rest[2];
+        int targets = 0;
+        bool any_rest = false;
+        for (int z = 0; z < count; ++z) {
+            const int kb_lo = s - (B.steps - padded_block_rows(ns[z]));
+            if (!B.p[z].tc || kb_lo <= 0) continue;
+            const int64_t o = (int64_t)kb_lo * FB;
+            const int t_all = (int)(o / 128), t_next = t_all - GROUP * FB / 128;  // tile rows above the group; those of the next group start at t_next
+            const int kw = (int)(ns[z] - o < GROUP * FB ? ns[z] - o : GROUP * FB);
+            SyrkTcTarget t{&pt_maps[z][(kb_lo / GROUP) & 1], (float *)B.p[z].a, ns[z], t_next, t_all, kw, B.p[z].flag};
+            next[targets] = t;
+            t.t_lo = 0;
+            t.t_hi = t_next;
+            rest[targets] = t;
+            any_rest = any_rest || t_next > 0;
+            ++targets;
+        }
+        if (targets == 0) continue;
+        rest_recorded[g & 3] = false;
+        if (any_rest) {  // the panels are final: the side stream may start on the rows above the next group
+            if (cudaEventRecord(lane->panel[g & 3], st) != cudaSuccess || cudaStreamWaitEvent(lane->stream, lane->panel[g & 3], 0) != cudaSuccess)
+                return G2D_ERR_CUDA;
+            const int status = launch_syrk_tc(targets, rest, lane->stream);
+            if (status != G2D_OK) return status;
+            if (cudaEventRecord(lane->rest[g & 3], lane->stream) != cudaSuccess) return G2D_ERR_CUDA;
+        }
+        if (!wait_rest(g + 1)) return G2D_ERR_CUDA;
+        const int status = launch_syrk_tc(targets, next, st);
+        if (status != G2D_OK) return status;
+        rest_recorded[g & 3] = any_rest;
     }
     // everything the side stream did joins the caller's stream before the inverse starts
     for (int k = 0; k < 4; ++k)
@@ -490,7 +577,8 @@ using namespace g2d;
 static size_t ldl_bytes(int dtype, int64_t n) {
     const size_t elem = dtype == G2D_F32 ? 4 : 8;
     const size_t nb = (size_t)ceil_div(n, FB);
-    const size_t planes = dtype == G2D_F32 ? 6 * (size_t)n * n : 0;  // operand planes of the tensor-core triangular inverse
+    // float: six operand planes of the tensor-core triangular inverse and two pairs of transposed split panels
+    const size_t planes = dtype == G2D_F32 ? 6 * (size_t)n * n + 4 * (size_t)n * GROUP * FB : 0;
     return ((nb * FB * FB + (size_t)n * FB + (size_t)n * n + planes) * elem + 255) & ~(size_t)255;
 }
 

@@ -1,4 +1,5 @@
-// Triangular inverse of the factor preparation on the tensor cores (float only).
+// The two bulk products of the factor preparation on the tensor cores (float only): the trailing update of the
+// blocked Cholesky factorization (second half of this file) and the triangular inverse.
 //
 // The inverse Lf = T^{-1} of the lower triangular Cholesky factor is built by doubling: at level b every aligned pair
 // of finished b x b diagonal blocks [A^{-1} 0; . B^{-1}] of Lf is completed by X = -B^{-1} (C A^{-1}) with
@@ -11,6 +12,8 @@
 // epilogue), and one plane pair whose lower triangle holds T and whose upper triangle receives W^T.
 // Same pipeline as the macro updates of the sweep: one warp issues TMA loads into a three-stage ring, one warp
 // issues the MMAs, four warps read the accumulator and store; every wait is bounded.
+#include <cstring>
+
 #include "g2d_tc.cuh"
 
 namespace g2d {
@@ -31,9 +34,7 @@ constexpr uint32_t TRINV_TMEM_COLS = 128;
 
 __global__ void __launch_bounds__(TC_THREADS) trinv_tc_kernel(const __grid_constant__ TrinvJob job) {
     extern __shared__ unsigned char tc_smem_raw[];
-    __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], accum_bar;
-    __shared__ uint32_t tmem_slot;
-    __shared__ int failed;
+    __shared__ __align__(8) TcRing ring;
     const int z = (int)blockIdx.x >= job.pairs ? 1 : 0;
     const int64_t pair = (int64_t)blockIdx.x - (int64_t)z * job.pairs;
     const FactorPlanes P = z ? job.p[1] : job.p[0];
@@ -66,64 +67,22 @@ __global__ void __launch_bounds__(TC_THREADS) trinv_tc_kernel(const __grid_const
 
     const uint32_t smem_base = (smem_u32(tc_smem_raw) + 1023u) & ~1023u;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) {
-            mbar_init(&full_bar[s], 1);
-            mbar_init(&empty_bar[s], 1);
-        }
-        mbar_init(&accum_bar, 1);
-        failed = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(TRINV_TMEM_COLS) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const uint32_t tmem = tmem_slot;
-
+    const uint32_t tmem = tc_ring_setup(ring, TRINV_TMEM_COLS);
     if (warp == 0) {
-        if (lane == 0) {
-            for (int ch = 0; ch < chunks; ++ch) {
-                const int stage = ch % STAGES, round = ch / STAGES;
-                if (round > 0 && !mbar_wait(&empty_bar[stage], (round - 1) & 1)) { failed = 1; break; }
+        if (lane == 0)
+            tc_ring_produce(ring, smem_base, chunks, [&](int ch, uint32_t dst, uint64_t *bar) {
                 const int k = (int)(k_lo + (int64_t)ch * KC);
-                const uint32_t dst = smem_base + stage * STAGE_BYTES;
-                mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
-                tma_load_2d(dst, a_hi, k, (int)m0, &full_bar[stage]);
-                tma_load_2d(dst + TILE_BYTES, a_lo, k, (int)m0, &full_bar[stage]);
-                tma_load_2d(dst + 2 * TILE_BYTES, &maps->tw_hi, k, (int)n0, &full_bar[stage]);
-                tma_load_2d(dst + 3 * TILE_BYTES, &maps->tw_lo, k, (int)n0, &full_bar[stage]);
-            }
-        }
+                tma_load_2d(dst, a_hi, k, (int)m0, bar);
+                tma_load_2d(dst + TILE_BYTES, a_lo, k, (int)m0, bar);
+                tma_load_2d(dst + 2 * TILE_BYTES, &maps->tw_hi, k, (int)n0, bar);
+                tma_load_2d(dst + 3 * TILE_BYTES, &maps->tw_lo, k, (int)n0, bar);
+            });
     } else if (warp == 1) {
-        if (lane == 0) {
-            for (int ch = 0; ch < chunks; ++ch) {
-                const int stage = ch % STAGES, round = ch / STAGES;
-                if (!mbar_wait(&full_bar[stage], round & 1)) { failed = 1; break; }
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t s_a_hi = smem_base + stage * STAGE_BYTES, s_a_lo = s_a_hi + TILE_BYTES, s_b_hi = s_a_hi + 2 * TILE_BYTES,
-                               s_b_lo = s_a_hi + 3 * TILE_BYTES;
-#pragma unroll
-                for (int ks = 0; ks < KC / 8; ++ks) {
-                    const uint32_t off = ks * 32;  // 8 tf32 values = 32 bytes along the swizzled row
-                    umma_tf32(tmem, umma_desc(s_a_hi + off), umma_desc(s_b_hi + off), IDESC, (ch == 0 && ks == 0) ? 0u : 1u);
-                    umma_tf32(tmem, umma_desc(s_a_lo + off), umma_desc(s_b_hi + off), IDESC, 1u);
-                    umma_tf32(tmem, umma_desc(s_a_hi + off), umma_desc(s_b_lo + off), IDESC, 1u);
-                }
-                umma_commit(&empty_bar[stage]);  // arrives when the MMAs above have read the stage
-            }
-            umma_commit(&accum_bar);             // arrives when every MMA issued so far has completed
-        }
+        if (lane == 0) tc_ring_mma(ring, smem_base, tmem, chunks);
     } else {
         // epilogue warps: lanes 32 q .. 32 q + 31 of tensor memory, q = warp % 4; one accumulator row per thread
         const int q = warp & 3;
-        const bool ok = mbar_wait(&accum_bar, 0);
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (!ok) failed = 1;
-        const bool go = __all_sync(0xffffffffu, ok && !failed);  // warp-uniform: the tensor-memory loads are warp-wide
+        const bool go = tc_ring_accumulator_ready(ring);
         if (go) {
             const int64_t gi = m0 + q * 32 + lane;
             for (int cb = 0; cb < MT / 32; ++cb) {
@@ -172,16 +131,7 @@ __global__ void __launch_bounds__(TC_THREADS) trinv_tc_kernel(const __grid_const
             }
         }
     }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    if (warp == 1) {
-        if (failed) {
-            // give outstanding loads and MMAs a bounded chance to land before the memory they target is released
-            if (lane == 0) mbar_wait(&accum_bar, 0);
-            __syncwarp();
-        }
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TRINV_TMEM_COLS) : "memory");
-    }
+    const bool failed = tc_ring_teardown(ring, tmem, TRINV_TMEM_COLS);
     if (threadIdx.x == 0 && failed && P.flag) atomicExch(P.flag, -1);
 }
 
@@ -248,6 +198,114 @@ int launch_trinv_tc(int count, const FactorPlanes *problems, cudaStream_t stream
         }
     }
     return G2D_OK;
+}
+
+// ---- trailing update of the blocked Cholesky factorization ----
+// After a group of four 64-row block rows [o, o + kw) is factored, everything above it receives
+//     a[r][c] -= sum_{k < kw} a[o + k][r] a[o + k][c],      c <= r < o,
+// one 128 x 128 tile per CTA.  Both operands are the same K-major planes pt[r][k] = a[o + k][r] (hi and lo), which
+// the panel kernel writes as it finishes a block row.  One CTA owns each target entry and no other kernel touches the
+// targets meanwhile, so the result does not depend on scheduling.
+struct SyrkJob {
+    CUtensorMap hi[2], lo[2];
+    float *a[2];
+    int64_t n[2];
+    int t_lo[2], t_hi[2];  // target tile rows [t_lo, t_hi), with every tile column up to the diagonal
+    int chunks[2];         // ceil(kw / 32)
+    int *flag[2];
+};
+
+__global__ void __launch_bounds__(TC_THREADS) syrk_tc_kernel(const __grid_constant__ SyrkJob job) {
+    extern __shared__ unsigned char tc_smem_raw[];
+    __shared__ __align__(8) TcRing ring;
+    const int z = blockIdx.y;
+    const int t_lo = z ? job.t_lo[1] : job.t_lo[0], t_hi = z ? job.t_hi[1] : job.t_hi[0];
+    const int64_t first = (int64_t)t_lo * (t_lo + 1) / 2, count = (int64_t)t_hi * (t_hi + 1) / 2 - first;
+    if ((int64_t)blockIdx.x >= count) return;
+    const int64_t lin = first + blockIdx.x;
+    int I2 = (int)((sqrt(8.0 * (double)lin + 1.0) - 1.0) / 2.0);
+    while ((int64_t)(I2 + 1) * (I2 + 2) / 2 <= lin) ++I2;
+    while ((int64_t)I2 * (I2 + 1) / 2 > lin) --I2;
+    const int J2 = (int)(lin - (int64_t)I2 * (I2 + 1) / 2);
+    const CUtensorMap *hi = z ? &job.hi[1] : &job.hi[0], *lo = z ? &job.lo[1] : &job.lo[0];
+    float *const a = z ? job.a[1] : job.a[0];
+    const int64_t n = z ? job.n[1] : job.n[0];
+    const int chunks = z ? job.chunks[1] : job.chunks[0];
+    int *const flag = z ? job.flag[1] : job.flag[0];
+    const int i0 = I2 * MT, j0 = J2 * MT;
+
+    const uint32_t smem_base = (smem_u32(tc_smem_raw) + 1023u) & ~1023u;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t tmem = tc_ring_setup(ring, TRINV_TMEM_COLS);
+    if (warp == 0) {
+        if (lane == 0)
+            tc_ring_produce(ring, smem_base, chunks, [&](int ch, uint32_t dst, uint64_t *bar) {
+                tma_load_2d(dst, hi, ch * KC, i0, bar);
+                tma_load_2d(dst + TILE_BYTES, lo, ch * KC, i0, bar);
+                tma_load_2d(dst + 2 * TILE_BYTES, hi, ch * KC, j0, bar);
+                tma_load_2d(dst + 3 * TILE_BYTES, lo, ch * KC, j0, bar);
+            });
+    } else if (warp == 1) {
+        if (lane == 0) tc_ring_mma(ring, smem_base, tmem, chunks);
+    } else {
+        const int q = warp & 3;
+        const bool go = tc_ring_accumulator_ready(ring);
+        if (go) {
+            const int64_t gi = (int64_t)i0 + q * 32 + lane;  // always a row of the matrix: the targets lie above the group
+            for (int cb = 0; cb < MT / 32; ++cb) {
+                uint32_t v[32];
+                tmem_load_32(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(cb * 32), v);
+                const int64_t gj0 = (int64_t)j0 + cb * 32;
+                float *dst = a + gi * n + gj0;
+#pragma unroll
+                for (int x = 0; x < 32; x += 4) {
+                    if (gj0 + x <= gi) {  // groups that start right of the diagonal are never read
+                        asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + x), "f"(-__uint_as_float(v[x])),
+                                     "f"(-__uint_as_float(v[x + 1])), "f"(-__uint_as_float(v[x + 2])), "f"(-__uint_as_float(v[x + 3]))
+                                     : "memory");
+                    }
+                }
+            }
+        }
+    }
+    const bool failed = tc_ring_teardown(ring, tmem, TRINV_TMEM_COLS);
+    if (threadIdx.x == 0 && failed && flag) atomicExch(flag, -1);
+}
+
+bool syrk_tc_maps(SyrkTcMaps *maps, const float *pt_hi, const float *pt_lo, int64_t n) {
+    static_assert(sizeof(maps->hi) == sizeof(CUtensorMap), "opaque tensor-map storage has the wrong size");
+    return make_map(reinterpret_cast<CUtensorMap *>(maps->hi), pt_hi, n, SYRK_TC_K) &&
+           make_map(reinterpret_cast<CUtensorMap *>(maps->lo), pt_lo, n, SYRK_TC_K);
+}
+
+int launch_syrk_tc(int count, const SyrkTcTarget *targets, cudaStream_t stream) {
+    static bool configured[64] = {};
+    const size_t smem = (size_t)STAGES * STAGE_BYTES + 1024;
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return G2D_ERR_CUDA;
+    if (!configured[device]) {
+        if (cudaFuncSetAttribute(syrk_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return G2D_ERR_CUDA;
+        configured[device] = true;
+    }
+    SyrkJob job;
+    int64_t most = 0;
+    for (int z = 0; z < 2; ++z) {
+        const SyrkTcTarget &t = targets[z < count ? z : 0];
+        memcpy(&job.hi[z], t.maps->hi, sizeof(CUtensorMap));
+        memcpy(&job.lo[z], t.maps->lo, sizeof(CUtensorMap));
+        job.a[z] = t.a;
+        job.n[z] = t.n;
+        job.t_lo[z] = t.t_lo;
+        job.t_hi[z] = t.t_hi;
+        job.chunks[z] = (t.kw + KC - 1) / KC;
+        job.flag[z] = t.flag;
+        const int64_t tiles = (int64_t)t.t_hi * (t.t_hi + 1) / 2 - (int64_t)t.t_lo * (t.t_lo + 1) / 2;
+        most = tiles > most ? tiles : most;
+    }
+    if (most <= 0) return G2D_OK;
+    if (most > 0x7fffffff) return G2D_ERR_TOO_LARGE;
+    syrk_tc_kernel<<<dim3((unsigned)most, count), TC_THREADS, smem, stream>>>(job);
+    return check_launch();
 }
 
 }  // namespace g2d

@@ -72,15 +72,6 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
 // D fp32, A and B tf32, both K-major, M = 128, N = 128
 constexpr uint32_t IDESC = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(MT >> 3) << 17) | ((uint32_t)(MT >> 4) << 24);
 
-// fp32 -> tf32 hi (round to nearest) and the fp32 remainder: a = hi + lo exactly, and hi*hi' + lo*hi' + hi*lo' recovers
-// the fp32 product to about 2^-21 relative
-__device__ __forceinline__ void split_tf32(float a, float &hi, float &lo) {
-    uint32_t h;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(a));
-    hi = __uint_as_float(h);
-    lo = a - hi;
-}
-
 // 32 consecutive accumulator columns of this warp's 32 tensor-memory lanes (one row per thread)
 __device__ __forceinline__ void tmem_load_32(uint32_t taddr, uint32_t (&v)[32]) {
     asm volatile(
@@ -94,6 +85,95 @@ __device__ __forceinline__ void tmem_load_32(uint32_t taddr, uint32_t (&v)[32]) 
         : "r"(taddr)
         : "memory");
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// ---- one-accumulator pipeline: C[128 x 128] = sum over k chunks of A[128 x 32] B[128 x 32]^T, 3xTF32 ----
+// Shared state of a CTA of TC_THREADS threads: warp 0 loads, warp 1 issues the MMAs, warps 2-5 read the accumulator.
+struct TcRing {
+    uint64_t full[STAGES], empty[STAGES], accum;
+    uint32_t tmem_slot;
+    int failed;
+};
+
+// All threads: barriers, tensor-memory allocation of `cols` columns (by warp 1); returns the accumulator's address.
+__device__ __forceinline__ uint32_t tc_ring_setup(TcRing &ring, uint32_t cols) {
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&ring.full[s], 1);
+            mbar_init(&ring.empty[s], 1);
+        }
+        mbar_init(&ring.accum, 1);
+        ring.failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if ((threadIdx.x >> 5) == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ring.tmem_slot)), "r"(cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    return ring.tmem_slot;
+}
+
+// One thread: for every chunk, wait for its stage to be free and call load(chunk, destination, barrier), which must
+// issue TMA loads of STAGE_BYTES in total (A_hi, A_lo, B_hi, B_lo tiles, TILE_BYTES apart).
+template <typename Load>
+__device__ __forceinline__ void tc_ring_produce(TcRing &ring, uint32_t smem_base, int chunks, Load load) {
+    for (int ch = 0; ch < chunks; ++ch) {
+        const int stage = ch % STAGES, round = ch / STAGES;
+        if (round > 0 && !mbar_wait(&ring.empty[stage], (round - 1) & 1)) {
+            ring.failed = 1;
+            break;
+        }
+        mbar_expect_tx(&ring.full[stage], STAGE_BYTES);
+        load(ch, smem_base + stage * STAGE_BYTES, &ring.full[stage]);
+    }
+}
+
+// One thread: the MMAs of every chunk into the accumulator at `tmem`, then the commit that the epilogue waits for.
+__device__ __forceinline__ void tc_ring_mma(TcRing &ring, uint32_t smem_base, uint32_t tmem, int chunks) {
+    for (int ch = 0; ch < chunks; ++ch) {
+        const int stage = ch % STAGES, round = ch / STAGES;
+        if (!mbar_wait(&ring.full[stage], round & 1)) {
+            ring.failed = 1;
+            break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a_hi = smem_base + stage * STAGE_BYTES, a_lo = a_hi + TILE_BYTES, b_hi = a_hi + 2 * TILE_BYTES, b_lo = a_hi + 3 * TILE_BYTES;
+#pragma unroll
+        for (int ks = 0; ks < KC / 8; ++ks) {
+            const uint32_t off = ks * 32;  // 8 tf32 values = 32 bytes along the swizzled row
+            umma_tf32(tmem, umma_desc(a_hi + off), umma_desc(b_hi + off), IDESC, (ch == 0 && ks == 0) ? 0u : 1u);
+            umma_tf32(tmem, umma_desc(a_lo + off), umma_desc(b_hi + off), IDESC, 1u);
+            umma_tf32(tmem, umma_desc(a_hi + off), umma_desc(b_lo + off), IDESC, 1u);
+        }
+        umma_commit(&ring.empty[stage]);  // arrives when the MMAs above have read the stage
+    }
+    umma_commit(&ring.accum);             // arrives when every MMA issued so far has completed
+}
+
+// Epilogue warps: wait for the accumulator; false (for the whole warp) if any wait of the CTA ran out.
+__device__ __forceinline__ bool tc_ring_accumulator_ready(TcRing &ring) {
+    const bool ok = mbar_wait(&ring.accum, 0);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (!ok) ring.failed = 1;
+    return __all_sync(0xffffffffu, ok && !ring.failed);  // warp-uniform: the tensor-memory loads are warp-wide
+}
+
+// All threads: release tensor memory; returns whether a wait ran out (meaningful in every thread).
+__device__ __forceinline__ bool tc_ring_teardown(TcRing &ring, uint32_t tmem, uint32_t cols) {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if ((threadIdx.x >> 5) == 1) {
+        if (ring.failed) {
+            // give outstanding loads and MMAs a bounded chance to land before the memory they target is released
+            if ((threadIdx.x & 31) == 0) mbar_wait(&ring.accum, 0);
+            __syncwarp();
+        }
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(cols) : "memory");
+    }
+    return ring.failed != 0;
 }
 
 // ---- host side: tensor maps ----
