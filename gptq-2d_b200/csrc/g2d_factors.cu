@@ -102,15 +102,20 @@ __device__ __forceinline__ void zero_acc(F (&acc)[8][8]) {
 }
 
 // ---- step 1a: factor the diagonal block kb (bs x bs), M_kk = T_kk^T T_kk, and invert T_kk ----
-// One CTA of 16 x 16 threads; thread (ty, tx) owns the entries (ty + 16 a, tx + 16 b).  Step j (last row first)
-// subtracts row j's outer product, scaled by 1 / pivot, from the leading j x j block and emits row j of T; the
-// unscaled row j is never written again, so one barrier per step is enough.
+// One CTA of 16 x 16 threads; thread (ty, tx) keeps the entries (ty + 16 a, tx + 16 b) of the (symmetric) working
+// block in registers.  Step j (last row first): the owners of row j publish it, then everyone subtracts row j's outer
+// product, scaled by 1 / pivot, from its part of the leading j x j block.  Row j is never touched again, the rows
+// alternate between two buffers, so one barrier per step is enough.  Rows scaled by 1 / sqrt(pivot) are the factor.
 template <typename F>
 __global__ void __launch_bounds__(256) ldl_diag_kernel(LdlBatch<F> B, int step_down) {
     LDL_PROBLEM(blockIdx.y)
     F *const tinv = Q.tinv;
     int *const flag = Q.flag;
-    __shared__ F S[FB][FB + 1];   // working block (kept symmetric); row j is final, unscaled, after step j
+    __shared__ F S[FB][FB + 1];   // the block as loaded (lower triangle), later T in the lower and V^T in the upper triangle
+    __shared__ F rowbuf[2][FB];   // published rows of the even and odd steps
+    __shared__ F piv[FB];         // pivots
+    __shared__ F Vd[FB];          // diagonal of the inverse
+    __shared__ F Wt[FB * FB / 4]; // intermediate product of a doubling level
     __shared__ int bad;
     const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
     const int64_t o = (int64_t)kb * FB;
@@ -119,61 +124,94 @@ __global__ void __launch_bounds__(256) ldl_diag_kernel(LdlBatch<F> B, int step_d
     for (int idx = tid; idx < FB * FB; idx += 256) {
         const int r = idx / FB, c = idx % FB;
         F v = (F)0;
-        if (r < bs && c < bs) v = r >= c ? a[(o + r) * n + o + c] : a[(o + c) * n + o + r];
+        if (r < bs && c <= r) v = a[(o + r) * n + o + c];
+        if (r >= bs && r == c) v = (F)1;  // identity beyond a ragged block: its steps change nothing and the inverse stays finite
         S[r][c] = v;
-        tinv[(int64_t)kb * FB * FB + idx] = (F)0;
     }
     __syncthreads();
-    for (int j = bs - 1; j >= 0; --j) {
-        const F d2 = S[j][j];
-        if (tid == 0 && !(d2 > (F)0)) bad = j + 1;
+    F reg[FB / 16][FB / 16];
+#pragma unroll
+    for (int aa = 0; aa < FB / 16; ++aa)
+#pragma unroll
+        for (int bb = 0; bb < FB / 16; ++bb) {
+            const int i1 = ty + 16 * aa, i2 = tx + 16 * bb;
+            reg[aa][bb] = i1 >= i2 ? S[i1][i2] : S[i2][i1];
+        }
+#pragma unroll
+    for (int j = FB - 1; j >= 0; --j) {
+        if (ty == (j & 15)) {
+#pragma unroll
+            for (int bb = 0; bb < FB / 16; ++bb) rowbuf[j & 1][tx + 16 * bb] = reg[j / 16][bb];
+        }
+        __syncthreads();
+        const F d2 = rowbuf[j & 1][j];
+        if (tid == 0) {
+            piv[j] = d2;
+            if (j < bs && !(d2 > (F)0)) bad = j + 1;
+        }
         const F inv_d2 = (F)1 / d2;
+        F rb[FB / 16];
+#pragma unroll
+        for (int bb = 0; bb < FB / 16; ++bb) rb[bb] = rowbuf[j & 1][tx + 16 * bb];
 #pragma unroll
         for (int aa = 0; aa < FB / 16; ++aa) {
-            const int i1 = ty + 16 * aa;
-            if (i1 < j) {
-                const F f = S[j][i1] * inv_d2;
+            if (16 * aa < j) {  // known at compile time: later blocks of rows are final already
+                const int i1 = ty + 16 * aa;
+                const F f = rowbuf[j & 1][i1] * inv_d2;
 #pragma unroll
-                for (int bb = 0; bb < FB / 16; ++bb) {
-                    const int i2 = tx + 16 * bb;
-                    if (i2 < j) S[i1][i2] -= f * S[j][i2];
-                }
+                for (int bb = 0; bb < FB / 16; ++bb)
+                    if (16 * bb < j && i1 < j && tx + 16 * bb < j) reg[aa][bb] -= f * rb[bb];
             }
-        }
-        __syncthreads();
-    }
-    // rows scaled by 1 / sqrt(pivot) are the factor: T[j][i] = S[j][i] / sqrt(S[j][j]), T[j][j] = sqrt(S[j][j])
-    {
-        F vals[FB * FB / 256];
-#pragma unroll
-        for (int t = 0; t < FB * FB / 256; ++t) {
-            const int idx = t * 256 + tid, r = idx / FB, c = idx % FB;
-            const F root = sqrt(S[r][r]);
-            vals[t] = r == c ? root : (c < r ? S[r][c] / root : (F)0);
-        }
-        __syncthreads();
-#pragma unroll
-        for (int t = 0; t < FB * FB / 256; ++t) {
-            const int idx = t * 256 + tid;
-            S[idx / FB][idx % FB] = vals[t];
-        }
-        __syncthreads();
-    }
-    // inverse V of the lower triangular T_kk: thread c solves T x = e_c by forward substitution.  The strict upper
-    // triangle of S is free, so column c of V is kept as row c there: V[r][c] = S[c][r] for r > c.
-    if (tid < bs) {
-        const int c = tid;
-        const F vcc = (F)1 / S[c][c];
-        for (int r = c + 1; r < bs; ++r) {
-            F acc = -S[r][c] * vcc;
-            for (int k = c + 1; k < r; ++k) acc -= S[r][k] * S[c][k];
-            S[c][r] = acc / S[r][r];
         }
     }
     __syncthreads();
+    if (tid < FB) Vd[tid] = (F)1 / sqrt(piv[tid]);  // 1 / T[r][r]
+    __syncthreads();
+#pragma unroll
+    for (int aa = 0; aa < FB / 16; ++aa)
+#pragma unroll
+        for (int bb = 0; bb < FB / 16; ++bb) {
+            const int i1 = ty + 16 * aa, i2 = tx + 16 * bb;
+            if (i1 > i2) S[i1][i2] = reg[aa][bb] * Vd[i1];
+            if (i1 == i2) S[i1][i1] = sqrt(piv[i1]);
+        }
+    __syncthreads();
+    // Inverse V of the lower triangular T_kk.  The strict upper triangle of S is free, so V is kept transposed there
+    // (V[r][c] = S[c][r] for r > c) with its diagonal in Vd.  First the four 16 x 16 diagonal blocks by forward
+    // substitution (one thread per column), then two doubling levels, each completing pairs of finished blocks
+    // [A^{-1} 0; X B^{-1}] with X = -B^{-1} (C A^{-1}) as two small products over all threads.
+    if (tid < FB) {
+        const int c = tid, end = (tid & ~15) + 16;
+        for (int r = c + 1; r < end; ++r) {
+            F acc = -S[r][c] * Vd[c];
+#pragma unroll 4
+            for (int k = c + 1; k < r; ++k) acc -= S[r][k] * S[c][k];
+            S[c][r] = acc * Vd[r];
+        }
+    }
+    __syncthreads();
+    for (int b = 16; b < FB; b *= 2) {
+        const int outputs = (FB / (2 * b)) * b * b;
+        for (int idx = tid; idx < outputs; idx += 256) {  // W = C A^{-1}, C = T[second half rows][first half columns]
+            const int p = idx / (b * b), i = (idx / b) % b, j = idx % b, r0 = p * 2 * b, r1 = r0 + b;
+            F acc = S[r1 + i][r0 + j] * Vd[r0 + j];
+#pragma unroll 4
+            for (int k = j + 1; k < b; ++k) acc += S[r1 + i][r0 + k] * S[r0 + j][r0 + k];
+            Wt[idx] = acc;
+        }
+        __syncthreads();
+        for (int idx = tid; idx < outputs; idx += 256) {  // X = -B^{-1} W, stored transposed
+            const int p = idx / (b * b), i = (idx / b) % b, j = idx % b, r0 = p * 2 * b, r1 = r0 + b;
+            F acc = Vd[r1 + i] * Wt[idx];
+#pragma unroll 4
+            for (int k = 0; k < i; ++k) acc += S[r1 + k][r1 + i] * Wt[(p * b + k) * b + j];
+            S[r0 + j][r1 + i] = -acc;
+        }
+        __syncthreads();
+    }
     for (int idx = tid; idx < FB * FB; idx += 256) {
         const int r = idx / FB, c = idx % FB;
-        if (r < bs && c < bs && r >= c) tinv[(int64_t)kb * FB * FB + idx] = r == c ? (F)1 / S[r][r] : S[c][r];
+        tinv[(int64_t)kb * FB * FB + idx] = (r < bs && c < bs && r >= c) ? (r == c ? Vd[r] : S[c][r]) : (F)0;
     }
     for (int idx = tid; idx < FB * FB; idx += 256) {
         const int r = idx / FB, c = idx % FB;
