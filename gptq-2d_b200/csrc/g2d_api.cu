@@ -3,6 +3,7 @@
 
 #include "g2d_common.cuh"
 
+#include <mutex>
 #include <vector>
 
 namespace g2d {
@@ -19,6 +20,10 @@ struct LaunchTimer {
     std::vector<Item> items;
     cudaStream_t stream;
     bool ok = true;
+    void begin_on(int kind, cudaStream_t on) {  // a launch on another stream than the previous one (the null stream included)
+        stream = on;
+        begin(kind);
+    }
     void begin(int kind) {
         Item it{};
         it.kind = kind;
@@ -60,7 +65,7 @@ inline bool tc_eligible(const g2d_sweep_desc *d) {
 }
 inline size_t tc_extra_bytes(const g2d_sweep_desc *d) {
     const size_t mn = align256(4 * (size_t)d->m * d->n), mm = align256(4 * (size_t)d->m * d->m), nn = align256(4 * (size_t)d->n * d->n);
-    return 256 + 4 * mn + 2 * mm + 2 * nn;
+    return 256 + 4 * mn + 2 * mm + 2 * nn + 2 * mn;  // flag, E^T and C splits, L and U^T splits, far planes of the pipelined schedule
 }
 
 int check_sweep(const g2d_sweep_desc *d) {
@@ -136,6 +141,118 @@ int sweep_macro(const g2d_sweep_desc *d, SweepArgs<F> &a, BandArgs<F> &b64, cuda
     return G2D_OK;
 }
 
+// Side streams and events of the pipelined schedule.  Calls take lanes round robin, so sweeps that a caller runs
+// concurrently on several streams do not share one.  Created on first use per device and kept.
+struct PipeLane {
+    cudaStream_t tiles = nullptr, near = nullptr, far = nullptr;  // in falling priority
+    cudaEvent_t swept[8] = {}, near_done[8] = {}, far_done[4] = {}, fork = nullptr, join = nullptr;
+};
+PipeLane *acquire_pipe_lane() {
+    static std::mutex mutex;
+    static PipeLane lanes[64][4];
+    static unsigned next[64] = {};
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return nullptr;
+    std::lock_guard<std::mutex> lock(mutex);
+    PipeLane *lane = &lanes[device][next[device]++ & 3];
+    if (!lane->near) {
+        // the tile launches are the critical path: their CTAs go first wherever a slot frees up, then the near updates
+        int least = 0, greatest = 0;
+        if (cudaDeviceGetStreamPriorityRange(&least, &greatest) != cudaSuccess) return nullptr;
+        const int middle = greatest + 1 <= least ? greatest + 1 : least;
+        if (cudaStreamCreateWithPriority(&lane->tiles, cudaStreamNonBlocking, greatest) != cudaSuccess ||
+            cudaStreamCreateWithPriority(&lane->near, cudaStreamNonBlocking, middle) != cudaSuccess ||
+            cudaStreamCreateWithPriority(&lane->far, cudaStreamNonBlocking, least) != cudaSuccess ||
+            cudaEventCreateWithFlags(&lane->fork, cudaEventDisableTiming) != cudaSuccess ||
+            cudaEventCreateWithFlags(&lane->join, cudaEventDisableTiming) != cudaSuccess)
+            return nullptr;
+        for (int k = 0; k < 8; ++k)
+            if (cudaEventCreateWithFlags(&lane->swept[k], cudaEventDisableTiming) != cudaSuccess ||
+                cudaEventCreateWithFlags(&lane->near_done[k], cudaEventDisableTiming) != cudaSuccess)
+                return nullptr;
+        for (int k = 0; k < 4; ++k)
+            if (cudaEventCreateWithFlags(&lane->far_done[k], cudaEventDisableTiming) != cudaSuccess) return nullptr;
+    }
+    return lane;
+}
+
+constexpr int kFarLagMacro = 2;  // a far update reaches the macro anti-diagonals from this many past its group's end
+
+// Pipelined schedule (float, tensor cores): one tile launch per tile anti-diagonal, and the feedback between tiles
+// carried by three mechanisms with growing lag, so that only the tile launches remain on the critical path:
+//   * a tile applies the feedback of its two neighbours of the previous anti-diagonal itself, as it loads;
+//   * near update of the tile anti-diagonal s (its tiles as sources, targets from s + 2 on), on a side stream,
+//     concurrent with the tile launch of s + 1;
+//   * far update of a group of macro anti-diagonals (128 x 128 macro tiles = 2 x 2 tiles; rank 512 by default), on a
+//     second side stream, into planes of its own that a tile adds when it loads.  It reaches the macro anti-diagonals
+//     from kFarLagMacro past the group's end, which the tile launches get to four launches after the group's last
+//     tile; the near updates stop where the far update of their source's group starts.
+// The tile launches run on a stream of the library's own with the highest priority, the near updates below it, the far
+// updates lowest: a CTA slot that frees up goes to the critical path first.  Updates that share target planes are
+// ordered on one stream, so the additions have a fixed order.
+int sweep_pipelined(const g2d_sweep_desc *d, SweepArgs<float> &a, const TcPlanes &planes, float *yf, float *cf, cudaStream_t caller,
+                    LaunchTimer *timer, double *flops) {
+    PipeLane *lane = acquire_pipe_lane();
+    if (!lane) return G2D_ERR_CUDA;
+    // fork: everything the caller's stream holds so far comes first
+    cudaStream_t stream = lane->tiles;
+    if (cudaEventRecord(lane->fork, caller) != cudaSuccess || cudaStreamWaitEvent(stream, lane->fork, 0) != cudaSuccess) return G2D_ERR_CUDA;
+    BandTcMaps maps;
+    int status = band_tc_prepare(&maps, planes, d->m, d->n);
+    if (status != G2D_OK) return status;
+    a.yf = yf; a.cf = cf; a.neighbours = 1;
+    const int waves = a.nI + a.nJ - 1;
+    const int waves_macro = (int)(ceil_div(d->m, MACRO) + ceil_div(d->n, MACRO)) - 1;
+    const int outer = d->outer_tiles > 0 ? (d->outer_tiles + 1) / 2 : kDefaultOuterMacro;  // macro anti-diagonals per far update
+    int last_near = -1, last_far = -1;
+    for (int s = 0; s < waves; ++s) {
+        // what the tiles of s need: every near update up to s - 2, and the far update whose first targets they are
+        if (s >= 2 && last_near >= s - 2 && cudaStreamWaitEvent(stream, lane->near_done[(s - 2) & 7], 0) != cudaSuccess) return G2D_ERR_CUDA;
+        if (s % 2 == 0 && s / 2 - kFarLagMacro > 0 && (s / 2 - kFarLagMacro) % outer == 0) {
+            const int gf = (s / 2 - kFarLagMacro) / outer - 1;  // the group that ended kFarLagMacro macro anti-diagonals ago
+            if (last_far >= gf && cudaStreamWaitEvent(stream, lane->far_done[gf & 3], 0) != cudaSuccess) return G2D_ERR_CUDA;
+        }
+        if (timer) timer->begin_on(0, stream);
+        status = launch_tile_sweep<float>(a, s, stream);
+        if (timer) timer->end();
+        if (status != G2D_OK) return status;
+        const bool feeds_near = s + 2 <= waves - 1;
+        // the last tiles of the macro anti-diagonal W1 - 1 lie on the tile anti-diagonal 2 W1
+        const int W1 = s / 2;
+        const bool feeds_far = s % 2 == 0 && W1 > 0 && W1 % outer == 0 && W1 + kFarLagMacro <= waves_macro - 1;
+        if (!feeds_near && !feeds_far) continue;
+        if (cudaEventRecord(lane->swept[s & 7], stream) != cudaSuccess) return G2D_ERR_CUDA;
+        if (feeds_near) {
+            const int reach = ((s / 2) / outer + 1) * outer + kFarLagMacro;  // of the latest group that has a source tile here
+            const int t0 = s + 2, t1 = 2 * reach < waves - 1 ? 2 * reach : waves - 1;
+            if (cudaStreamWaitEvent(lane->near, lane->swept[s & 7], 0) != cudaSuccess) return G2D_ERR_CUDA;
+            if (timer) timer->begin_on(1, lane->near);
+            status = launch_band_tc(&maps, a.y, a.c, d->m, d->n, s, s + 1, t0, t1, outer, kFarLagMacro, planes.error_flag, lane->near);
+            if (timer) timer->end();
+            if (status != G2D_OK) return status;
+            if (cudaEventRecord(lane->near_done[s & 7], lane->near) != cudaSuccess) return G2D_ERR_CUDA;
+            last_near = s;
+        }
+        if (feeds_far) {
+            const int g = W1 / outer - 1;
+            if (cudaStreamWaitEvent(lane->far, lane->swept[s & 7], 0) != cudaSuccess) return G2D_ERR_CUDA;
+            if (timer) timer->begin_on(2, lane->far);
+            status = launch_macro_update_tc(planes, yf, cf, d->m, d->n, W1 - outer, W1, waves_macro, lane->far, W1 + kFarLagMacro, 2);
+            if (timer) timer->end();
+            if (status != G2D_OK) return status;
+            if (flops)
+                flops[2] += band_flops(d->m, d->n, W1 - outer, W1, waves_macro, MACRO) - band_flops(d->m, d->n, W1 - outer, W1, W1 + kFarLagMacro, MACRO);
+            if (cudaEventRecord(lane->far_done[g & 3], lane->far) != cudaSuccess) return G2D_ERR_CUDA;
+            last_far = g;
+        }
+    }
+    // join: what follows the call on the caller's stream follows everything the call did
+    if (last_near >= 0 && cudaStreamWaitEvent(stream, lane->near_done[last_near & 7], 0) != cudaSuccess) return G2D_ERR_CUDA;
+    if (last_far >= 0 && cudaStreamWaitEvent(stream, lane->far_done[last_far & 3], 0) != cudaSuccess) return G2D_ERR_CUDA;
+    if (cudaEventRecord(lane->join, stream) != cudaSuccess || cudaStreamWaitEvent(caller, lane->join, 0) != cudaSuccess) return G2D_ERR_CUDA;
+    return G2D_OK;
+}
+
 template <typename F>
 int sweep_fused(const g2d_sweep_desc *d, cudaStream_t stream, LaunchTimer *timer = nullptr, double *flops = nullptr) {
     const int64_t count = d->batch * d->m * d->n;
@@ -178,6 +295,13 @@ int sweep_fused(const g2d_sweep_desc *d, cudaStream_t stream, LaunchTimer *timer
         const int status = tc_prepare_operands((const float *)d->l, (const float *)d->u, d->m, d->n, planes, stream);
         if (status != G2D_OK) return status;
         a.et_hi = planes.et_hi; a.et_lo = planes.et_lo; a.c_hi = planes.c_hi; a.c_lo = planes.c_lo;
+        if constexpr (sizeof(F) == sizeof(float)) {
+            if (d->reserved == 3) {
+                float *yf = (float *)p, *cf = (float *)(p + mn);
+                if (cudaMemsetAsync(yf, 0, 2 * mn, stream) != cudaSuccess) return G2D_ERR_CUDA;
+                return sweep_pipelined(d, a, planes, yf, cf, stream, timer, flops);
+            }
+        }
         return sweep_macro<F>(d, a, b, stream, timer, flops, &planes);
     }
     if (d->reserved == 2) return sweep_macro<F>(d, a, b, stream, timer, flops, nullptr);

@@ -96,6 +96,10 @@ struct SweepArgs {
     // float, single matrix, tensor-core updates only (else null): tf32 hi / lo copies of the finished tiles,
     // E transposed ([n, m]) and the completed C ([m, n]), operands of the macro updates
     float *et_hi = nullptr, *et_lo = nullptr, *c_hi = nullptr, *c_lo = nullptr;
+    // pipelined schedule only (else null / 0): planes that collect the far feedback apart from Y and C, added when a
+    // tile is loaded, and the switch that makes a tile apply the feedback of its two nearest finished neighbours itself
+    const F *yf = nullptr, *cf = nullptr;
+    int neighbours = 0;
 };
 
 // fp32 -> tf32 hi (round to nearest) and the fp32 remainder: a = hi + lo exactly, and hi*hi' + lo*hi' + hi*lo' recovers
@@ -113,8 +117,19 @@ struct TcPlanes {
     float *l_hi, *l_lo, *ut_hi, *ut_lo;  // written once per sweep from L and U
     int *error_flag;                     // set when a bounded wait inside a kernel ran out
 };
+// Band updates between tiles on the tensor cores (pipelined schedule; see g2d_band_tc.cu): sources are the tile
+// anti-diagonals s0..s1-1, targets t0..t1 (t0 >= s1 + 1), feedback is added into the planes y (right) and c (down).
+// With outer_macro > 0 a target is left out when a far update on 128 x 128 macro tiles carries its source instead:
+// when its macro anti-diagonal is lag_macro or more past the end of the source's group of outer_macro macro anti-diagonals.
+struct BandTcMaps {
+    alignas(64) unsigned char bytes[8 * 128];  // tensor maps of the eight operand planes (opaque here)
+};
+int band_tc_prepare(BandTcMaps *maps, const TcPlanes &planes, int64_t m, int64_t n);
+int launch_band_tc(const BandTcMaps *maps, float *y, float *c, int64_t m, int64_t n, int s0, int s1, int t0, int t1, int outer_macro,
+                   int lag_macro, int *error_flag, cudaStream_t stream);
 int tc_prepare_operands(const float *l, const float *u, int64_t m, int64_t n, const TcPlanes &planes, cudaStream_t stream);
-int launch_macro_update_tc(const TcPlanes &planes, float *y, float *c, int64_t m, int64_t n, int s0, int s1, int s_end, cudaStream_t stream);
+int launch_macro_update_tc(const TcPlanes &planes, float *y, float *c, int64_t m, int64_t n, int s0, int s1, int s_end, cudaStream_t stream,
+                           int t_first = 0, int stages = 3);
 
 // One problem of the tensor-core triangular inverse of the factor preparation (all [n][n] float; see g2d_factors_tc.cu).
 struct FactorPlanes {

@@ -25,11 +25,12 @@ struct TcMaps {
     CUtensorMap et_hi, et_lo, ut_hi, ut_lo;  // B operands: [columns][k]
 };
 
+template <int NSTAGES>
 __global__ void __launch_bounds__(TC_THREADS) macro_update_tc_kernel(const __grid_constant__ TcMaps maps, float *y, float *c, int64_t m,
-                                                                     int64_t n, int nI2, int nJ2, int s0, int s1, int s_end,
+                                                                     int64_t n, int nI2, int nJ2, int s0, int s1, int t_first, int s_end,
                                                                      int raster, int *error_flag) {
     extern __shared__ unsigned char tc_smem_raw[];
-    __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], accum_bar;
+    __shared__ __align__(8) uint64_t full_bar[NSTAGES], empty_bar[NSTAGES], accum_bar;
     __shared__ uint32_t tmem_slot;
     __shared__ int failed;
     // Target macro tile.  With gridDim.y > 1, blockIdx.y selects the macro anti-diagonal and blockIdx.x the tile on it
@@ -37,7 +38,7 @@ __global__ void __launch_bounds__(TC_THREADS) macro_update_tc_kernel(const __gri
     // CTAs resident at one time cover a compact patch and share their L / C row strips and E^T / U^T column strips in L2.
     int I2, J2;
     if (raster == 0) {
-        const int W = s1 + (int)blockIdx.y;
+        const int W = t_first + (int)blockIdx.y;
         const int ti_lo = max(0, W - nJ2 + 1), ti_hi = min(W + 1, nI2);
         I2 = ti_lo + (int)blockIdx.x;
         if (W >= s_end || I2 >= ti_hi) return;
@@ -47,7 +48,7 @@ __global__ void __launch_bounds__(TC_THREADS) macro_update_tc_kernel(const __gri
         const int blk = (int)blockIdx.x / (RB_I * RB_J), within = (int)blockIdx.x % (RB_I * RB_J);
         I2 = (blk / blocks_j) * RB_I + within / RB_J;
         J2 = (blk % blocks_j) * RB_J + within % RB_J;
-        if (I2 >= nI2 || J2 >= nJ2 || I2 + J2 < s1 || I2 + J2 >= s_end) return;
+        if (I2 >= nI2 || J2 >= nJ2 || I2 + J2 < t_first || I2 + J2 >= s_end) return;
     }
     // source macro rows (down) and macro columns (right) of the band
     const int kd_lo = max(s0 - J2, 0), kd_hi = min(s1 - J2, I2);
@@ -60,7 +61,7 @@ __global__ void __launch_bounds__(TC_THREADS) macro_update_tc_kernel(const __gri
     const uint32_t smem_base = (smem_u32(tc_smem_raw) + 1023u) & ~1023u;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) {
+        for (int s = 0; s < NSTAGES; ++s) {
             mbar_init(&full_bar[s], 1);
             mbar_init(&empty_bar[s], 1);
         }
@@ -81,7 +82,7 @@ __global__ void __launch_bounds__(TC_THREADS) macro_update_tc_kernel(const __gri
     if (warp == 0) {
         if (lane == 0) {
             for (int ch = 0; ch < chunks; ++ch) {
-                const int stage = ch % STAGES, round = ch / STAGES;
+                const int stage = ch % NSTAGES, round = ch / NSTAGES;
                 if (round > 0 && !mbar_wait(&empty_bar[stage], (round - 1) & 1)) { failed = 1; break; }
                 const bool down = ch < chunks_d;
                 const int k = down ? kd_lo * MT + ch * KC : kr_lo * MT + (ch - chunks_d) * KC;
@@ -97,7 +98,7 @@ __global__ void __launch_bounds__(TC_THREADS) macro_update_tc_kernel(const __gri
         if (lane == 0) {
             bool ok = true;
             for (int ch = 0; ch < chunks && ok; ++ch) {
-                const int stage = ch % STAGES, round = ch / STAGES;
+                const int stage = ch % NSTAGES, round = ch / NSTAGES;
                 if (!mbar_wait(&full_bar[stage], round & 1)) { failed = 1; ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const bool down = ch < chunks_d;
@@ -218,13 +219,20 @@ int tc_prepare_operands(const float *l, const float *u, int64_t m, int64_t n, co
     return check_launch();
 }
 
-int launch_macro_update_tc(const TcPlanes &pl, float *y, float *c, int64_t m, int64_t n, int s0, int s1, int s_end, cudaStream_t stream) {
+// Sources: the macro anti-diagonals s0..s1-1; targets: t_first..s_end-1 (t_first >= s1).  `stages` 3 is the full pipeline
+// (one CTA per SM); 2 leaves room for a CTA of the tile sweep beside it (pipelined schedule).
+int launch_macro_update_tc(const TcPlanes &pl, float *y, float *c, int64_t m, int64_t n, int s0, int s1, int s_end, cudaStream_t stream,
+                           int t_first, int stages) {
     static bool configured[64] = {};
-    const size_t smem = (size_t)STAGES * STAGE_BYTES + 1024;
+    if (t_first < s1) t_first = s1;
+    const int depth = stages == 2 ? 2 : STAGES;
+    const size_t smem = (size_t)depth * STAGE_BYTES + 1024;
     int device = 0;
     if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return G2D_ERR_CUDA;
     if (!configured[device]) {
-        if (cudaFuncSetAttribute(macro_update_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return G2D_ERR_CUDA;
+        if (cudaFuncSetAttribute(macro_update_tc_kernel<STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, STAGES * STAGE_BYTES + 1024) != cudaSuccess ||
+            cudaFuncSetAttribute(macro_update_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * STAGE_BYTES + 1024) != cudaSuccess)
+            return G2D_ERR_CUDA;
         configured[device] = true;
     }
     TcMaps maps;
@@ -233,14 +241,17 @@ int launch_macro_update_tc(const TcPlanes &pl, float *y, float *c, int64_t m, in
         !make_map(&maps.ut_hi, pl.ut_hi, n, n) || !make_map(&maps.ut_lo, pl.ut_lo, n, n))
         return G2D_ERR_CUDA;
     const int nI2 = (int)ceil_div(m, MT), nJ2 = (int)ceil_div(n, MT);
-    if (s_end <= s1) return G2D_OK;
-    const int raster = s_end - s1 > 8 ? 1 : 0;
-    dim3 grid((unsigned)(nI2 < nJ2 ? nI2 : nJ2), (unsigned)(s_end - s1));
+    if (s_end <= t_first) return G2D_OK;
+    const int raster = s_end - t_first > 8 ? 1 : 0;
+    dim3 grid((unsigned)(nI2 < nJ2 ? nI2 : nJ2), (unsigned)(s_end - t_first));
     if (raster) {
         const int64_t blocks = ceil_div(nI2, RB_I) * ceil_div(nJ2, RB_J);
         grid = dim3((unsigned)(blocks * RB_I * RB_J), 1);
     }
-    macro_update_tc_kernel<<<grid, TC_THREADS, smem, stream>>>(maps, y, c, m, n, nI2, nJ2, s0, s1, s_end, raster, pl.error_flag);
+    if (depth == 2)
+        macro_update_tc_kernel<2><<<grid, TC_THREADS, smem, stream>>>(maps, y, c, m, n, nI2, nJ2, s0, s1, t_first, s_end, raster, pl.error_flag);
+    else
+        macro_update_tc_kernel<STAGES><<<grid, TC_THREADS, smem, stream>>>(maps, y, c, m, n, nI2, nJ2, s0, s1, t_first, s_end, raster, pl.error_flag);
     return check_launch();
 }
 

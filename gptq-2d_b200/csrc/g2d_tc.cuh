@@ -193,13 +193,13 @@ static EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
-// row-major fp32 matrix [rows][cols]; boxes of 128 rows x 32 columns, 128-byte swizzle, zero fill outside
-static bool make_map(CUtensorMap *map, const float *base, int64_t rows, int64_t cols) {
+// row-major fp32 matrix [rows][cols]; boxes of box_rows rows x 32 columns, 128-byte swizzle, zero fill outside
+static bool make_map(CUtensorMap *map, const float *base, int64_t rows, int64_t cols, int box_rows = MT) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return false;
     const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
     const cuuint64_t strides[1] = {(cuuint64_t)cols * sizeof(float)};
-    const cuuint32_t box[2] = {KC, MT};
+    const cuuint32_t box[2] = {KC, (cuuint32_t)box_rows};
     const cuuint32_t elem[2] = {1, 1};
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;

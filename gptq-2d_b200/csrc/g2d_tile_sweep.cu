@@ -81,6 +81,80 @@ __device__ __forceinline__ void mm16(F *__restrict__ D, const F *__restrict__ A,
     store4(D + (r + 1) * LD + c, d1);
 }
 
+// D[64 x 64, shared, row stride LD] += A[64 x 64] B[64 x 64], A and B row-major in global memory (leading dimensions
+// lda, ldb), for all TTH threads of the CTA: thread (ty, tx) forms the outputs of rows 8 ty .. 8 ty + 7 and columns
+// 4 tx .. 4 tx + 3 from k chunks of 16 staged in `stage` (2 x 16 x LD values).  Rows of A from `rows` on and columns
+// of B from `cols` on read as zero (ragged last tiles); `vec` promises whole, 16-byte aligned operands.
+template <typename F>
+__device__ __forceinline__ void tile_mm64(F *D, const F *__restrict__ A, int64_t lda, const F *__restrict__ B, int64_t ldb, int rows, int cols,
+                                          F *stage, int tid, bool vec) {
+    constexpr int KCH = 16;
+    F *As = stage, *Bs = stage + KCH * LD;  // As[kk][i], Bs[kk][j]
+    const int ty = tid >> 4, tx = tid & 15;
+    F acc[8][4];
+#pragma unroll
+    for (int x = 0; x < 8; ++x)
+#pragma unroll
+        for (int y = 0; y < 4; ++y) acc[x][y] = (F)0;
+    F ra[2][4], rb[2][4];
+    auto fetch = [&](int k0) {  // global -> registers; consumed one iteration later, so the latency hides behind the products
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+            const int idx = t * TTH + tid;
+            const int ar = idx >> 2, aq = (idx & 3) * 4;   // A chunk: 64 rows x 16 k
+            const int br = idx >> 4, bq = (idx & 15) * 4;  // B chunk: 16 k x 64 columns
+            if (vec) {
+                load4(A + ar * lda + k0 + aq, ra[t]);
+                load4(B + (k0 + br) * ldb + bq, rb[t]);
+            } else {
+#pragma unroll
+                for (int x = 0; x < 4; ++x) {
+                    ra[t][x] = ar < rows ? A[ar * lda + k0 + aq + x] : (F)0;
+                    rb[t][x] = bq + x < cols ? B[(k0 + br) * ldb + bq + x] : (F)0;
+                }
+            }
+        }
+    };
+    fetch(0);
+    for (int k0 = 0; k0 < TILE; k0 += KCH) {
+        __syncthreads();  // the previous chunk has been consumed
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+            const int idx = t * TTH + tid;
+            const int ar = idx >> 2, aq = (idx & 3) * 4, br = idx >> 4, bq = (idx & 15) * 4;
+#pragma unroll
+            for (int x = 0; x < 4; ++x) As[(aq + x) * LD + ar] = ra[t][x];
+            store4(Bs + br * LD + bq, rb[t]);
+        }
+        __syncthreads();
+        if (k0 + KCH < TILE) fetch(k0 + KCH);
+#pragma unroll
+        for (int kk = 0; kk < KCH; ++kk) {
+            F a0[4], a1[4], b[4];
+            load4(As + kk * LD + 8 * ty, a0);
+            load4(As + kk * LD + 8 * ty + 4, a1);
+            load4(Bs + kk * LD + 4 * tx, b);
+#pragma unroll
+            for (int y = 0; y < 4; ++y) {
+#pragma unroll
+                for (int x = 0; x < 4; ++x) {
+                    acc[x][y] += a0[x] * b[y];
+                    acc[4 + x][y] += a1[x] * b[y];
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int x = 0; x < 8; ++x) {
+        F d[4];
+        load4(D + (8 * ty + x) * LD + 4 * tx, d);
+#pragma unroll
+        for (int y = 0; y < 4; ++y) d[y] += acc[x][y];
+        store4(D + (8 * ty + x) * LD + 4 * tx, d);
+    }
+    __syncthreads();
+}
+
 template <typename F, int KIND>
 __global__ void __launch_bounds__(TTH) tile_sweep_kernel(SweepArgs<F> P, int S, int i_first, int i_step) {
     extern __shared__ __align__(16) unsigned char g2d_smem[];
@@ -105,6 +179,7 @@ __global__ void __launch_bounds__(TTH) tile_sweep_kernel(SweepArgs<F> P, int S, 
         const F *zg = KIND == G2D_Q_AFFINE ? P.zero + (P.zero_off ? P.zero_off[batch] : 0) : nullptr;
         const F *fg = KIND == G2D_Q_FORCED ? P.forced + batch * m * n : nullptr;
         F *pre = P.y_pre ? P.y_pre + batch * m * n : nullptr;
+        const F *yfg = P.yf ? P.yf + batch * m * n : nullptr, *cfg = P.yf ? P.cf + batch * m * n : nullptr;
 
         // ---- load the tile; all global loads of a pass are issued before its shared-memory stores ----
         const bool vec = full && (n % 4 == 0) && (m % 4 == 0) &&
@@ -121,6 +196,16 @@ __global__ void __launch_bounds__(TTH) tile_sweep_kernel(SweepArgs<F> P, int S, 
                     if (pass == 0) {
                         load4(yg + (i0 + r) * n + j0 + c, va[t]);
                         load4(cg + (i0 + r) * n + j0 + c, vb[t]);
+                        if (yfg != nullptr) {
+                            F fa[4], fb[4];
+                            load4(yfg + (i0 + r) * n + j0 + c, fa);
+                            load4(cfg + (i0 + r) * n + j0 + c, fb);
+#pragma unroll
+                            for (int x = 0; x < 4; ++x) {
+                                va[t][x] += fa[x];
+                                vb[t][x] += fb[x];
+                            }
+                        }
                     } else {
                         load4(lg + (i0 + r) * m + i0 + c, va[t]);
                         load4(ug + (j0 + r) * n + j0 + c, vb[t]);
@@ -151,6 +236,10 @@ __global__ void __launch_bounds__(TTH) tile_sweep_kernel(SweepArgs<F> P, int S, 
                     const bool in = gi < m && gj < n;
                     vy[t] = in ? yg[gi * n + gj] : (F)0;
                     vc[t] = in ? cg[gi * n + gj] : (F)0;
+                    if (in && yfg != nullptr) {
+                        vy[t] += yfg[gi * n + gj];
+                        vc[t] += cfg[gi * n + gj];
+                    }
                     vl[t] = (F)0;
                     if (r > c) {
                         if (gi < m) vl[t] = lg[gi * m + i0 + c];
@@ -168,6 +257,14 @@ __global__ void __launch_bounds__(TTH) tile_sweep_kernel(SweepArgs<F> P, int S, 
             }
         }
         __syncthreads();
+        if (P.neighbours) {
+            // pipelined schedule: the feedback of the two tiles finished one launch ago, which no update kernel has carried yet
+            const int rows = (int)(m - i0 < TILE ? m - i0 : TILE), cols = (int)(n - j0 < TILE ? n - j0 : TILE);
+            if (I > 0)  // C[I, J] += L[I, I - 1] E[I - 1, J]
+                tile_mm64<F>(Cs, lg + i0 * m + (i0 - TILE), m, eg + (i0 - TILE) * n + j0, n, rows, cols, Zs, tid, vec);
+            if (J > 0)  // Y[I, J] += C[I, J - 1] U[J - 1, J], with the completed C of the left neighbour
+                tile_mm64<F>(Ys, cg + i0 * n + (j0 - TILE), n, ug + (j0 - TILE) * n + j0, n, rows, cols, Zs, tid, vec);
+        }
         for (int idx = tid; idx < 2 * NSUB * DBLK; idx += TTH) {
             const int which = idx / (NSUB * DBLK), blk = idx / DBLK % NSUB, p = idx % DBLK / DLD, dd = idx % DLD;
             F v = (F)0;

@@ -87,7 +87,8 @@ def _row_major(t: torch.Tensor) -> torch.Tensor:
 # --------------------------------------------------------------------------------------------------------
 
 # Launch schedule of the fused engine: 0 lets the library choose, 1 forces the tile schedule (64 x 64 tiles, FFMA
-# updates), 2 forces the macro schedule (128 x 128 macro tiles; tensor-core updates where the library has them).
+# updates), 2 forces the macro schedule (128 x 128 macro tiles; tensor-core updates where the library has them),
+# 3 the pipelined schedule (tile launches on the critical path only, tensor-core updates on side streams; float32).
 SWEEP_SCHEDULE = 0
 
 _AFFINE_PLAIN = (quantizer_int.affine_quantizer_cuda,)

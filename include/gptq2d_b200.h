@@ -62,7 +62,7 @@ typedef struct g2d_sweep_desc {
     void *workspace;             /* g2d_sweep_workspace_bytes() bytes, 256-byte aligned */
     size_t workspace_bytes;
     int32_t outer_tiles;         /* tile anti-diagonals per far update; 0 selects the default */
-    int32_t reserved;            /* launch schedule: 0 library default, 1 tile schedule, 2 macro schedule */
+    int32_t reserved;            /* launch schedule: 0 library default, 1 tile, 2 macro, 3 pipelined schedule */
 } g2d_sweep_desc;
 
 const char *g2d_status_string(int status);

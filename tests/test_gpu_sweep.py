@@ -35,9 +35,9 @@ def python_round(y_flat, selection, *, out):
     torch.round(selected, out=out)
 
 
-@pytest.fixture(params=[1, 2], ids=["tile-schedule", "macro-schedule"])
+@pytest.fixture(params=[1, 2, 3], ids=["tile-schedule", "macro-schedule", "pipelined-schedule"])
 def schedule(request, api):
-    """Run a test under both launch schedules of the fused engine."""
+    """Run a test under every launch schedule of the fused engine."""
     G, _ = api
     before = G.SWEEP_SCHEDULE
     G.SWEEP_SCHEDULE = request.param
@@ -318,7 +318,7 @@ def test_unused_triangles_are_never_read_fp32(api):
     poisoned_u = torch.where(torch.ones_like(u).triu(1) > 0, u, torch.nan)
     before = G.SWEEP_SCHEDULE
     try:
-        for schedule in (0, 1, 2):
+        for schedule in (0, 1, 2, 3):
             G.SWEEP_SCHEDULE = schedule
             clean = G.gptq_2d(w, l, u, quantizer=quantizer, quantizer_inputs=(scale, zero))
             dirty = G.gptq_2d(w, poisoned_l, poisoned_u, quantizer=quantizer, quantizer_inputs=(scale, zero))
