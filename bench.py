@@ -254,11 +254,20 @@ def main() -> None:
     host_z = torch.empty_like(host_w).pin_memory()
     dev_w, dev_l, dev_u = torch.empty_like(w), torch.empty_like(g), torch.empty_like(h)
 
+    copy_stream, w_arrived = torch.cuda.Stream(device=device), torch.cuda.Event()
+
     def e2e_step():
-        dev_w.copy_(host_w, non_blocking=True)
+        # G and H first, on the compute stream; W travels on a second stream while the factors are prepared
+        current = torch.cuda.current_stream(device)
+        copy_stream.wait_stream(current)  # the previous step has finished with dev_w
         dev_l.copy_(host_l, non_blocking=True)
         dev_u.copy_(host_u, non_blocking=True)
-        out = step(dev_w, dev_l, dev_u)
+        with torch.cuda.stream(copy_stream):
+            dev_w.copy_(host_w, non_blocking=True)
+            w_arrived.record(copy_stream)
+        l_dev, u_dev = K.feedback_factors_from_grams(dev_l, dev_u)
+        current.wait_event(w_arrived)
+        out = sweep_only(dev_w, l_dev, u_dev)
         host_z.copy_(out, non_blocking=True)
 
     e2e_step()
@@ -303,7 +312,7 @@ def main() -> None:
     tensor_peak = pk["bf16_tflops_sustained"] / 6.0  # fp32-faithful tensor roofline: TF32 = bf16 / 2, three TF32 products per fp32 product
     far_tflops = far_flops / (far_ms * 1e-3) / 1e12 if far_ms > 0 else 0.0
     roofline = {
-        "bound": "tensor", "kernel": "macro_update_tc_kernel (tcgen05 kind::tf32, 3xTF32 split; far updates)",
+        "bound": "tensor", "kernel": "macro_update_tc_kernel (tcgen05 kind::tf32, 3xTF32 split; far updates, running beside the tile launches)",
         "achieved": far_tflops, "peak": tensor_peak, "unit": "TFLOP/s", "frac": far_tflops / tensor_peak if tensor_peak else None,
         # dram bytes read + written of one far-update launch, from the ncu capture of a 4096 x 4096 run (149.7 MB for
         # 946 target macro tiles, profiles/macro_update_tc_kernel_far_4096.md), scaled by the target tiles of an average launch here
@@ -316,6 +325,10 @@ def main() -> None:
         "whole_sweep_tflops": sweep_flops(m, n) / (parts["sweep"] * 1e-3) / 1e12,
         "prep_tflops": 2 * (2 * float(n) ** 3 / 3) / (parts["prep"] * 1e-3) / 1e12,
         "timed_in": "separate profiled pass of the same step inside bench.py, one CUDA event pair per launch on the launching stream",
+        # the critical path: one tile launch per tile anti-diagonal, each a chain of 7 x 31 dependent rounding stages;
+        # bound by that latency, not by memory or arithmetic throughput
+        "critical_path": {"kernel": "tile_sweep_kernel", "launches": int(tile_n), "avg_launch_us": 1e3 * tile_ms / tile_n if tile_n else None,
+                          "bound": "latency"},
     }
 
     line = {
@@ -324,7 +337,7 @@ def main() -> None:
         "data": "synthetic",
         "config": {
             "workload": f"{m}x{n} fp32 layer from W, G, H: ldl_of_inverse x2, INT4 symmetric per-row fp16 abs-max scales, two-sided sweep (one layer per GPU per step)",
-            "step": "kron_factors.feedback_factors_from_grams(G, H) (two ldl_of_inverse on two streams), int_abs_max_scale, gptq_2d (fused engine) through the public API",
+            "step": "kron_factors.feedback_factors_from_grams(G, H) (both factors in shared launches), int_abs_max_scale, gptq_2d (fused engine, pipelined schedule) through the public API",
             "l2": "inputs larger than L2: W, G, H are 3 x %.0f MB" % (m * n * 4 / 1e6),
             "sweep_ms": parts["sweep"], "prep_ms": parts["prep"],
             "stages": m + n - 1, "sweep_us_per_stage": parts["sweep"] * 1e3 / (m + n - 1),

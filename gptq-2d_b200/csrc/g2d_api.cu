@@ -296,7 +296,7 @@ int sweep_fused(const g2d_sweep_desc *d, cudaStream_t stream, LaunchTimer *timer
         if (status != G2D_OK) return status;
         a.et_hi = planes.et_hi; a.et_lo = planes.et_lo; a.c_hi = planes.c_hi; a.c_lo = planes.c_lo;
         if constexpr (sizeof(F) == sizeof(float)) {
-            if (d->reserved == 3) {
+            if (d->reserved == 3 || d->reserved == 0) {
                 float *yf = (float *)p, *cf = (float *)(p + mn);
                 if (cudaMemsetAsync(yf, 0, 2 * mn, stream) != cudaSuccess) return G2D_ERR_CUDA;
                 return sweep_pipelined(d, a, planes, yf, cf, stream, timer, flops);

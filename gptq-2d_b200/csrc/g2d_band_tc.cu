@@ -121,7 +121,7 @@ __global__ void __launch_bounds__(TC_THREADS) band_tc_kernel(const __grid_consta
     } else {
         // epilogue warps: lanes 32 q .. 32 q + 31 of tensor memory, q = warp % 4; lanes 0-63 belong to tile a, 64-127 to tile b
         const int q = warp & 3;
-        const bool ok = mbar_wait(&accum_bar, 0);
+        const bool ok = mbar_wait(&accum_bar, 0, 256);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (!ok) failed = 1;
         const bool go = __all_sync(0xffffffffu, ok && !failed);  // warp-uniform: the tensor-memory loads are warp-wide

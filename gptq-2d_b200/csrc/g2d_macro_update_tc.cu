@@ -120,7 +120,7 @@ __global__ void __launch_bounds__(TC_THREADS) macro_update_tc_kernel(const __gri
     } else {
         // epilogue warps: lanes 32 q .. 32 q + 31 of tensor memory, q = warp % 4
         const int q = warp & 3;
-        const bool ok = mbar_wait(&accum_bar, 0);
+        const bool ok = mbar_wait(&accum_bar, 0, 256);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (!ok) failed = 1;
         const int64_t row = (int64_t)i0 + q * 32 + lane;

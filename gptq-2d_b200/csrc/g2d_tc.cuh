@@ -35,11 +35,13 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// false on time-out
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
+// false on time-out.  Between polls the warp sleeps for `nap` nanoseconds: these kernels share SMs with the tile sweep,
+// whose two working warps should not lose issue slots to a spinning neighbour.
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, unsigned nap = 32) {
     const long long start = clock64();
     while (!mbar_try_wait(bar, parity)) {
         if (clock64() - start > WAIT_CYCLES) return false;
+        __nanosleep(nap);
     }
     return true;
 }
@@ -155,7 +157,7 @@ __device__ __forceinline__ void tc_ring_mma(TcRing &ring, uint32_t smem_base, ui
 
 // Epilogue warps: wait for the accumulator; false (for the whole warp) if any wait of the CTA ran out.
 __device__ __forceinline__ bool tc_ring_accumulator_ready(TcRing &ring) {
-    const bool ok = mbar_wait(&ring.accum, 0);
+    const bool ok = mbar_wait(&ring.accum, 0, 256);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     if (!ok) ring.failed = 1;
     return __all_sync(0xffffffffu, ok && !ring.failed);  // warp-uniform: the tensor-memory loads are warp-wide
