@@ -280,6 +280,32 @@ def test_cuda_graph(api):
             assert torch.equal(target, run(x + .25, l, u, quantizer_inputs=(scale, zero)))
 
 
+def test_cuda_graph_pipelined_schedule_fp32(api):
+    """The pipelined schedule forks to streams of the library's own and joins back: a capture on the caller's stream
+    must hold all of it, and replays must reproduce direct runs bit for bit (the additions have a fixed order)."""
+    G, Q = api
+    gen = torch.Generator(device="cuda").manual_seed(99)
+    m, n = 456, 328
+    x = 0.02 * torch.randn(m, n, generator=gen, device="cuda")
+    l = torch.tril(torch.randn(m, m, generator=gen, device="cuda") * (0.3 / m ** .5), -1)
+    u = torch.triu(torch.randn(n, n, generator=gen, device="cuda") * (0.3 / n ** .5), 1)
+    scale = Q.int_abs_max_scale_triton(x, qmin=-8, qmax=7, dtype=torch.float16).expand(m, n).contiguous()
+    zero = torch.zeros_like(scale)
+    quantizer = functools.partial(Q.affine_quantizer_triton, qmin=-8, qmax=7)
+    before = G.SWEEP_SCHEDULE
+    try:
+        G.SWEEP_SCHEDULE = 3
+        direct = G.gptq_2d(x, l, u, quantizer=quantizer, quantizer_inputs=(scale, zero))
+        assert torch.equal(direct, G.gptq_2d(x, l, u, quantizer=quantizer, quantizer_inputs=(scale, zero)))
+        replay = G.capture_gptq_2d(x, l, u, quantizer=quantizer, quantizer_inputs=(scale, zero))
+        assert torch.equal(replay(x, l, u, scale, zero), direct)
+        shifted = G.gptq_2d(x + 0.01, l, u, quantizer=quantizer, quantizer_inputs=(scale, zero))
+        assert torch.equal(replay(x + 0.01, l, u, scale, zero), shifted)
+        assert torch.equal(replay(x, l, u, scale, zero), direct)
+    finally:
+        G.SWEEP_SCHEDULE = before
+
+
 def test_quantizer_sees_quantized_values(api):
     """test_gptq_2d.py:113-127: live Y holds the quantized values of all earlier antidiagonals."""
     G, _ = api
