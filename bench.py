@@ -207,7 +207,15 @@ def main() -> None:
         scale = Q.int_abs_max_scale_triton(weights, qmin=-8, qmax=7, dtype=torch.float16).expand(m, n)
         return G.gptq_2d(weights, l, u, quantizer=quantizer, quantizer_inputs=(scale, zero))
 
+    import layer_set
+    pipeline = layer_set.LayerPipeline(device)
+
     def step(weights, gram_out=g, gram_in=h):
+        # the call a layer-set job makes per matrix: factor preparation on the pipeline's front stream (beside the sweep
+        # of the step before), scales and sweep on the current stream
+        return pipeline.quantize(weights, gram_out, gram_in)
+
+    def single_layer(weights, gram_out=g, gram_in=h):
         l, u = K.feedback_factors_from_grams(gram_out, gram_in)
         return sweep_only(weights, l, u)
 
@@ -239,7 +247,8 @@ def main() -> None:
     ms_per_step = elapsed_ms / args.steps
     # the sweep alone and the preparation alone, same events, outside the headline region
     parts = {}
-    for name, fn in (("sweep", lambda: sweep_only(w, l, u)), ("prep", lambda: K.feedback_factors_from_grams(g, h))):
+    for name, fn in (("sweep", lambda: sweep_only(w, l, u)), ("prep", lambda: K.feedback_factors_from_grams(g, h)),
+                     ("single_layer", lambda: single_layer(w))):
         fn()
         torch.cuda.synchronize()
         begin.record()
@@ -251,30 +260,21 @@ def main() -> None:
 
     # ---- end to end through the public call with HOST buffers: H2D of W, L, U and D2H of Z inside the timed region ----
     host_w, host_l, host_u = (t.cpu().pin_memory() for t in (w, g, h))
-    host_z = torch.empty_like(host_w).pin_memory()
-    dev_w, dev_l, dev_u = torch.empty_like(w), torch.empty_like(g), torch.empty_like(h)
-
-    copy_stream, w_arrived = torch.cuda.Stream(device=device), torch.cuda.Event()
+    host_z = [torch.empty_like(host_w).pin_memory() for _ in range(2)]
+    e2e_count = [0]
 
     def e2e_step():
-        # G and H first, on the compute stream; W travels on a second stream while the factors are prepared
-        current = torch.cuda.current_stream(device)
-        copy_stream.wait_stream(current)  # the previous step has finished with dev_w
-        dev_l.copy_(host_l, non_blocking=True)
-        dev_u.copy_(host_u, non_blocking=True)
-        with torch.cuda.stream(copy_stream):
-            dev_w.copy_(host_w, non_blocking=True)
-            w_arrived.record(copy_stream)
-        l_dev, u_dev = K.feedback_factors_from_grams(dev_l, dev_u)
-        current.wait_event(w_arrived)
-        out = sweep_only(dev_w, l_dev, u_dev)
-        host_z.copy_(out, non_blocking=True)
+        # host buffers in, host buffer out, every step: G and H then the factors on the front stream, W on a copy stream,
+        # Z back on an output stream behind the sweep; two layers in flight
+        e2e_count[0] += 1
+        return pipeline.quantize_from_host(host_w, host_l, host_u, host_z[e2e_count[0] % 2])
 
     e2e_step()
     barrier()
     begin.record()
     for _ in range(args.steps):
-        e2e_step()
+        arrived = e2e_step()
+    torch.cuda.current_stream(device).wait_event(arrived)  # the last result has reached the host buffer
     end.record()
     barrier()
     e2e_ms = begin.elapsed_time(end)
@@ -284,7 +284,7 @@ def main() -> None:
         e2e_ms = t.item()
     e2e_ms /= args.steps
     h2d = (host_w.numel() + host_l.numel() + host_u.numel()) * 4
-    d2h = host_z.numel() * 4
+    d2h = host_z[0].numel() * 4
 
     if rank != 0:
         if world > 1:
@@ -337,8 +337,9 @@ def main() -> None:
         "data": "synthetic",
         "config": {
             "workload": f"{m}x{n} fp32 layer from W, G, H: ldl_of_inverse x2, INT4 symmetric per-row fp16 abs-max scales, two-sided sweep (one layer per GPU per step)",
-            "step": "kron_factors.feedback_factors_from_grams(G, H) (both factors in shared launches), int_abs_max_scale, gptq_2d (fused engine, pipelined schedule) through the public API",
+            "step": "kron_factors.feedback_factors_from_grams(G, H) (both factors in shared launches), int_abs_max_scale, gptq_2d (fused engine, pipelined schedule) through layer_set.LayerPipeline: the factor preparation of a step runs beside the sweep of the step before",
             "l2": "inputs larger than L2: W, G, H are 3 x %.0f MB" % (m * n * 4 / 1e6),
+            "layers_in_flight": 2, "single_layer_ms": parts["single_layer"],
             "sweep_ms": parts["sweep"], "prep_ms": parts["prep"],
             "stages": m + n - 1, "sweep_us_per_stage": parts["sweep"] * 1e3 / (m + n - 1),
         },

@@ -53,6 +53,117 @@ def partition(items: list[dict], world: int) -> list[list[dict]]:
     return shares
 
 
+class LayerPipeline:
+    """Two layers of one GPU in flight: the factor preparation of a layer runs on a stream of its own ("front"), so it
+    overlaps the sweep of the layer before it.  Both are chains of short dependent launches that leave most SMs idle,
+    and the layers of a set are independent, so a set finishes in about the time of its sweeps alone.
+
+    ``quantize`` takes inputs that are resident on the device; ``quantize_from_host`` takes pinned host tensors, moves
+    them in on the front stream (the weights on a third one) and moves the result out behind the sweep.  Results come
+    back in stream order of the caller's current stream.  INT4 symmetric per-row scales, as the layer-set benchmark."""
+
+    def __init__(self, device, qmin: int = -8, qmax: int = 7):
+        import torch
+
+        self.device, self.qmin, self.qmax = device, qmin, qmax
+        self.front = torch.cuda.Stream(device=device)
+        self.copy = torch.cuda.Stream(device=device)
+        self.out = torch.cuda.Stream(device=device)
+        self.swept = [None, None]  # events: the sweeps of the last two layers have finished (the older bounds the run-ahead)
+        self.slots = {}        # device buffers of quantize_from_host, two per shape
+        self.count = 0
+
+    def _sweep(self, w, l, u):
+        import torch
+
+        import gptq_2d as G
+        import quantizer_int as Q
+
+        m, n = w.shape
+        scale = Q.int_abs_max_scale_triton(w, qmin=self.qmin, qmax=self.qmax, dtype=torch.float16).expand(m, n)
+        zero = torch.zeros(1, 1, device=w.device, dtype=w.dtype).expand(m, n)
+        quantizer = functools.partial(Q.affine_quantizer_triton, qmin=self.qmin, qmax=self.qmax)
+        return G.gptq_2d(w, l, u, quantizer=quantizer, quantizer_inputs=(scale, zero))
+
+    def _prepare(self, g, h, main):
+        """Factors of (g, h) on the front stream; the caller's stream waits for them.  At most one layer ahead."""
+        import torch
+
+        import kron_factors as K
+
+        with torch.cuda.stream(self.front):
+            l, u = K.feedback_factors_from_grams(g, h)
+            ready = torch.cuda.Event()
+            ready.record(self.front)
+        main.wait_event(ready)
+        l.record_stream(main)
+        u.record_stream(main)
+        return l, u
+
+    def _after_sweep(self, main):
+        import torch
+
+        event = torch.cuda.Event()
+        event.record(main)
+        self.swept = [self.swept[1], event]
+        return event
+
+    def _throttle(self):
+        # the preparation of this layer may run beside the sweep of the layer before it, not further ahead
+        if self.swept[0] is not None:
+            self.front.wait_event(self.swept[0])
+
+    def quantize(self, w, g, h, inputs_ready=None):
+        """Quantize one layer whose inputs are on the device.  ``inputs_ready``: an event after which ``g`` and ``h`` may
+        be read, or None when they were complete before the call (the front stream does not wait for the caller's)."""
+        import torch
+
+        main = torch.cuda.current_stream(self.device)
+        self._throttle()
+        if inputs_ready is not None:
+            self.front.wait_event(inputs_ready)
+        l, u = self._prepare(g, h, main)
+        z = self._sweep(w, l, u)
+        self._after_sweep(main)
+        return z
+
+    def quantize_from_host(self, host_w, host_g, host_h, host_z):
+        """The same from pinned host tensors into a pinned host result; returns the event that marks ``host_z`` complete."""
+        import torch
+
+        main = torch.cuda.current_stream(self.device)
+        key = (tuple(host_w.shape), host_w.dtype)
+        if key not in self.slots:
+            self.slots[key] = [{"w": torch.empty(host_w.shape, dtype=host_w.dtype, device=self.device),
+                                "g": torch.empty(host_g.shape, dtype=host_g.dtype, device=self.device),
+                                "h": torch.empty(host_h.shape, dtype=host_h.dtype, device=self.device),
+                                "free": None} for _ in range(2)]
+        slot = self.slots[key][self.count % 2]
+        self.count += 1
+        if slot["free"] is not None:  # the sweep that read this slot two layers ago has finished
+            self.front.wait_event(slot["free"])
+            self.copy.wait_event(slot["free"])
+        self._throttle()
+        with torch.cuda.stream(self.front):
+            slot["g"].copy_(host_g, non_blocking=True)
+            slot["h"].copy_(host_h, non_blocking=True)
+        with torch.cuda.stream(self.copy):
+            slot["w"].copy_(host_w, non_blocking=True)
+            arrived = torch.cuda.Event()
+            arrived.record(self.copy)
+        l, u = self._prepare(slot["g"], slot["h"], main)
+        main.wait_event(arrived)
+        z = self._sweep(slot["w"], l, u)
+        slot["free"] = self._after_sweep(main)
+        self.out.wait_event(slot["free"])
+        with torch.cuda.stream(self.out):  # behind the sweep, beside the next layer
+            host_z.copy_(z, non_blocking=True)
+            done = torch.cuda.Event()
+            done.record(self.out)
+        z.record_stream(self.out)
+        return done
+
+
 def quantize_matrix(item: dict, device) -> dict:
     """Generate one seeded layer on ``device``, prepare its factors, quantize it to INT4; returns timings and checks."""
     import torch
