@@ -164,8 +164,12 @@ class LayerPipeline:
         return done
 
 
-def quantize_matrix(item: dict, device) -> dict:
-    """Generate one seeded layer on ``device``, prepare its factors, quantize it to INT4; returns timings and checks."""
+def quantize_matrix(item: dict, device, pipeline: LayerPipeline | None = None):
+    """Generate one seeded layer on ``device``, prepare its factors, quantize it to INT4; returns timings and checks.
+
+    With a ``pipeline`` the layer is generated and its factors are prepared on the pipeline's front stream, beside the
+    sweep of the layer before it; the statistics then stay on the device and the call returns a function that fetches
+    them (calling it waits for this layer), so that the host can enqueue the next layer first."""
     import torch
 
     import gptq_2d as G
@@ -174,26 +178,52 @@ def quantize_matrix(item: dict, device) -> dict:
     import synthetic
 
     m, n = item["m"], item["n"]
-    w, g, h = synthetic.make_layer(m, n, seed=item["seed"], device=device, samples=min(8192, max(m, n)))
+    samples = min(8192, max(m, n))
     events = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
-    events[0].record()
-    l, u = K.feedback_factors_from_grams(g, h)
-    events[1].record()
-    scale = Q.int_abs_max_scale_triton(w, qmin=-8, qmax=7, dtype=torch.float16).expand(m, n)
-    zero = torch.zeros(1, 1, device=device, dtype=w.dtype).expand(m, n)
-    z = G.gptq_2d(w, l, u, quantizer=functools.partial(Q.affine_quantizer_triton, qmin=-8, qmax=7), quantizer_inputs=(scale, zero))
-    events[2].record()
-    torch.cuda.synchronize(device)
+    if pipeline is None:
+        w, g, h = synthetic.make_layer(m, n, seed=item["seed"], device=device, samples=samples)
+        events[0].record()
+        l, u = K.feedback_factors_from_grams(g, h)
+        events[1].record()
+        scale = Q.int_abs_max_scale_triton(w, qmin=-8, qmax=7, dtype=torch.float16).expand(m, n)
+        zero = torch.zeros(1, 1, device=device, dtype=w.dtype).expand(m, n)
+        z = G.gptq_2d(w, l, u, quantizer=functools.partial(Q.affine_quantizer_triton, qmin=-8, qmax=7), quantizer_inputs=(scale, zero))
+        events[2].record()
+    else:
+        main = torch.cuda.current_stream(device)
+        pipeline._throttle()
+        with torch.cuda.stream(pipeline.front):
+            w, g, h = synthetic.make_layer(m, n, seed=item["seed"], device=device, samples=samples)
+            events[0].record(pipeline.front)
+        l, u = pipeline._prepare(g, h, main)
+        for t in (w, g, h):
+            t.record_stream(main)
+        events[1].record(main)
+        z = pipeline._sweep(w, l, u)
+        pipeline._after_sweep(main)
+        events[2].record(main)
+        scale = Q.int_abs_max_scale_triton(w, qmin=-8, qmax=7, dtype=torch.float16).expand(m, n)
     codes = torch.round(z / scale)
-    stats = {
-        **item, "prep_ms": events[0].elapsed_time(events[1]), "sweep_ms": events[1].elapsed_time(events[2]),
-        "codes_in_range": bool((codes.min() >= -8) & (codes.max() <= 7)), "finite": bool(torch.isfinite(z).all()),
-        "code_sum": float(codes.double().sum().item()),
-    }
+    on_device = {"lo": codes.min(), "hi": codes.max(), "finite": torch.isfinite(z).all(), "code_sum": codes.double().sum()}
     if m * n <= 4096 * 4096:  # the objective needs two more products; keep it to the smaller matrices
         rtn = torch.clamp(torch.round(w / scale), -8, 7) * scale
-        stats["objective_vs_rtn"] = synthetic.objective(z, w, g, h) / synthetic.objective(rtn, w, g, h)
-    return stats
+        r, r0 = (z - w).double(), (rtn - w).double()
+        on_device["objective"] = ((g.double() @ r) * (r @ h.double())).sum()
+        on_device["objective_rtn"] = ((g.double() @ r0) * (r0 @ h.double())).sum()
+
+    def finish() -> dict:
+        torch.cuda.synchronize(device)
+        stats = {
+            **item, "prep_ms": events[0].elapsed_time(events[1]) if pipeline is None else None,
+            "sweep_ms": events[1].elapsed_time(events[2]),
+            "codes_in_range": bool((on_device["lo"] >= -8) & (on_device["hi"] <= 7)), "finite": bool(on_device["finite"]),
+            "code_sum": float(on_device["code_sum"].item()),
+        }
+        if "objective" in on_device:
+            stats["objective_vs_rtn"] = float(on_device["objective"].item() / on_device["objective_rtn"].item())
+        return stats
+
+    return finish() if pipeline is None else finish
 
 
 def run(items: list[dict], process: Callable[[dict], dict], *, rank: int, world: int, gather: Callable | None = None,
@@ -205,6 +235,7 @@ def run(items: list[dict], process: Callable[[dict], dict], *, rank: int, world:
         barrier()
     start = time.perf_counter()
     results = [process(item) for item in share]
+    results = [r() if callable(r) else r for r in results]  # a pipelined process hands back fetchers of its statistics
     busy = time.perf_counter() - start
     if barrier is not None:
         barrier()
@@ -220,8 +251,8 @@ def run(items: list[dict], process: Callable[[dict], dict], *, rank: int, world:
     for r in results:
         entry = by_shape.setdefault(f"{r['m']}x{r['n']}", {"count": 0, "prep_ms": 0.0, "sweep_ms": 0.0})
         entry["count"] += 1
-        entry["prep_ms"] += r.get("prep_ms", 0.0)
-        entry["sweep_ms"] += r.get("sweep_ms", 0.0)
+        entry["prep_ms"] += r.get("prep_ms") or 0.0
+        entry["sweep_ms"] += r.get("sweep_ms") or 0.0
     for entry in by_shape.values():
         entry["prep_ms"] /= entry["count"]
         entry["sweep_ms"] /= entry["count"]
@@ -240,6 +271,7 @@ def main() -> None:
     parser = argparse.ArgumentParser()
     parser.add_argument("--blocks", type=int, default=80)
     parser.add_argument("--divide", type=int, default=1, help="shrink every dimension by this factor")
+    parser.add_argument("--serial", action="store_true", help="one layer at a time (per-part timings) instead of two in flight")
     args = parser.parse_args()
     sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
     import torch
@@ -263,8 +295,9 @@ def main() -> None:
     # one small matrix through every kernel first: the CUDA module loads on first use and would otherwise be charged
     # to the first (largest) matrix of every rank
     quantize_matrix({"block": -1, "name": "warm-up", "m": 384, "n": 512, "seed": 1}, device)
-    summary = run(layer_list(args.blocks, args.divide), functools.partial(quantize_matrix, device=device), rank=rank, world=world,
-                  gather=gather, barrier=barrier)
+    pipeline = None if args.serial else LayerPipeline(device)
+    summary = run(layer_list(args.blocks, args.divide), functools.partial(quantize_matrix, device=device, pipeline=pipeline), rank=rank,
+                  world=world, gather=gather, barrier=barrier)
     if summary is not None:
         print(json.dumps(summary))
     if world > 1:
