@@ -8,15 +8,17 @@
 //
 //   * the host launches one grid per tile anti-diagonal; the tiles of one anti-diagonal are
 //     independent, all feedback from earlier tiles is already in Y (right) and C (down);
-//   * inside the CTA the tile lives in shared memory; warp a sweeps sub-tile (a, w - a) of the
-//     sub-tile anti-diagonal w in registers, then all warps apply the finished sub-tiles'
-//     feedback to the rest of the tile as small dense products;
-//   * inside a sub-tile the 16 + 16 lanes of a warp own its columns and rows.  Lane j < 16 holds
-//     the down feedback ("C") of column j, lane 16 + i the right feedback ("Y") of row i, both
-//     skewed so that the entries of anti-diagonal s sit in register s mod 16 of every lane: the
-//     stage loop is fully unrolled and indexes registers statically.  The feedback coefficients
-//     of a sub-tile come from zero-padded copies of the diagonal blocks of L and U^T, so the
-//     pushes need no bounds predicates: out-of-range pushes multiply by zero.
+//   * inside the CTA the tile lives in shared memory; the 16 x 16 sub-tiles are taken on a sub-tile wavefront: the
+//     up to four sub-tiles of one sub-tile anti-diagonal are swept in registers by the four half-warps of warps 0 and 1,
+//     then all warps apply the finished sub-tiles' feedback to the rest of the tile as small dense products;
+//   * inside a sub-tile lane k of the half-warp owns column k (the down feedback, "C") and row k (the right feedback,
+//     "Y"), both skewed so that the entries of anti-diagonal s sit in register s mod 16 of every lane: the stage loop
+//     is fully unrolled and indexes registers statically; two shuffles per stage exchange the row accumulator and the
+//     completed C with the partner lane.  The feedback coefficients of a sub-tile come from zero-padded copies of the
+//     diagonal blocks of L and U^T, so the pushes need no bounds predicates: out-of-range pushes multiply by zero;
+//   * pipelined schedule: a tile also adds the far-feedback planes as it loads and applies the feedback of its two
+//     neighbours of the previous tile anti-diagonal itself; warps 2 and 3, idle during a sub-tile sweep, do that for
+//     the sub-tiles of the next sub-tile anti-diagonal.
 #include <type_traits>
 
 #include "g2d_common.cuh"
@@ -81,78 +83,42 @@ __device__ __forceinline__ void mm16(F *__restrict__ D, const F *__restrict__ A,
     store4(D + (r + 1) * LD + c, d1);
 }
 
-// D[64 x 64, shared, row stride LD] += A[64 x 64] B[64 x 64], A and B row-major in global memory (leading dimensions
-// lda, ldb), for all TTH threads of the CTA: thread (ty, tx) forms the outputs of rows 8 ty .. 8 ty + 7 and columns
-// 4 tx .. 4 tx + 3 from k chunks of 16 staged in `stage` (2 x 16 x LD values).  Rows of A from `rows` on and columns
-// of B from `cols` on read as zero (ragged last tiles); `vec` promises whole, 16-byte aligned operands.
+// Feedback of a neighbour tile into one 16 x 16 sub-tile, for a group of 16 threads (t = 0..15): thread t forms the
+// 4 x 4 patch at rows 4 (t / 4), columns 4 (t % 4) of  A[16 x K] B[K x 16]  over k = k0 .. k0 + kn - 1 and returns it
+// in acc.  A and B are row-major in global memory (written by an earlier launch, or constant); A points at the
+// sub-tile's row strip, B at its column strip.  Rows of A from `rows` on and columns of B from `cols` on read as zero
+// (ragged last tiles); `vec` promises whole, 16-byte aligned operands.
 template <typename F>
-__device__ __forceinline__ void tile_mm64(F *D, const F *__restrict__ A, int64_t lda, const F *__restrict__ B, int64_t ldb, int rows, int cols,
-                                          F *stage, int tid, bool vec) {
-    constexpr int KCH = 16;
-    F *As = stage, *Bs = stage + KCH * LD;  // As[kk][i], Bs[kk][j]
-    const int ty = tid >> 4, tx = tid & 15;
-    F acc[8][4];
+__device__ __forceinline__ void neighbour_patch(F (&acc)[4][4], const F *__restrict__ A, int64_t lda, const F *__restrict__ B, int64_t ldb,
+                                                int t, int k0, int kn, int rows, int cols, bool vec) {
+    const int pr = (t >> 2) * 4, pc = (t & 3) * 4;
 #pragma unroll
-    for (int x = 0; x < 8; ++x)
+    for (int x = 0; x < 4; ++x)
 #pragma unroll
         for (int y = 0; y < 4; ++y) acc[x][y] = (F)0;
-    F ra[2][4], rb[2][4];
-    auto fetch = [&](int k0) {  // global -> registers; consumed one iteration later, so the latency hides behind the products
+#pragma unroll 2
+    for (int k = k0; k < k0 + kn; k += 4) {
+        F a[4][4], b[4][4];
 #pragma unroll
-        for (int t = 0; t < 2; ++t) {
-            const int idx = t * TTH + tid;
-            const int ar = idx >> 2, aq = (idx & 3) * 4;   // A chunk: 64 rows x 16 k
-            const int br = idx >> 4, bq = (idx & 15) * 4;  // B chunk: 16 k x 64 columns
+        for (int x = 0; x < 4; ++x) {
             if (vec) {
-                load4(A + ar * lda + k0 + aq, ra[t]);
-                load4(B + (k0 + br) * ldb + bq, rb[t]);
+                load4(A + (pr + x) * lda + k, a[x]);
+                load4(B + (k + x) * ldb + pc, b[x]);
             } else {
 #pragma unroll
-                for (int x = 0; x < 4; ++x) {
-                    ra[t][x] = ar < rows ? A[ar * lda + k0 + aq + x] : (F)0;
-                    rb[t][x] = bq + x < cols ? B[(k0 + br) * ldb + bq + x] : (F)0;
+                for (int y = 0; y < 4; ++y) {
+                    a[x][y] = pr + x < rows ? A[(pr + x) * lda + k + y] : (F)0;
+                    b[x][y] = pc + y < cols ? B[(k + x) * ldb + pc + y] : (F)0;
                 }
             }
         }
-    };
-    fetch(0);
-    for (int k0 = 0; k0 < TILE; k0 += KCH) {
-        __syncthreads();  // the previous chunk has been consumed
 #pragma unroll
-        for (int t = 0; t < 2; ++t) {
-            const int idx = t * TTH + tid;
-            const int ar = idx >> 2, aq = (idx & 3) * 4, br = idx >> 4, bq = (idx & 15) * 4;
+        for (int kk = 0; kk < 4; ++kk)
 #pragma unroll
-            for (int x = 0; x < 4; ++x) As[(aq + x) * LD + ar] = ra[t][x];
-            store4(Bs + br * LD + bq, rb[t]);
-        }
-        __syncthreads();
-        if (k0 + KCH < TILE) fetch(k0 + KCH);
+            for (int x = 0; x < 4; ++x)
 #pragma unroll
-        for (int kk = 0; kk < KCH; ++kk) {
-            F a0[4], a1[4], b[4];
-            load4(As + kk * LD + 8 * ty, a0);
-            load4(As + kk * LD + 8 * ty + 4, a1);
-            load4(Bs + kk * LD + 4 * tx, b);
-#pragma unroll
-            for (int y = 0; y < 4; ++y) {
-#pragma unroll
-                for (int x = 0; x < 4; ++x) {
-                    acc[x][y] += a0[x] * b[y];
-                    acc[4 + x][y] += a1[x] * b[y];
-                }
-            }
-        }
+                for (int y = 0; y < 4; ++y) acc[x][y] += a[x][kk] * b[kk][y];
     }
-#pragma unroll
-    for (int x = 0; x < 8; ++x) {
-        F d[4];
-        load4(D + (8 * ty + x) * LD + 4 * tx, d);
-#pragma unroll
-        for (int y = 0; y < 4; ++y) d[y] += acc[x][y];
-        store4(D + (8 * ty + x) * LD + 4 * tx, d);
-    }
-    __syncthreads();
 }
 
 template <typename F, int KIND>
@@ -196,20 +162,27 @@ __global__ void __launch_bounds__(TTH) tile_sweep_kernel(SweepArgs<F> P, int S, 
                     if (pass == 0) {
                         load4(yg + (i0 + r) * n + j0 + c, va[t]);
                         load4(cg + (i0 + r) * n + j0 + c, vb[t]);
-                        if (yfg != nullptr) {
-                            F fa[4], fb[4];
-                            load4(yfg + (i0 + r) * n + j0 + c, fa);
-                            load4(cfg + (i0 + r) * n + j0 + c, fb);
-#pragma unroll
-                            for (int x = 0; x < 4; ++x) {
-                                va[t][x] += fa[x];
-                                vb[t][x] += fb[x];
-                            }
-                        }
                     } else {
                         load4(lg + (i0 + r) * m + i0 + c, va[t]);
                         load4(ug + (j0 + r) * n + j0 + c, vb[t]);
                     }
+                }
+                if (pass == 0 && yfg != nullptr) {
+                    // the far planes, in a batch of their own so that no addition waits between two loads
+                    F fa[PER][4], fb[PER][4];
+#pragma unroll
+                    for (int t = 0; t < PER; ++t) {
+                        const int idx = t * TTH + tid, r = idx / (TILE / 4), c = (idx % (TILE / 4)) * 4;
+                        load4(yfg + (i0 + r) * n + j0 + c, fa[t]);
+                        load4(cfg + (i0 + r) * n + j0 + c, fb[t]);
+                    }
+#pragma unroll
+                    for (int t = 0; t < PER; ++t)
+#pragma unroll
+                        for (int x = 0; x < 4; ++x) {
+                            va[t][x] += fa[t][x];
+                            vb[t][x] += fb[t][x];
+                        }
                 }
 #pragma unroll
                 for (int t = 0; t < PER; ++t) {
@@ -257,13 +230,38 @@ __global__ void __launch_bounds__(TTH) tile_sweep_kernel(SweepArgs<F> P, int S, 
             }
         }
         __syncthreads();
+        // Pipelined schedule: the feedback of the two tiles finished one launch ago, which no update kernel has carried yet:
+        //     C[I, J] += L[I, I - 1] E[I - 1, J],      Y[I, J] += C[I, J - 1] U[J - 1, J]  (the completed C of the left neighbour).
+        // Only the first sub-tile needs it before the sweep starts (here, all threads: eight groups of 16 split the two
+        // products and four quarters of k, partial patches are summed in a fixed order through shared memory); the
+        // sub-tiles of a later sub-tile anti-diagonal get theirs from the two warps that idle while the one before is swept.
+        const int nb_rows = (int)(m - i0 < TILE ? m - i0 : TILE), nb_cols = (int)(n - j0 < TILE ? n - j0 : TILE);
+        const F *const nb_a[2] = {lg + i0 * m + (i0 - TILE), cg + i0 * n + (j0 - TILE)};       // A operands: L block, left C
+        const F *const nb_b[2] = {eg + (i0 - TILE) * n + j0, ug + (j0 - TILE) * n + j0};       // B operands: upper E, U block
+        const int64_t nb_lda[2] = {m, n};
+        const bool nb_on[2] = {P.neighbours && I > 0, P.neighbours && J > 0};
         if (P.neighbours) {
-            // pipelined schedule: the feedback of the two tiles finished one launch ago, which no update kernel has carried yet
-            const int rows = (int)(m - i0 < TILE ? m - i0 : TILE), cols = (int)(n - j0 < TILE ? n - j0 : TILE);
-            if (I > 0)  // C[I, J] += L[I, I - 1] E[I - 1, J]
-                tile_mm64<F>(Cs, lg + i0 * m + (i0 - TILE), m, eg + (i0 - TILE) * n + j0, n, rows, cols, Zs, tid, vec);
-            if (J > 0)  // Y[I, J] += C[I, J - 1] U[J - 1, J], with the completed C of the left neighbour
-                tile_mm64<F>(Ys, cg + i0 * n + (j0 - TILE), n, ug + (j0 - TILE) * n + j0, n, rows, cols, Zs, tid, vec);
+            const int group = tid >> 4, t = tid & 15, prod = group & 1, quarter = group >> 1;
+            F acc[4][4];
+            if (nb_on[prod]) {
+                neighbour_patch<F>(acc, nb_a[prod], nb_lda[prod], nb_b[prod], n, t, quarter * (TILE / 4), TILE / 4, nb_rows, nb_cols, vec);
+#pragma unroll
+                for (int x = 0; x < 4; ++x)
+#pragma unroll
+                    for (int y = 0; y < 4; ++y) Zs[group * (SUB * SUB) + ((t >> 2) * 4 + x) * SUB + (t & 3) * 4 + y] = acc[x][y];
+            }
+            __syncthreads();
+            for (int idx = tid; idx < 2 * SUB * SUB; idx += TTH) {
+                const int prod2 = idx / (SUB * SUB), e = idx % (SUB * SUB);
+                if (nb_on[prod2]) {
+                    F *dst = (prod2 == 0 ? Cs : Ys) + (e / SUB) * LD + e % SUB;
+                    F sum = *dst;
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4) sum += Zs[((q4 << 1) | prod2) * (SUB * SUB) + e];
+                    *dst = sum;
+                }
+            }
+            __syncthreads();
         }
         for (int idx = tid; idx < 2 * NSUB * DBLK; idx += TTH) {
             const int which = idx / (NSUB * DBLK), blk = idx / DBLK % NSUB, p = idx % DBLK / DLD, dd = idx % DLD;
@@ -397,6 +395,29 @@ __global__ void __launch_bounds__(TTH) tile_sweep_kernel(SweepArgs<F> P, int S, 
                 const int bn = w + 1 - sub_a;
                 fetch_params(bn >= 0 && bn < NSUB ? bn : 0);
                 have_params = true;
+            } else if (P.neighbours && w + 1 < 2 * NSUB - 1) {
+                // warps 2 and 3: the neighbour feedback for the sub-tiles of the next sub-tile anti-diagonal, one group of 16
+                // threads per sub-tile row; nobody else touches those sub-tiles until the barrier below
+                const int group = (tid - 2 * 32) >> 4, t = tid & 15;
+                const int ap = group, bp = w + 1 - ap;
+                if (bp >= 0 && bp < NSUB) {
+#pragma unroll 1
+                    for (int prod = 0; prod < 2; ++prod) {
+                        if (!nb_on[prod]) continue;
+                        F acc[4][4];
+                        neighbour_patch<F>(acc, nb_a[prod] + (int64_t)ap * SUB * nb_lda[prod], nb_lda[prod], nb_b[prod] + bp * SUB, n, t, 0, TILE,
+                                           nb_rows - ap * SUB, nb_cols - bp * SUB, vec);
+                        F *dst = (prod == 0 ? Cs : Ys) + (ap * SUB + (t >> 2) * 4) * LD + bp * SUB + (t & 3) * 4;
+#pragma unroll
+                        for (int x = 0; x < 4; ++x) {
+                            F d[4];
+                            load4(dst + x * LD, d);
+#pragma unroll
+                            for (int y = 0; y < 4; ++y) d[y] += acc[x][y];
+                            store4(dst + x * LD, d);
+                        }
+                    }
+                }
             }
             __syncthreads();
             // ---- apply the finished sub-tiles to the rest of the tile ----
