@@ -186,6 +186,20 @@ int g2d_ldl_of_inverse_pair(int dtype, int64_t n0, void *a0, int32_t size0, void
                             size_t workspace0_bytes, int64_t n1, void *a1, int32_t size1, void *out1,
                             void *workspace1, size_t workspace1_bytes, int32_t *status_flags, void *stream);
 
+/* Packed integer codes of a rounded matrix z [m, n] and back.  The reference has no counterpart: it returns
+ * dequantised floats and notes that the code can be recovered from them (quantizer_trellis.py:11-14; for the
+ * affine quantizer, quantizer_int.py:63-83, code = rint(z / scale + zero point)).  Entry j of a row is the
+ * `bits`-bit unsigned field code - qmin (clamped to the field) at the bits j*bits .. j*bits+bits-1 of the
+ * row's byte string (little-endian); rows are row_bytes >= ceil(n*bits/8) apart.  scale and zero point are
+ * addressed by row and column strides in elements (0 = broadcast).  g2d_unpack_codes forms
+ * (code + qmin - zero point) * scale, the value the affine quantizer returned, bit for bit. */
+int g2d_pack_codes(int dtype, int64_t m, int64_t n, const void *z, const void *scale, int64_t scale_row_stride,
+                   int64_t scale_col_stride, const void *zero, int64_t zero_row_stride, int64_t zero_col_stride,
+                   double qmin, int32_t bits, uint8_t *codes, int64_t row_bytes, void *stream);
+int g2d_unpack_codes(int dtype, int64_t m, int64_t n, const uint8_t *codes, int64_t row_bytes, const void *scale,
+                     int64_t scale_row_stride, int64_t scale_col_stride, const void *zero, int64_t zero_row_stride,
+                     int64_t zero_col_stride, double qmin, int32_t bits, void *z, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

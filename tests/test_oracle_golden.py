@@ -123,3 +123,19 @@ def test_d_sided_golden(oracle):
     l1, l2, l3 = (g[f"l{k}_{d}"] for d in range(3))
     z2 = oracle.sweep(x.reshape(x.shape[0] * x.shape[1], x.shape[2]), np.kron(l1, l2), l3.T.copy())
     assert np.array_equal(z2.reshape(x.shape), g[f"z{k}"])
+
+
+def test_packed_codes_known_answers(oracle):
+    """The packing is this library's own format: pinned by hand-computed bytes and by the round trip."""
+    scale = np.full((1, 4), 0.5, dtype=np.float32)
+    z = (np.array([[1, 2, 3, 4]], dtype=np.float32) - 8) * scale            # codes 1..4 with qmin = -8
+    assert oracle.pack_codes(z, scale, 0.0, -8, 4).tolist() == [[0x21, 0x43]]
+    codes3 = np.array([[1, 2, 3, 4, 5, 6, 7, 0, 5]])                           # nine 3-bit fields: 27 bits -> 4 bytes
+    value = sum(int(c) << (3 * j) for j, c in enumerate(codes3[0]))
+    z3 = (codes3.astype(np.float64) - 2.0) * 0.25                              # zero point 2
+    packed = oracle.pack_codes(z3, 0.25, 2.0, 0, 3)
+    assert packed.tolist() == [[(value >> (8 * b)) & 0xFF for b in range(4)]]
+    assert np.array_equal(oracle.unpack_codes(packed, 0.25, 2.0, 0, 3, 9, np.float64), z3)
+    rng = np.random.default_rng(0)
+    z = (rng.integers(0, 32, (7, 21)) * 0.125).astype(np.float32)
+    assert np.array_equal(oracle.unpack_codes(oracle.pack_codes(z, 0.125, 0.0, 0, 5), 0.125, 0.0, 0, 5, 21), z)
