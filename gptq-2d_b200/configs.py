@@ -148,14 +148,9 @@ def pack(divide: int, device) -> dict:
     z = torch.clamp(torch.round(w / scale), -8, 7) * scale
     codes = P.pack_codes(z, scale, zero, qmin=-8, bits=4)
     assert torch.equal(P.unpack_codes(codes, scale, zero, qmin=-8, bits=4, n=n), z)
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)  # larger than L2
-
-    def timed(fn, repeats=5):
-        total = 0.0
-        for _ in range(repeats):
-            flush.zero_()
-            total += _timed(fn)[1]
-        return total / repeats
+    def timed(fn, repeats=10):  # back to back: the host side of a call hides behind the previous launch
+        fn()
+        return _timed(lambda: [fn() for _ in range(repeats)])[1] / repeats
 
     pack_ms = timed(lambda: P.pack_codes(z, scale, zero, qmin=-8, bits=4))
     unpack_ms = timed(lambda: P.unpack_codes(codes, scale, zero, qmin=-8, bits=4, n=n))
@@ -170,7 +165,7 @@ def pack(divide: int, device) -> dict:
         "config": "pack", "shape": [m, n], "bits": 4, "pack_ms": pack_ms, "unpack_ms": unpack_ms, "algorithmic_bytes": moved,
         "pack_gbs": moved / pack_ms / 1e6, "unpack_gbs": moved / unpack_ms / 1e6, "hbm_peak_gbs": peak, "peak_source": source,
         "pack_frac": moved / pack_ms / 1e6 / peak, "unpack_frac": moved / unpack_ms / 1e6 / peak,
-        "l2": "a 256 MB buffer is rewritten between timed launches; each launch includes a torch.empty of its output",
+        "l2": "inputs and outputs (0.94 GB + 0.12 GB) are larger than L2; ten launches back to back",
     }
 
 

@@ -11,7 +11,7 @@
 namespace g2d {
 
 // Eight consecutive entries of a row of a matrix whose column stride is 0 (one value per row), 1 or anything else;
-// entries past the row's end read as `fill`.  `vec` promises a unit column stride, eight whole entries and 16-byte alignment.
+// entries past the row's end read as `fill`.  `vec` promises a unit column stride and 32-byte alignment of every group of eight.
 template <typename F>
 __device__ __forceinline__ void load8(const F *__restrict__ row, int64_t c0, int64_t cs, int64_t n, bool vec, F fill, F (&v)[8]) {
     if (cs == 0) {
@@ -20,8 +20,10 @@ __device__ __forceinline__ void load8(const F *__restrict__ row, int64_t c0, int
         for (int x = 0; x < 8; ++x) v[x] = one;
     } else if (vec && c0 + 8 <= n) {
         if constexpr (sizeof(F) == 4) {
-            const float4 a = *reinterpret_cast<const float4 *>(row + c0), b = *reinterpret_cast<const float4 *>(row + c0 + 4);
-            v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+            // one 32-byte load: consecutive lanes then cover whole sectors with every instruction
+            asm volatile("ld.global.v8.f32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                         : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]), "=f"(v[4]), "=f"(v[5]), "=f"(v[6]), "=f"(v[7])
+                         : "l"(row + c0));
         } else {
 #pragma unroll
             for (int x = 0; x < 8; x += 2) {
@@ -35,33 +37,68 @@ __device__ __forceinline__ void load8(const F *__restrict__ row, int64_t c0, int
     }
 }
 
+// z / s for the code of a value on the quantizer's grid.  float: the product with the correctly rounded reciprocal
+// plus one residual correction, which is the IEEE quotient except, rarely, in its last bit; a rounded value lies
+// within an ulp of (code - zero point) * scale, so its code never depends on that bit.  double: IEEE division.
+__device__ __forceinline__ float reciprocal(float s) { return __frcp_rn(s); }
+__device__ __forceinline__ double reciprocal(double) { return 0.0; }
+__device__ __forceinline__ float quotient(float z, float s, float rc) {
+    const float q0 = z * rc;
+    const float q1 = fmaf(fmaf(-q0, s, z), rc, q0);
+    return (fabsf(s) > 1e-30f && fabsf(s) < 1e30f && fabsf(q1) < 1e30f) ? q1 : div_rn(z, s);  // extreme scales take the exact path
+}
+__device__ __forceinline__ double quotient(double z, double s, double) { return div_rn(z, s); }
+__device__ __forceinline__ int to_int_rn(float a) { return __float2int_rn(a); }
+__device__ __forceinline__ int to_int_rn(double a) { return __double2int_rn(a); }
+
 template <typename F>
-__global__ void pack_codes_kernel(int64_t m, int64_t n, const F *__restrict__ z, const F *__restrict__ scale, int64_t srs, int64_t scs,
-                                  const F *__restrict__ zero, int64_t zrs, int64_t zcs, F qmin, int bits, unsigned char *__restrict__ out,
-                                  int64_t row_bytes) {
-    const int64_t groups = ceil_div(n, (int64_t)8), total = m * groups;
+__global__ void __launch_bounds__(256) pack_codes_kernel(int64_t m, int64_t n, const F *__restrict__ z, const F *__restrict__ scale, int64_t srs,
+                                                         int64_t scs, const F *__restrict__ zero, int64_t zrs, int64_t zcs, F qmin, int bits,
+                                                         unsigned char *__restrict__ out, int64_t row_bytes) {
+    // a thread takes two neighbouring groups of eight entries; all its loads are issued before any arithmetic
+    const int64_t groups = ceil_div(n, (int64_t)8), pairs = ceil_div(groups, (int64_t)2), total = m * pairs;
     const unsigned top = (1u << bits) - 1u;
-    const bool vec_z = n % 4 == 0 && reinterpret_cast<uintptr_t>(z) % 16 == 0;
-    const bool vec_s = scs == 1 && srs % 4 == 0 && reinterpret_cast<uintptr_t>(scale) % 16 == 0;
-    const bool vec_o = zcs == 1 && zrs % 4 == 0 && reinterpret_cast<uintptr_t>(zero) % 16 == 0;
+    const int qmin_int = to_int_rn(qmin);  // an integer by contract
+    const bool vec_z = n % 8 == 0 && reinterpret_cast<uintptr_t>(z) % 32 == 0;
+    const bool vec_s = scs == 1 && srs % 8 == 0 && reinterpret_cast<uintptr_t>(scale) % 32 == 0;
+    const bool vec_o = zcs == 1 && zrs % 8 == 0 && reinterpret_cast<uintptr_t>(zero) % 32 == 0;
+    const bool wide = (bits == 2 || bits == 4 || bits == 8) && row_bytes % bits == 0 && reinterpret_cast<uintptr_t>(out) % bits == 0;
     for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (int64_t)gridDim.x * blockDim.x) {
-        const int64_t r = t / groups, c0 = (t % groups) * 8;
-        F zv[8], sv[8], ov[8];
-        load8(z + r * n, c0, 1, n, vec_z, (F)0, zv);
-        load8(scale + r * srs, c0, scs, n, vec_s, (F)1, sv);
-        load8(zero + r * zrs, c0, zcs, n, vec_o, (F)0, ov);
-        unsigned long long field = 0;  // 8 codes of at most 8 bits
+        const int64_t r = t / pairs, g0 = (t % pairs) * 2;
+        F zv[2][8], sv[2][8], ov[2][8];
 #pragma unroll
-        for (int x = 0; x < 8; ++x) {
-            if (c0 + x < n) {
-                const F q = rint_even(add_rn(div_rn(zv[x], sv[x]), ov[x])) - qmin;
-                const unsigned code = q < (F)0 ? 0u : (q > (F)top ? top : (unsigned)q);
-                field |= (unsigned long long)code << (x * bits);
+        for (int h = 0; h < 2; ++h) {
+            const int64_t c0 = (g0 + h) * 8;
+            load8(z + r * n, c0, 1, n, vec_z, (F)0, zv[h]);
+            load8(scale + r * srs, c0, scs, n, vec_s, (F)1, sv[h]);
+            load8(zero + r * zrs, c0, zcs, n, vec_o, (F)0, ov[h]);
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int64_t c0 = (g0 + h) * 8;
+            if (c0 >= n) continue;
+            const F row_rc = reciprocal(sv[h][0]);  // shared by the group when the scale is per row
+            unsigned long long field = 0;           // 8 codes of at most 8 bits
+#pragma unroll
+            for (int x = 0; x < 8; ++x) {
+                if (c0 + x < n) {
+                    const F rc = scs == 0 ? row_rc : reciprocal(sv[h][x]);
+                    // round half to even and convert in one step; saturating, so values far outside clamp as they should
+                    const long long q = (long long)to_int_rn(add_rn(quotient(zv[h][x], sv[h][x], rc), ov[h][x])) - (long long)qmin_int;
+                    const unsigned code = q < 0 ? 0u : (q > (long long)top ? top : (unsigned)q);
+                    field |= (unsigned long long)code << (x * bits);
+                }
+            }
+            unsigned char *dst = out + r * row_bytes + (c0 / 8) * bits;
+            const int64_t left = row_bytes - (c0 / 8) * bits;  // a ragged last group owns fewer than `bits` bytes
+            if (wide && left >= bits) {  // the group's bytes as one aligned word
+                if (bits == 4) *reinterpret_cast<unsigned *>(dst) = (unsigned)field;
+                else if (bits == 8) *reinterpret_cast<unsigned long long *>(dst) = field;
+                else *reinterpret_cast<unsigned short *>(dst) = (unsigned short)field;
+            } else {
+                for (int b = 0; b < bits && b < left; ++b) dst[b] = (unsigned char)(field >> (8 * b));
             }
         }
-        unsigned char *dst = out + r * row_bytes + (c0 / 8) * bits;
-        const int64_t left = row_bytes - (c0 / 8) * bits;  // a ragged last group owns fewer than `bits` bytes
-        for (int b = 0; b < bits && b < left; ++b) dst[b] = (unsigned char)(field >> (8 * b));
     }
 }
 
@@ -71,15 +108,22 @@ __global__ void unpack_codes_kernel(int64_t m, int64_t n, const unsigned char *_
                                     int64_t zcs, F qmin, int bits, F *__restrict__ z) {
     const int64_t groups = ceil_div(n, (int64_t)8), total = m * groups;
     const unsigned top = (1u << bits) - 1u;
-    const bool vec_z = n % 4 == 0 && reinterpret_cast<uintptr_t>(z) % 16 == 0;
-    const bool vec_s = scs == 1 && srs % 4 == 0 && reinterpret_cast<uintptr_t>(scale) % 16 == 0;
-    const bool vec_o = zcs == 1 && zrs % 4 == 0 && reinterpret_cast<uintptr_t>(zero) % 16 == 0;
+    const bool vec_z = n % 8 == 0 && reinterpret_cast<uintptr_t>(z) % 32 == 0;
+    const bool vec_s = scs == 1 && srs % 8 == 0 && reinterpret_cast<uintptr_t>(scale) % 32 == 0;
+    const bool vec_o = zcs == 1 && zrs % 8 == 0 && reinterpret_cast<uintptr_t>(zero) % 32 == 0;
+    const bool wide = (bits == 2 || bits == 4 || bits == 8) && row_bytes % bits == 0 && reinterpret_cast<uintptr_t>(codes) % bits == 0;
     for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (int64_t)gridDim.x * blockDim.x) {
         const int64_t r = t / groups, c0 = (t % groups) * 8;
         const unsigned char *src = codes + r * row_bytes + (c0 / 8) * bits;
         const int64_t left = row_bytes - (c0 / 8) * bits;
         unsigned long long field = 0;
-        for (int b = 0; b < bits && b < left; ++b) field |= (unsigned long long)src[b] << (8 * b);
+        if (wide && left >= bits) {
+            if (bits == 4) field = *reinterpret_cast<const unsigned *>(src);
+            else if (bits == 8) field = *reinterpret_cast<const unsigned long long *>(src);
+            else field = *reinterpret_cast<const unsigned short *>(src);
+        } else {
+            for (int b = 0; b < bits && b < left; ++b) field |= (unsigned long long)src[b] << (8 * b);
+        }
         F sv[8], ov[8], zv[8];
         load8(scale + r * srs, c0, scs, n, vec_s, (F)1, sv);
         load8(zero + r * zrs, c0, zcs, n, vec_o, (F)0, ov);
@@ -89,9 +133,9 @@ __global__ void unpack_codes_kernel(int64_t m, int64_t n, const unsigned char *_
             zv[x] = mul_rn(sub_rn(q, ov[x]), sv[x]);  // as the affine quantizer forms its value
         }
         if (vec_z && c0 + 8 <= n && sizeof(F) == 4) {
-            float4 *dst = reinterpret_cast<float4 *>(z + r * n + c0);
-            dst[0] = make_float4((float)zv[0], (float)zv[1], (float)zv[2], (float)zv[3]);
-            dst[1] = make_float4((float)zv[4], (float)zv[5], (float)zv[6], (float)zv[7]);
+            asm volatile("st.global.v8.f32 [%8], {%0, %1, %2, %3, %4, %5, %6, %7};" ::"f"((float)zv[0]), "f"((float)zv[1]), "f"((float)zv[2]),
+                         "f"((float)zv[3]), "f"((float)zv[4]), "f"((float)zv[5]), "f"((float)zv[6]), "f"((float)zv[7]), "l"(z + r * n + c0)
+                         : "memory");
         } else {
 #pragma unroll
             for (int x = 0; x < 8; ++x)
