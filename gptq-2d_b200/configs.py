@@ -4,6 +4,7 @@
     python gptq-2d_b200/configs.py --config c3        # 4096 x 14336 as [16, 256, 14336], three factors, 2-bit HYB trellis
     python gptq-2d_b200/configs.py --config c3 --divide 4   # every dimension but the super-entry shrunk (short run)
     python gptq-2d_b200/configs.py --config pack      # INT4 codes of an 8192 x 28672 matrix packed and unpacked
+    python gptq-2d_b200/configs.py --config prep      # the factor preparation of an 8192 x 8192 layer alone
 
 Seeded synthetic inputs with the shapes and value distributions of the configurations (``synthetic.py``); everything
 goes through the public entry points.  Configuration 3 rounds ``(1, 16, 16)`` super-entries of the three-factor problem,
@@ -150,7 +151,12 @@ def pack(divide: int, device) -> dict:
     assert torch.equal(P.unpack_codes(codes, scale, zero, qmin=-8, bits=4, n=n), z)
     def timed(fn, repeats=10):  # back to back: the host side of a call hides behind the previous launch
         fn()
-        return _timed(lambda: [fn() for _ in range(repeats)])[1] / repeats
+
+        def loop():
+            for _ in range(repeats):
+                fn()  # the result is dropped at once, so every call reuses the same block of the caching allocator
+
+        return _timed(loop)[1] / repeats
 
     pack_ms = timed(lambda: P.pack_codes(z, scale, zero, qmin=-8, bits=4))
     unpack_ms = timed(lambda: P.unpack_codes(codes, scale, zero, qmin=-8, bits=4, n=n))
@@ -169,9 +175,31 @@ def pack(divide: int, device) -> dict:
     }
 
 
+def prep(divide: int, device) -> dict:
+    """The factor preparation alone: both factors of an 8192 x 8192 layer in shared launches, and one factor."""
+    import torch
+
+    import kron_factors as K
+    import synthetic
+
+    n = 8192 // divide
+    generator = torch.Generator(device=device).manual_seed(5)
+    g = synthetic.hessian_factor(n, n, 1.0, 0.01, generator, device)
+    h = synthetic.hessian_factor(n, n, 1.0, 0.01, generator, device)
+    K.feedback_factors_from_grams(g, h, check=True)
+    _, pair_ms = _timed(lambda: K.feedback_factors_from_grams(g, h))
+    K.ldl_of_inverse(g)
+    l, single_ms = _timed(lambda: K.ldl_of_inverse(g, check=False))
+    residual = (l.T.double() @ g.double() @ l.double())
+    off = residual - torch.diag(residual.diagonal())
+    return {"config": "prep", "n": n, "pair_ms": pair_ms, "single_ms": single_ms, "pair_tflops": 2 * (2 * n ** 3 / 3) / pair_ms / 1e9,
+            "single_tflops": (2 * n ** 3 / 3) / single_ms / 1e9,
+            "off_diagonal_of_LtGL_relative": (off.abs().max() / residual.diagonal().abs().max()).item()}
+
+
 def main() -> None:
     parser = argparse.ArgumentParser()
-    parser.add_argument("--config", required=True, choices=("c2", "c3", "pack"))
+    parser.add_argument("--config", required=True, choices=("c2", "c3", "pack", "prep"))
     parser.add_argument("--divide", type=int, default=1, help="shrink the dimensions by this factor")
     args = parser.parse_args()
     sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
@@ -180,7 +208,7 @@ def main() -> None:
     if not torch.cuda.is_available():
         raise SystemExit("configs.py needs a CUDA device (B200); there is no CPU path")
     device = torch.device("cuda", 0)
-    print(json.dumps({"c2": config2, "c3": config3, "pack": pack}[args.config](args.divide, device)))
+    print(json.dumps({"c2": config2, "c3": config3, "pack": pack, "prep": prep}[args.config](args.divide, device)))
 
 
 if __name__ == "__main__":

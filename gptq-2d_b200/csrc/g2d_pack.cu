@@ -51,10 +51,11 @@ __device__ __forceinline__ double quotient(double z, double s, double) { return 
 __device__ __forceinline__ int to_int_rn(float a) { return __float2int_rn(a); }
 __device__ __forceinline__ int to_int_rn(double a) { return __double2int_rn(a); }
 
-template <typename F>
-__global__ void __launch_bounds__(256) pack_codes_kernel(int64_t m, int64_t n, const F *__restrict__ z, const F *__restrict__ scale, int64_t srs,
-                                                         int64_t scs, const F *__restrict__ zero, int64_t zrs, int64_t zcs, F qmin, int bits,
-                                                         unsigned char *__restrict__ out, int64_t row_bytes) {
+template <typename F, int BITS>
+__global__ void __launch_bounds__(256, 3) pack_codes_kernel(int64_t m, int64_t n, const F *__restrict__ z, const F *__restrict__ scale, int64_t srs,
+                                                            int64_t scs, const F *__restrict__ zero, int64_t zrs, int64_t zcs, F qmin,
+                                                            unsigned char *__restrict__ out, int64_t row_bytes) {
+    constexpr int bits = BITS;  // the field width as a compile-time constant: shifts and store widths are immediates
     // a thread takes two neighbouring groups of eight entries; all its loads are issued before any arithmetic
     const int64_t groups = ceil_div(n, (int64_t)8), pairs = ceil_div(groups, (int64_t)2), total = m * pairs;
     const unsigned top = (1u << bits) - 1u;
@@ -78,17 +79,19 @@ __global__ void __launch_bounds__(256) pack_codes_kernel(int64_t m, int64_t n, c
             const int64_t c0 = (g0 + h) * 8;
             if (c0 >= n) continue;
             const F row_rc = reciprocal(sv[h][0]);  // shared by the group when the scale is per row
-            unsigned long long field = 0;           // 8 codes of at most 8 bits
+            unsigned half_field[2] = {0u, 0u};      // four codes of at most 8 bits each
 #pragma unroll
             for (int x = 0; x < 8; ++x) {
                 if (c0 + x < n) {
                     const F rc = scs == 0 ? row_rc : reciprocal(sv[h][x]);
-                    // round half to even and convert in one step; saturating, so values far outside clamp as they should
-                    const long long q = (long long)to_int_rn(add_rn(quotient(zv[h][x], sv[h][x], rc), ov[h][x])) - (long long)qmin_int;
-                    const unsigned code = q < 0 ? 0u : (q > (long long)top ? top : (unsigned)q);
-                    field |= (unsigned long long)code << (x * bits);
+                    // round half to even and convert in one step (the conversion saturates); the clamp is done on
+                    // integers: the field's bounds moved by qmin, both well inside the int range
+                    int q = to_int_rn(add_rn(quotient(zv[h][x], sv[h][x], rc), ov[h][x]));
+                    q = q < qmin_int ? qmin_int : (q > qmin_int + (int)top ? qmin_int + (int)top : q);
+                    half_field[x >> 2] |= (unsigned)(q - qmin_int) << ((x & 3) * bits);
                 }
             }
+            const unsigned long long field = (unsigned long long)half_field[0] | ((unsigned long long)half_field[1] << (4 * bits));
             unsigned char *dst = out + r * row_bytes + (c0 / 8) * bits;
             const int64_t left = row_bytes - (c0 / 8) * bits;  // a ragged last group owns fewer than `bits` bytes
             if (wide && left >= bits) {  // the group's bytes as one aligned word
@@ -166,12 +169,21 @@ extern "C" int g2d_pack_codes(int dtype, int64_t m, int64_t n, const void *z, co
     const int status = pack_check(dtype, m, n, z, scale, zero, bits, codes, row_bytes);
     if (status != G2D_OK || m == 0 || n == 0) return status;
     cudaStream_t st = (cudaStream_t)stream;
-    if (dtype == G2D_F32)
-        pack_codes_kernel<float><<<pack_grid(m, n), 256, 0, st>>>(m, n, (const float *)z, (const float *)scale, scale_row_stride, scale_col_stride,
-                                                                 (const float *)zero, zero_row_stride, zero_col_stride, (float)qmin, bits, codes, row_bytes);
-    else
-        pack_codes_kernel<double><<<pack_grid(m, n), 256, 0, st>>>(m, n, (const double *)z, (const double *)scale, scale_row_stride, scale_col_stride,
-                                                                  (const double *)zero, zero_row_stride, zero_col_stride, qmin, bits, codes, row_bytes);
+    const unsigned grid = pack_grid(m, n);
+#define G2D_PACK_CASE(B)                                                                                                                     \
+    case B:                                                                                                                                  \
+        if (dtype == G2D_F32)                                                                                                                \
+            pack_codes_kernel<float, B><<<grid, 256, 0, st>>>(m, n, (const float *)z, (const float *)scale, scale_row_stride, scale_col_stride, \
+                                                              (const float *)zero, zero_row_stride, zero_col_stride, (float)qmin, codes, row_bytes); \
+        else                                                                                                                                 \
+            pack_codes_kernel<double, B><<<grid, 256, 0, st>>>(m, n, (const double *)z, (const double *)scale, scale_row_stride, scale_col_stride, \
+                                                               (const double *)zero, zero_row_stride, zero_col_stride, qmin, codes, row_bytes); \
+        break;
+    switch (bits) {
+        G2D_PACK_CASE(1) G2D_PACK_CASE(2) G2D_PACK_CASE(3) G2D_PACK_CASE(4) G2D_PACK_CASE(5) G2D_PACK_CASE(6) G2D_PACK_CASE(7) G2D_PACK_CASE(8)
+    default: return G2D_ERR_BAD_ARGUMENT;
+    }
+#undef G2D_PACK_CASE
     return check_launch();
 }
 
