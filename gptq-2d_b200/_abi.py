@@ -70,6 +70,8 @@ _SIGNATURES = {
     "g2d_trellis_quantize": (ctypes.c_int, [ctypes.c_int, _i64, _i32, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp, ctypes.c_size_t, _vp]),
     "g2d_ldl_workspace_bytes": (ctypes.c_int, [ctypes.c_int, _i64, ctypes.POINTER(ctypes.c_size_t)]),
     "g2d_ldl_of_inverse": (ctypes.c_int, [ctypes.c_int, _i64, _vp, _i32, _vp, _vp, _vp, ctypes.c_size_t, _vp]),
+    "g2d_gram_workspace_bytes": (ctypes.c_int, [_i64, _i64, ctypes.POINTER(ctypes.c_size_t)]),
+    "g2d_gram_accumulate": (ctypes.c_int, [_i64, _i64, _vp, ctypes.c_float, _vp, _vp, _vp, ctypes.c_size_t, _vp]),
     "g2d_pack_codes": (ctypes.c_int, [ctypes.c_int, _i64, _i64, _vp, _vp, _i64, _i64, _vp, _i64, _i64, ctypes.c_double, _i32, _vp, _i64, _vp]),
     "g2d_unpack_codes": (ctypes.c_int, [ctypes.c_int, _i64, _i64, _vp, _i64, _vp, _i64, _i64, _vp, _i64, _i64, ctypes.c_double, _i32, _vp, _vp]),
     "g2d_ldl_of_inverse_pair": (ctypes.c_int, [ctypes.c_int, _i64, _vp, _i32, _vp, _vp, ctypes.c_size_t,

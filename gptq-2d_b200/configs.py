@@ -5,6 +5,7 @@
     python gptq-2d_b200/configs.py --config c3 --divide 4   # every dimension but the super-entry shrunk (short run)
     python gptq-2d_b200/configs.py --config pack      # INT4 codes of an 8192 x 28672 matrix packed and unpacked
     python gptq-2d_b200/configs.py --config prep      # the factor preparation of an 8192 x 8192 layer alone
+    python gptq-2d_b200/configs.py --config gram      # Hessian-factor accumulation, 8192 samples of 8192 channels
 
 Seeded synthetic inputs with the shapes and value distributions of the configurations (``synthetic.py``); everything
 goes through the public entry points.  Configuration 3 rounds ``(1, 16, 16)`` super-entries of the three-factor problem,
@@ -197,9 +198,30 @@ def prep(divide: int, device) -> dict:
             "off_diagonal_of_LtGL_relative": (off.abs().max() / residual.diagonal().abs().max()).item()}
 
 
+def gram(divide: int, device) -> dict:
+    """Hessian-factor accumulation h += x^T x / k for 8192 samples of 8192 channels on the tensor cores."""
+    import torch
+
+    import kron_factors as K
+
+    n = k = 8192 // divide
+    generator = torch.Generator(device=device).manual_seed(6)
+    x = torch.randn(k, n, generator=generator, device=device) * torch.exp(torch.randn(n, generator=generator, device=device))
+    h = torch.zeros(n, n, device=device)
+    K.accumulate_gram(h, x, 1.0 / k)
+    want = x.double().T @ x.double() / k
+    error = ((h.double() - want).abs().max() / want.abs().max()).item()
+    plain = ((x.T @ x / k).double() - want).abs().max().item() / want.abs().max().item()
+    _, ms = _timed(lambda: K.accumulate_gram(h, x, 1.0 / k))
+    _, torch_ms = _timed(lambda: h.addmm_(x.T, x, alpha=1.0 / k))
+    flops = float(n) * (n + 1) * k  # the lower triangle with the diagonal, two flops per multiply-add
+    return {"config": "gram", "n": n, "k": k, "ms": ms, "tflops": flops / ms / 1e9, "torch_addmm_ms": torch_ms,
+            "relative_error": error, "relative_error_of_torch_fp32": plain}
+
+
 def main() -> None:
     parser = argparse.ArgumentParser()
-    parser.add_argument("--config", required=True, choices=("c2", "c3", "pack", "prep"))
+    parser.add_argument("--config", required=True, choices=("c2", "c3", "pack", "prep", "gram"))
     parser.add_argument("--divide", type=int, default=1, help="shrink the dimensions by this factor")
     args = parser.parse_args()
     sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
@@ -208,7 +230,7 @@ def main() -> None:
     if not torch.cuda.is_available():
         raise SystemExit("configs.py needs a CUDA device (B200); there is no CPU path")
     device = torch.device("cuda", 0)
-    print(json.dumps({"c2": config2, "c3": config3, "pack": pack, "prep": prep}[args.config](args.divide, device)))
+    print(json.dumps({"c2": config2, "c3": config3, "pack": pack, "prep": prep, "gram": gram}[args.config](args.divide, device)))
 
 
 if __name__ == "__main__":

@@ -46,6 +46,28 @@ def ldl_of_inverse(M: torch.Tensor, size: int = 1, check: bool = True) -> torch.
     return out
 
 
+@torch.no_grad()
+def accumulate_gram(h: torch.Tensor, x: torch.Tensor, alpha: float = 1.0) -> torch.Tensor:
+    """``h += alpha * x.T @ x`` in place on the tensor cores, at float32 fidelity: the Hessian-factor accumulation that
+    precedes ``ldl_of_inverse`` in a pipeline (``x [k samples, n channels]``, ``h [n, n]``, float32, CUDA, contiguous,
+    ``n`` a multiple of 4).  The reference leaves this step to the caller (demo.ipynb:103-106)."""
+    assert h.is_cuda and x.is_cuda and h.device == x.device, "the Gram accumulation requires CUDA tensors (there is no CPU path)"
+    assert h.dtype == torch.float32 and x.dtype == torch.float32, "float32 only"
+    assert x.dim() == 2 and h.shape == (x.size(1), x.size(1)) and h.is_contiguous() and x.is_contiguous(), "expected x [k, n] and h [n, n], contiguous"
+    k, n = x.shape
+    assert n % 4 == 0, "the channel count must be a multiple of 4"
+    if n == 0 or k == 0:
+        return h
+    lib = _abi.library()
+    need = ctypes.c_size_t()
+    _abi.check(lib.g2d_gram_workspace_bytes(n, k, ctypes.byref(need)), "g2d_gram_workspace_bytes")
+    workspace = torch.empty(need.value, dtype=torch.uint8, device=h.device)
+    with torch.cuda.device(h.device):
+        _abi.check(lib.g2d_gram_accumulate(n, k, x.data_ptr(), float(alpha), h.data_ptr(), None, workspace.data_ptr(), need.value,
+                                           _abi.stream_of(h)), "g2d_gram_accumulate")
+    return h
+
+
 def feedback_factors(A: torch.Tensor, B: torch.Tensor, super_entry_shape: tuple[int, int] = (1, 1)) -> tuple[torch.Tensor, torch.Tensor]:
     """L and U with ``G^{-1} = L Lambda_L L^T`` and ``H^{-1} = U^T Lambda_U U`` for the Grams ``G = A^T A`` and
     ``H = B B^T``, with ``p x p`` and ``q x q`` identity diagonal blocks for ``p x q`` super-entries."""

@@ -186,6 +186,15 @@ int g2d_ldl_of_inverse_pair(int dtype, int64_t n0, void *a0, int32_t size0, void
                             size_t workspace0_bytes, int64_t n1, void *a1, int32_t size1, void *out1,
                             void *workspace1, size_t workspace1_bytes, int32_t *status_flags, void *stream);
 
+/* Hessian-factor accumulation h += alpha * x^T x on the tensor cores: x is [k samples, n channels] float, h is
+ * [n, n] float (both row-major, n a multiple of 4).  No counterpart in the reference, which takes its Hessian
+ * factors from the caller (demo.ipynb:103-106 forms them with a plain matrix product); it is the step before
+ * g2d_ldl_of_inverse in a pipeline.  workspace: g2d_gram_workspace_bytes(); status_flag (device int32, may be
+ * NULL) is set to -1 if a bounded wait inside the kernel ran out. */
+int g2d_gram_workspace_bytes(int64_t n, int64_t k, size_t *bytes);
+int g2d_gram_accumulate(int64_t n, int64_t k, const float *x, float alpha, float *h, int32_t *status_flag,
+                        void *workspace, size_t workspace_bytes, void *stream);
+
 /* Packed integer codes of a rounded matrix z [m, n] and back.  The reference has no counterpart: it returns
  * dequantised floats and notes that the code can be recovered from them (quantizer_trellis.py:11-14; for the
  * affine quantizer, quantizer_int.py:63-83, code = rint(z / scale + zero point)).  Entry j of a row is the

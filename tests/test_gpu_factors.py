@@ -111,3 +111,19 @@ def test_d_sided_golden(K):
         factors = [cuda(g[f"l{k}_{d}"]) for d in range(x.dim())]
         z = K.gptq_d_sided(x, factors)
         assert torch.equal(z.cpu(), torch.from_numpy(g[f"z{k}"])), k
+
+
+@pytest.mark.parametrize("k, n", [(1000, 512), (37, 132), (4096, 1100), (64, 4)])
+def test_gram_accumulation(K, k, n):
+    """h += alpha x^T x on the tensor cores stays at float32 fidelity (3xTF32) and is symmetric bit for bit."""
+    gen = torch.Generator(device="cuda").manual_seed(k + n)
+    x = torch.randn(k, n, generator=gen, device="cuda") * torch.exp(torch.randn(n, generator=gen, device="cuda"))
+    h0 = torch.randn(n, n, generator=gen, device="cuda")
+    h0 = h0 + h0.T
+    h = K.accumulate_gram(h0.clone(), x, alpha=1.0 / k)
+    want = h0.double() + x.double().T @ x.double() / k
+    scale = want.abs().max().item()
+    assert (h.double() - want).abs().max().item() <= 3e-6 * scale
+    assert torch.equal(h, h.T)
+    again = K.accumulate_gram(h0.clone(), x, alpha=1.0 / k)
+    assert torch.equal(h, again)  # one owner per entry: run-to-run identical
