@@ -16,7 +16,9 @@ import sys
 import numpy as np
 import torch
 
-REF = os.environ.get("GPTQ2D_REF", "/root/reference")
+REF = os.environ.get("GPTQ2D_REF")
+if not REF:
+    raise SystemExit("set GPTQ2D_REF to a checkout of the reference project (its gptq_2d.py is imported from there)")
 sys.path.insert(0, REF)
 HERE = os.path.dirname(os.path.abspath(__file__))
 
