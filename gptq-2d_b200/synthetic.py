@@ -16,13 +16,18 @@ def hessian_factor(dim: int, samples: int, sigma_h: float, damp: float, generato
     """``X^T X / samples + lambda I`` for seeded heavy-tailed activations, accumulated in row chunks."""
     channel = torch.exp(sigma_h * torch.randn(dim, generator=generator, device=device, dtype=dtype))
     h = torch.zeros(dim, dim, device=device, dtype=dtype)
+    on_tensor_cores = h.is_cuda and dtype == torch.float32 and dim % 4 == 0  # the library's own accumulation kernel
     done = 0
     while done < samples:
         rows = min(chunk, samples - done)
         x = torch.randn(rows, dim, generator=generator, device=device, dtype=dtype) * channel
-        h.addmm_(x.T, x)
+        if on_tensor_cores:
+            import kron_factors
+
+            kron_factors.accumulate_gram(h, x, 1.0 / samples)
+        else:
+            h.addmm_(x.T, x, alpha=1.0 / samples)
         done += rows
-    h /= samples
     h.diagonal().add_(damp * h.diagonal().mean())
     return h
 
