@@ -211,8 +211,11 @@ def quantize_matrix(item: dict, device, pipeline: LayerPipeline | None = None):
         on_device["objective"] = ((g.double() @ r) * (r @ h.double())).sum()
         on_device["objective_rtn"] = ((g.double() @ r0) * (r0 @ h.double())).sum()
 
+    ready = torch.cuda.Event()
+    ready.record(torch.cuda.current_stream(device))
+
     def finish() -> dict:
-        torch.cuda.synchronize(device)
+        ready.synchronize()  # this matrix only: the next one may already be running
         stats = {
             **item, "prep_ms": events[0].elapsed_time(events[1]) if pipeline is None else None,
             "sweep_ms": events[1].elapsed_time(events[2]),
@@ -226,16 +229,72 @@ def quantize_matrix(item: dict, device, pipeline: LayerPipeline | None = None):
     return finish() if pipeline is None else finish
 
 
+def read_journal(path: str | None) -> dict:
+    """Statistics of the matrices a previous run finished, keyed by (block, name); lines that do not parse (a run killed
+    in the middle of a write) are dropped."""
+    done: dict = {}
+    if path and os.path.exists(path):
+        with open(path) as f:
+            for line in f:
+                try:
+                    stats = json.loads(line)
+                    done[(stats["block"], stats["name"])] = stats
+                except (ValueError, KeyError):
+                    continue
+    return done
+
+
 def run(items: list[dict], process: Callable[[dict], dict], *, rank: int, world: int, gather: Callable | None = None,
-        barrier: Callable | None = None) -> dict | None:
+        barrier: Callable | None = None, journal: str | None = None) -> dict | None:
     """Process this rank's share; rank 0 returns the summary of the whole set.  ``gather(obj)`` must return the list
-    of every rank's object on rank 0 (None elsewhere); ``barrier()`` aligns the ranks before the clock starts."""
+    of every rank's object on rank 0 (None elsewhere); ``barrier()`` aligns the ranks before the clock starts.
+
+    With a ``journal`` (a path; every rank appends to ``<journal>.<rank>``) each finished matrix is written down at
+    once, and matrices that any rank's journal of an earlier run already holds are not processed again: a set that was
+    interrupted resumes where it stopped, whatever the number of ranks of the new run."""
     share = partition(items, world)[rank]
+    finished: dict = {}
+    if journal:
+        directory, prefix = os.path.split(journal)
+        for name in sorted(os.listdir(directory or ".")):
+            if name.startswith(prefix + "."):
+                finished.update(read_journal(os.path.join(directory, name)))
+    log = None
+    if journal:
+        mine = f"{journal}.{rank}"
+        cut_off = False
+        if os.path.exists(mine) and os.path.getsize(mine) > 0:
+            with open(mine, "rb") as f:
+                f.seek(-1, os.SEEK_END)
+                cut_off = f.read(1) != b"\n"  # a run killed in the middle of a line
+        log = open(mine, "a")
+        if cut_off:
+            log.write("\n")
+
+    def settle(entry):  # statistics of a matrix: fetched (a pipelined process hands back a fetcher) and written down
+        stats = entry() if callable(entry) else entry
+        if log is not None:
+            log.write(json.dumps(stats) + "\n")
+            log.flush()
+        return stats
+
     if barrier is not None:
         barrier()
     start = time.perf_counter()
-    results = [process(item) for item in share]
-    results = [r() if callable(r) else r for r in results]  # a pipelined process hands back fetchers of its statistics
+    results, pending = [], None
+    for item in share:
+        key = (item["block"], item["name"])
+        if key in finished:
+            results.append({**finished[key], "resumed": True})
+            continue
+        entry = process(item)
+        if pending is not None:  # one behind: the host has enqueued the next matrix before it waits for this one
+            results.append(settle(pending))
+        pending = entry
+    if pending is not None:
+        results.append(settle(pending))
+    if log is not None:
+        log.close()
     busy = time.perf_counter() - start
     if barrier is not None:
         barrier()
@@ -264,6 +323,7 @@ def run(items: list[dict], process: Callable[[dict], dict], *, rank: int, world:
         "all_codes_in_range": all(r.get("codes_in_range", True) for r in results),
         "objective_vs_rtn": [r["objective_vs_rtn"] for r in results if "objective_vs_rtn" in r][:8],
         "weights": sum(r["m"] * r["n"] for r in results),
+        "resumed": sum(1 for r in results if r.get("resumed")),
     }
 
 
@@ -272,6 +332,7 @@ def main() -> None:
     parser.add_argument("--blocks", type=int, default=80)
     parser.add_argument("--divide", type=int, default=1, help="shrink every dimension by this factor")
     parser.add_argument("--serial", action="store_true", help="one layer at a time (per-part timings) instead of two in flight")
+    parser.add_argument("--journal", default=None, help="path prefix of the per-rank journals: finished matrices are written down and skipped on a rerun")
     args = parser.parse_args()
     sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
     import torch
@@ -297,7 +358,7 @@ def main() -> None:
     quantize_matrix({"block": -1, "name": "warm-up", "m": 384, "n": 512, "seed": 1}, device)
     pipeline = None if args.serial else LayerPipeline(device)
     summary = run(layer_list(args.blocks, args.divide), functools.partial(quantize_matrix, device=device, pipeline=pipeline), rank=rank,
-                  world=world, gather=gather, barrier=barrier)
+                  world=world, gather=gather, barrier=barrier, journal=args.journal)
     if summary is not None:
         print(json.dumps(summary))
     if world > 1:

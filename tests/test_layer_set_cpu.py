@@ -55,3 +55,51 @@ def test_two_ranks_over_gloo():
         summary = json.load(open(out))
     assert summary["matrices"] == 21 and summary["n_gpus"] == 2 and len(summary["busy_s"]) == 2
     assert summary["mean_ms_by_shape"]["448x128"]["count"] == 6 and summary["all_finite"]
+
+
+def test_journal_resumes_an_interrupted_set():
+    """A run that dies half way leaves a journal; the next run (here with another number of ranks) skips what is done."""
+    import json
+
+    import layer_set
+
+    items = layer_set.layer_list(2, divide=64)
+    calls = []
+
+    def process(item, fail_after=None):
+        if fail_after is not None and len(calls) >= fail_after:
+            raise RuntimeError("interrupted")
+        calls.append((item["block"], item["name"]))
+        stats = {**item, "prep_ms": 1.0, "sweep_ms": 2.0, "finite": True, "codes_in_range": True}
+        return lambda: stats  # as a pipelined process does: a fetcher
+
+    with tempfile.TemporaryDirectory() as tmp:
+        journal = os.path.join(tmp, "set.journal")
+        try:
+            layer_set.run(items, lambda item: process(item, fail_after=5), rank=0, world=1, journal=journal)
+        except RuntimeError:
+            pass
+        # the fifth matrix was enqueued but never settled: four are written down
+        assert len(layer_set.read_journal(journal + ".0")) == 4
+        with open(journal + ".0", "a") as f:
+            f.write('{"block": 1, "na')  # a line cut off by the kill
+        calls.clear()
+        stash = []
+
+        def gather_for(rank):
+            def gather(obj):
+                if rank == 1:
+                    stash.append(obj)
+                    return None
+                return [obj] + stash
+            return gather
+
+        assert layer_set.run(items, process, rank=1, world=2, journal=journal, gather=gather_for(1)) is None
+        summary = layer_set.run(items, process, rank=0, world=2, journal=journal, gather=gather_for(0))
+        assert len(calls) == len(items) - 4  # nothing done twice
+        assert summary["matrices"] == len(items) and summary["resumed"] == 4
+        done = {}
+        for name in os.listdir(tmp):
+            done.update(layer_set.read_journal(os.path.join(tmp, name)))
+        assert set(done) == {(i["block"], i["name"]) for i in items}
+        assert all(json.dumps(v) for v in done.values())
