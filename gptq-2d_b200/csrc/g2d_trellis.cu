@@ -32,6 +32,16 @@ __device__ __forceinline__ F local_cost(const F *__restrict__ table, int64_t s, 
 template <typename F>
 __device__ __forceinline__ F pos_inf() { return (F)INFINITY; }
 
+// the two values of a table entry in one load (V = 2: entries are pairs, naturally aligned)
+__device__ __forceinline__ void load_pair(const float *p, float &a, float &b) {
+    const float2 t = *reinterpret_cast<const float2 *>(p);
+    a = t.x; b = t.y;
+}
+__device__ __forceinline__ void load_pair(const double *p, double &a, double &b) {
+    const double2 t = *reinterpret_cast<const double2 *>(p);
+    a = t.x; b = t.y;
+}
+
 template <typename F, int R>
 __global__ void __launch_bounds__(VT) viterbi_kernel(int64_t rows, int T, const F *__restrict__ x, const F *__restrict__ table,
                                                      int Lbits, int shift, int V, int tail_biting, const F *__restrict__ scale,
@@ -69,29 +79,82 @@ __global__ void __launch_bounds__(VT) viterbi_kernel(int64_t rows, int T, const 
                     x1[r] = V == 2 ? xt[1] : (F)0;
                     ov[r] = seq_overlap[r];
                 }
-                for (int64_t g = tid; g < G; g += VT) {
+                const int Gi = (int)G;  // the states fit 32-bit arithmetic (L <= 24)
+                int ovi[R];
+#pragma unroll
+                for (int r = 0; r < R; ++r) ovi[r] = (int)ov[r];
+                // The common shape (sixteen predecessors, pairs of values, not the first step) has a path of its own:
+                // everything that the generic loop below derives per predecessor is a constant stride here.
+                const bool fast = H == 16 && V == 2 && t > 0 && (Gi & 15) == 0;
+                for (int g = tid; fast && g < Gi; g += VT) {
+                    const F *entry = table + 2 * g;            // predecessor h: + h * 2 Gi
+                    const F *before = prev + (g >> 4);         // its group minimum: + h * (Gi >> 4), + r * Gi
+                    const int table_stride = 2 * Gi, low_stride = Gi >> 4;
+                    F best[R];
+                    int arg[R];
+#pragma unroll
+                    for (int half_h = 0; half_h < 2; ++half_h) {
+                        F tt0[8], tt1[8];
+#pragma unroll
+                        for (int q = 0; q < 8; ++q) load_pair(entry + (half_h * 8 + q) * table_stride, tt0[q], tt1[q]);
+#pragma unroll
+                        for (int q = 0; q < 8; ++q) {
+                            const int h = half_h * 8 + q;
+#pragma unroll
+                            for (int r = 0; r < R; ++r) {
+                                const F d0 = sub_rn(tt0[q], x0[r]), d1 = sub_rn(tt1[q], x1[r]);
+                                const F c = add_rn(before[r * Gi + h * low_stride], add_rn(mul_rn(d0, d0), mul_rn(d1, d1)));
+                                if (h == 0 || c < best[r]) { best[r] = c; arg[r] = h; }
+                            }
+                        }
+                    }
+#pragma unroll
+                    for (int r = 0; r < R; ++r) {
+                        next[r * Gi + g] = best[r];
+                        if (row0 + r < rows) choices[((row0 + r) * slots + t) * G + g] = (uint8_t)arg[r];
+                    }
+                }
+                for (int g = tid; !fast && g < Gi; g += VT) {
                     F best[R];
                     int arg[R];
 #pragma unroll
                     for (int r = 0; r < R; ++r) { best[r] = pos_inf<F>(); arg[r] = 0; }
-                    for (int h = 0; h < H; ++h) {
-                        const int64_t s = (int64_t)h * G + g;
-                        const F t0 = table[s * V], t1 = V == 2 ? table[s * V + 1] : (F)0;
-                        const int64_t low = s >> shift;
+                    // the table entries of eight predecessors are fetched before any of them is used: a thread's loads
+                    // (L2 hits: the table is larger than L1) overlap instead of queueing behind the running minimum
+                    constexpr int HB = 8;
+                    for (int h0 = 0; h0 < H; h0 += HB) {
+                        F tt0[HB], tt1[HB];
 #pragma unroll
-                        for (int r = 0; r < R; ++r) {
-                            const F d0 = sub_rn(t0, x0[r]);
-                            F c = mul_rn(d0, d0);
+                        for (int q = 0; q < HB; ++q) {
+                            const int s = (h0 + q < H ? h0 + q : H - 1) * Gi + g;
                             if (V == 2) {
-                                const F d1 = sub_rn(t1, x1[r]);
-                                c = add_rn(c, mul_rn(d1, d1));
-                            }
-                            if (t == 0) {
-                                if (ov[r] >= 0 && low != ov[r]) c = pos_inf<F>();
+                                load_pair(table + 2 * s, tt0[q], tt1[q]);
                             } else {
-                                c = add_rn(prev[(size_t)r * G + low], c);
+                                tt0[q] = table[s];
+                                tt1[q] = (F)0;
                             }
-                            if (h == 0 || c < best[r]) { best[r] = c; arg[r] = h; }
+                        }
+#pragma unroll
+                        for (int q = 0; q < HB; ++q) {
+                            const int h = h0 + q;
+                            if (h >= H) break;
+                            const int low = (h * Gi + g) >> shift;
+                            const F t0 = tt0[q], t1 = tt1[q];
+#pragma unroll
+                            for (int r = 0; r < R; ++r) {
+                                const F d0 = sub_rn(t0, x0[r]);
+                                F c = mul_rn(d0, d0);
+                                if (V == 2) {
+                                    const F d1 = sub_rn(t1, x1[r]);
+                                    c = add_rn(c, mul_rn(d1, d1));
+                                }
+                                if (t == 0) {
+                                    if (ovi[r] >= 0 && low != ovi[r]) c = pos_inf<F>();
+                                } else {
+                                    c = add_rn(prev[r * Gi + low], c);
+                                }
+                                if (h == 0 || c < best[r]) { best[r] = c; arg[r] = h; }
+                            }
                         }
                     }
 #pragma unroll
@@ -214,10 +277,11 @@ static int trellis_dispatch(int64_t rows, int T, const void *x, const void *tabl
     const size_t per_seq = sizeof(F) * 2 * (size_t)G;
     const size_t budget = 200 * 1024;
     if (per_seq > budget) return G2D_ERR_TOO_LARGE;
-    // more sequences per CTA share each table read; fewer keep more SMs busy on short antidiagonals
+    // More sequences per CTA share each table read, but several single-sequence CTAs on one SM overlap each other's
+    // latencies: measured on B200 (HYB, L = 16, T = 256), single-sequence CTAs win below about seven waves of SMs
+    // (296 rows 6.3 ms against 8.9 ms in pairs, 512 rows 12.3 against 17.2), four per CTA above (4096 rows 65 against 83).
     int R = 1;
-    if (rows >= 2 * 148 && 2 * per_seq <= budget) R = 2;
-    if (rows >= 4 * 148 && 4 * per_seq <= budget) R = 4;
+    if (rows >= 7 * 148) R = 4 * per_seq <= budget ? 4 : (2 * per_seq <= budget ? 2 : 1);
     switch (R) {
     case 4: return launch_viterbi<F, 4>(rows, T, x, table, L, K, V, tail, scale, out, states, workspace, st);
     case 2: return launch_viterbi<F, 2>(rows, T, x, table, L, K, V, tail, scale, out, states, workspace, st);
