@@ -277,11 +277,12 @@ static int trellis_dispatch(int64_t rows, int T, const void *x, const void *tabl
     const size_t per_seq = sizeof(F) * 2 * (size_t)G;
     const size_t budget = 200 * 1024;
     if (per_seq > budget) return G2D_ERR_TOO_LARGE;
-    // More sequences per CTA share each table read, but several single-sequence CTAs on one SM overlap each other's
-    // latencies: measured on B200 (HYB, L = 16, T = 256), single-sequence CTAs win below about seven waves of SMs
-    // (296 rows 6.3 ms against 8.9 ms in pairs, 512 rows 12.3 against 17.2), four per CTA above (4096 rows 65 against 83).
+    // More sequences per CTA share each table read and its address arithmetic, fewer finish a short coarse anti-diagonal
+    // sooner.  Measured on B200 (HYB, L = 16, T = 256) one wave of CTAs with 1 / 2 / 4 sequences each takes 1.6 / 2.4 /
+    // 4.3 ms, so the fewest sequences per CTA that still fit one wave of SMs win, and four per CTA beyond that.
     int R = 1;
-    if (rows >= 7 * 148) R = 4 * per_seq <= budget ? 4 : (2 * per_seq <= budget ? 2 : 1);
+    if (rows > 148 && 2 * per_seq <= budget) R = 2;
+    if (rows > 2 * 148 && 4 * per_seq <= budget) R = 4;
     switch (R) {
     case 4: return launch_viterbi<F, 4>(rows, T, x, table, L, K, V, tail, scale, out, states, workspace, st);
     case 2: return launch_viterbi<F, 2>(rows, T, x, table, L, K, V, tail, scale, out, states, workspace, st);
