@@ -82,3 +82,33 @@ def test_config3_trellis_three_factors(oracle):
     expected = oracle.sweep(x.reshape(n1 * n2, n3), row_factor.cpu().numpy(), l3.T.cpu().numpy(), kind=oracle.Q_TRELLIS,
                             super_entry_shape=(16, 16), scale=1.1, table=table.cpu().numpy(), K=2)
     assert torch.equal(z.cpu(), torch.from_numpy(expected))
+
+
+def test_layer_pipeline_equals_plain_calls():
+    """Two layers in flight (preparation of one beside the sweep of the other, host buffers in and out) give exactly
+    what one call after the other gives."""
+    import gptq_2d as G
+    import kron_factors as K
+    import layer_set
+    import quantizer_int as Q
+    import synthetic
+
+    device = torch.device("cuda", 0)
+    layers = [synthetic.make_layer(392, 520, seed=11 + k, device=device, samples=1024, sigma_h=0.5) for k in range(3)]
+    expected = []
+    for w, g, h in layers:
+        l, u = K.feedback_factors_from_grams(g, h)
+        scale = Q.int_abs_max_scale_triton(w, qmin=-8, qmax=7, dtype=torch.float16).expand_as(w)
+        zero = torch.zeros(1, 1, device=device).expand_as(w)
+        expected.append(G.gptq_2d(w, l, u, quantizer=functools.partial(Q.affine_quantizer_triton, qmin=-8, qmax=7), quantizer_inputs=(scale, zero)))
+    pipeline = layer_set.LayerPipeline(device)
+    got = [pipeline.quantize(w, g, h) for w, g, h in layers]
+    torch.cuda.synchronize()
+    for a, b in zip(got, expected):
+        assert torch.equal(a, b)
+    host = [[t.cpu().pin_memory() for t in layer] for layer in layers]
+    outs = [torch.empty_like(h[0]).pin_memory() for h in host]
+    done = [pipeline.quantize_from_host(hw, hg, hh, out) for (hw, hg, hh), out in zip(host, outs)]
+    for event, out, want in zip(done, outs, expected):
+        event.synchronize()
+        assert torch.equal(out, want.cpu())
