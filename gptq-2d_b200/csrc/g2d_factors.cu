@@ -367,20 +367,15 @@ __global__ void __launch_bounds__(FTH) ldl_trinv_level_kernel(LdlBatch<F> B, int
     }
 }
 
-// ---- step 3: out = Lf D^{-1}; one thread per row and diagonal block of `size` columns ----
+// ---- step 3: out = Lf D^{-1}.  Everything above the diagonal blocks is zero already (the output starts as zeros and
+// only blocks on and below the diagonal are written), so the normalisation proper only sets the diagonal blocks to the
+// identity: one thread per row ----
 template <typename F>
 __global__ void ldl_normalize_kernel(F *out, int64_t n, int size) {
-    const int64_t blocks = n / size;
-    const int64_t total = n * blocks;
-    for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (int64_t)gridDim.x * blockDim.x) {
-        const int64_t row = t / blocks, b = t % blocks;  // consecutive threads: consecutive column blocks of one row
-        const int64_t c0 = b * size;
+    for (int64_t row = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; row < n; row += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t c0 = row / size * size;
         F *p = out + row * n + c0;
-        if (c0 > row) {
-            for (int x = 0; x < size; ++x) p[x] = (F)0;
-        } else if (row / size == b) {
-            for (int x = 0; x < size; ++x) p[x] = c0 + x == row ? (F)1 : (F)0;
-        }
+        for (int x = 0; x < size; ++x) p[x] = c0 + x == row ? (F)1 : (F)0;
     }
 }
 
@@ -395,21 +390,20 @@ __global__ void ldl_copy_diag_kernel(const F *out, int64_t n, int size, F *dblk)
     }
 }
 
+// One CTA walks rows, its threads the column blocks left of the row's diagonal block (no index divisions per entry).
 template <typename F>
 __global__ void ldl_scale_kernel(F *out, int64_t n, int size, const F *dblk) {
-    const int64_t blocks = n / size;
-    const int64_t total = n * blocks;
-    for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (int64_t)gridDim.x * blockDim.x) {
-        const int64_t row = t / blocks, b = t % blocks;
-        const int64_t c0 = b * size;
-        if (row / size <= b) continue;  // diagonal block and above: set by ldl_normalize_kernel
-        F *p = out + row * n + c0;
-        const F *d = dblk + b * size * size;
-        // x D = r with D lower triangular: back substitution from the last column of the block
-        for (int x = size - 1; x >= 0; --x) {
-            F acc = p[x];
-            for (int x2 = x + 1; x2 < size; ++x2) acc -= p[x2] * d[x2 * size + x];
-            p[x] = acc / d[x * size + x];
+    for (int64_t row = blockIdx.x; row < n; row += gridDim.x) {
+        const int64_t below = row / size;  // column blocks strictly left of the diagonal block
+        for (int64_t b = threadIdx.x; b < below; b += blockDim.x) {
+            F *p = out + row * n + b * size;
+            const F *d = dblk + b * size * size;
+            // x D = r with D lower triangular: back substitution from the last column of the block
+            for (int x = size - 1; x >= 0; --x) {
+                F acc = p[x];
+                for (int x2 = x + 1; x2 < size; ++x2) acc -= p[x2] * d[x2 * size + x];
+                p[x] = acc / d[x * size + x];
+            }
         }
     }
 }
@@ -595,14 +589,12 @@ int ldl_run(int count, const int64_t *ns, F *const *as, const int *sizes, F *con
     for (int z = 0; z < count; ++z) {
         const int64_t n = ns[z];
         const int size = sizes[z];
-        const int64_t work = n * (n / size);
-        int64_t blocks = ceil_div(work, 256);
-        if (blocks > 148 * 64) blocks = 148 * 64;
+        const int64_t blocks = n < 148 * 16 ? n : 148 * 16;  // rows are dealt out to CTAs
         ldl_copy_diag_kernel<F><<<(unsigned)(ceil_div(n * size, 256) < 148 * 64 ? ceil_div(n * size, 256) : 148 * 64), 256, 0, st>>>(outs[z], n, size, dblks[z]);
         if (check_launch() != G2D_OK) return G2D_ERR_CUDA;
         ldl_scale_kernel<F><<<(unsigned)blocks, 256, 0, st>>>(outs[z], n, size, dblks[z]);
         if (check_launch() != G2D_OK) return G2D_ERR_CUDA;
-        ldl_normalize_kernel<F><<<(unsigned)blocks, 256, 0, st>>>(outs[z], n, size);
+        ldl_normalize_kernel<F><<<(unsigned)ceil_div(n, (int64_t)256), 256, 0, st>>>(outs[z], n, size);
         if (check_launch() != G2D_OK) return G2D_ERR_CUDA;
     }
     return G2D_OK;
