@@ -5,8 +5,12 @@
 One step = quantize one synthetic 8192 x 8192 fp32 layer to INT4 (symmetric, per-row fp16 abs-max scales) from its
 weights and its two Hessian factors G (output side) and H (input side): factor preparation ``ldl_of_inverse`` of both,
 the per-row scales, and the two-sided GPTQ-2D sweep, all through the package's public calls (which reach the kernels
-through the C ABI).  The sweep alone (the reference's own timing unit, demo.ipynb:157) is reported in ``config``.  With N > 1 ranks (one
-per GPU, launched by torchrun) every rank quantizes its own layer: the path shards by matrix and has no collective.
+through the C ABI).  Steps are issued through ``layer_set.LayerPipeline``, as a layer-set job issues its matrices: the
+factor preparation of a step runs beside the sweep of the step before, so the headline is the time per layer of a running
+job with two layers in flight; ``config`` also reports one layer alone, and the sweep alone (the reference's own timing
+unit, demo.ipynb:157).  ``e2e`` is the same with host buffers: G, H and W in from pinned memory and Z out, every step,
+inside the timed region.  With N > 1 ranks (one per GPU, launched by torchrun) every rank quantizes its own layer: the
+path shards by matrix and has no collective.
 Rank 0 prints one JSON line.  ``--impl reference`` times the CPU restatement of the reference's PyTorch path
 (``oracle/``) on the host cores instead, on a bounded sample scaled by the algorithmic work.
 """
