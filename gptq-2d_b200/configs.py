@@ -6,6 +6,7 @@
     python gptq-2d_b200/configs.py --config pack      # INT4 codes of an 8192 x 28672 matrix packed and unpacked
     python gptq-2d_b200/configs.py --config prep      # the factor preparation of an 8192 x 8192 layer alone
     python gptq-2d_b200/configs.py --config gram      # Hessian-factor accumulation, 8192 samples of 8192 channels
+    python gptq-2d_b200/configs.py --config viterbi   # the trellis quantizer alone
 
 Seeded synthetic inputs with the shapes and value distributions of the configurations (``synthetic.py``); everything
 goes through the public entry points.  Configuration 3 rounds ``(1, 16, 16)`` super-entries of the three-factor problem,
@@ -219,9 +220,26 @@ def gram(divide: int, device) -> dict:
             "relative_error": error, "relative_error_of_torch_fp32": plain}
 
 
+def viterbi(divide: int, device) -> dict:
+    """The trellis quantizer alone: HYB code, L = 16, K = 2, V = 2, tail-biting, 256-weight sequences."""
+    import torch
+
+    import quantizer_trellis as T
+
+    table = T.hyb(L=16, seed=0, device=device, dtype=torch.float32)
+    generator = torch.Generator(device=device).manual_seed(7)
+    out = {"config": "viterbi", "flops_per_sequence": 1.174e8}
+    for rows in (148, 296, 4096 // divide):
+        x = torch.randn(rows, 256, generator=generator, device=device)
+        T._trellis_quantize(x, table, 2, True)
+        _, ms = _timed(lambda: T._trellis_quantize(x, table, 2, True))
+        out[f"rows_{rows}"] = {"ms": ms, "sequences_per_s": rows / ms * 1e3, "tflops": rows * 1.174e8 / ms / 1e9}
+    return out
+
+
 def main() -> None:
     parser = argparse.ArgumentParser()
-    parser.add_argument("--config", required=True, choices=("c2", "c3", "pack", "prep", "gram"))
+    parser.add_argument("--config", required=True, choices=("c2", "c3", "pack", "prep", "gram", "viterbi"))
     parser.add_argument("--divide", type=int, default=1, help="shrink the dimensions by this factor")
     args = parser.parse_args()
     sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
@@ -230,7 +248,7 @@ def main() -> None:
     if not torch.cuda.is_available():
         raise SystemExit("configs.py needs a CUDA device (B200); there is no CPU path")
     device = torch.device("cuda", 0)
-    print(json.dumps({"c2": config2, "c3": config3, "pack": pack, "prep": prep, "gram": gram}[args.config](args.divide, device)))
+    print(json.dumps({"c2": config2, "c3": config3, "pack": pack, "prep": prep, "gram": gram, "viterbi": viterbi}[args.config](args.divide, device)))
 
 
 if __name__ == "__main__":
