@@ -11,8 +11,13 @@ job with two layers in flight; ``config`` also reports one layer alone, and the 
 unit, demo.ipynb:157).  ``e2e`` is the same with host buffers: G, H and W in from pinned memory and Z out, every step,
 inside the timed region.  With N > 1 ranks (one per GPU, launched by torchrun) every rank quantizes its own layer: the
 path shards by matrix and has no collective.
-Rank 0 prints one JSON line.  ``--impl reference`` times the CPU restatement of the reference's PyTorch path
-(``oracle/``) on the host cores instead, on a bounded sample scaled by the algorithmic work.
+After the timed steps every rank takes its share of a fixed subset of the 70B-shaped layer set (``--layer-set-blocks``
+blocks of 7 matrices at full size, dealt out longest first, no collective on the data path): the second half of the
+metric, reported under ``layer_set`` with the wall time over ranks.
+Rank 0 prints one JSON line.  ``--impl reference`` times the reference's PyTorch path on the host cores instead, on a
+bounded sample scaled by the algorithmic work: the reference's own ``gptq_2d_torch`` and ``ldl_of_inverse`` when a copy
+of the reference is importable from ``baseline/_ref``, else the CPU restatement under ``oracle/`` (OpenMP sweep, LAPACK
+factorisation); the line says which.
 """
 from __future__ import annotations
 
@@ -31,7 +36,8 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.join(ROOT, "gptq-2d_b200"))
 sys.path.insert(0, ROOT)
 
-METRIC = "s per 8192x8192 INT4 GPTQ-2D layer"
+def metric(size: int) -> str:
+    return f"s per {size}x{size} INT4 GPTQ-2D layer"
 
 
 def sweep_flops(m: int, n: int) -> float:
@@ -99,35 +105,49 @@ class ClockSampler:
         return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(sm_max), "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def cpu_prep_sample(size: int):
-    """Time the CPU oracle's ldl_of_inverse on one bounded sample; returns seconds."""
-    import numpy as np
-    from oracle import oracle
+def host_threads() -> int:
+    """Use every host core for the CPU arm, whatever a launcher put into OMP_NUM_THREADS (torchrun sets it to 1)."""
+    cores = os.cpu_count() or 1
+    try:
+        ctypes.CDLL("libgomp.so.1").omp_set_num_threads(cores)
+    except OSError:
+        pass
+    try:
+        import torch
 
-    rng = np.random.default_rng(1)
-    x = (rng.standard_normal((2 * size, size)) * np.exp(rng.standard_normal(size))).astype(np.float32)
-    gram = x.T @ x / (2 * size)
-    gram += 0.01 * np.mean(np.diag(gram)) * np.eye(size, dtype=np.float32)
-    oracle.lib()
-    start = time.perf_counter()
-    oracle.ldl_of_inverse(gram.astype(np.float32))
-    return time.perf_counter() - start
-
-
-def cpu_layer_estimate(args):
-    """Seconds per full-size layer on the host: sweep sample and factor-preparation sample, each scaled by its work."""
-    sweep_s, cores = cpu_sweep_sample(args.cpu_sample)
-    sweep_factor = sweep_flops(args.size, args.size) / sweep_flops(args.cpu_sample, args.cpu_sample)
-    prep_size = max(256, args.cpu_sample // 2)
-    prep_s = cpu_prep_sample(prep_size)
-    prep_factor = 2 * (args.size / prep_size) ** 3
-    note = (f"oracle port (OpenMP): {args.cpu_sample}x{args.cpu_sample} INT4 sweep {sweep_s:.2f} s scaled x{sweep_factor:.1f} by m n (m + n - 2), "
-            f"plus ldl_of_inverse at n={prep_size} {prep_s:.2f} s scaled x{prep_factor:.0f} (two factors, n^3)")
-    return sweep_s * sweep_factor + prep_s * prep_factor, sweep_s + prep_s, cores, note
+        torch.set_num_threads(cores)
+    except Exception:
+        pass
+    return cores
 
 
-def cpu_sweep_sample(size: int, threads_hint: int | None = None):
-    """Time the CPU oracle's sweep (the restated reference PyTorch path) on a bounded sample; returns (seconds, cores)."""
+def reference_modules():
+    """The reference's own modules when a copy is importable from baseline/_ref (not part of this repository), else None."""
+    path = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.exists(os.path.join(path, "gptq_2d.py")):
+        return None
+    import importlib.util
+
+    loaded = {}
+    try:
+        for name in ("quantizer_int", "gptq_2d", "gptq_2d_reference"):
+            spec = importlib.util.spec_from_file_location(f"_reference_{name}", os.path.join(path, f"{name}.py"))
+            module = importlib.util.module_from_spec(spec)
+            saved = sys.modules.get(name)
+            if name == "gptq_2d":
+                sys.modules["quantizer_int"] = loaded["quantizer_int"]  # the reference imports its sibling by this name
+            spec.loader.exec_module(module)
+            loaded[name] = module
+            if name == "gptq_2d":
+                sys.modules.pop("quantizer_int", None)
+            if saved is not None:
+                sys.modules[name] = saved
+    except Exception:
+        return None
+    return loaded
+
+
+def cpu_inputs(size: int):
     import numpy as np
     from oracle import oracle
 
@@ -135,37 +155,130 @@ def cpu_sweep_sample(size: int, threads_hint: int | None = None):
     w = (0.02 * rng.standard_normal((size, size))).astype(np.float32)
     l = np.tril(rng.standard_normal((size, size)) * (0.3 / np.sqrt(size)), -1).astype(np.float32)
     u = np.triu(rng.standard_normal((size, size)) * (0.3 / np.sqrt(size)), 1).astype(np.float32)
-    scale = np.broadcast_to(oracle.absmax_scale(w, -8, 7, oracle.FP16), (size, size))
+    scale = np.ascontiguousarray(np.broadcast_to(oracle.absmax_scale(w, -8, 7, oracle.FP16), (size, size)))
+    return w, l, u, scale
+
+
+def cpu_sweep_sample(size: int, reference) -> float:
+    """Seconds of one size x size INT4 sweep on the host: the reference's gptq_2d_torch, or the oracle's restatement of it."""
+    import numpy as np
+    from oracle import oracle
+
+    w, l, u, scale = cpu_inputs(size)
     zero = np.zeros((size, size), dtype=np.float32)
+    if reference is not None:
+        import torch
+
+        quantizer = functools.partial(reference["quantizer_int"].affine_quantizer_torch, qmin=-8, qmax=7)
+        tensors = [torch.from_numpy(a) for a in (w, l, u, scale, zero)]
+        start = time.perf_counter()
+        reference["gptq_2d"].gptq_2d_torch(tensors[0], tensors[1], tensors[2], quantizer=quantizer, quantizer_inputs=(tensors[3], tensors[4]))
+        return time.perf_counter() - start
     oracle.lib()
     start = time.perf_counter()
     oracle.sweep(w, l, u, kind=oracle.Q_AFFINE, scale=scale, zero_point=zero, qmin=-8, qmax=7)
-    return time.perf_counter() - start, os.cpu_count() or 1
+    return time.perf_counter() - start
+
+
+def cpu_prep_sample(size: int, reference) -> float:
+    """Seconds of one ldl_of_inverse at n = size on the host (float32): the reference's, or the oracle's LAPACK restatement."""
+    import numpy as np
+    from oracle import oracle
+
+    gram = oracle.dyadic_gram(size, seed=1)
+    if reference is not None:
+        import torch
+
+        tensor = torch.from_numpy(gram)
+        start = time.perf_counter()
+        reference["gptq_2d_reference"].ldl_of_inverse(tensor)
+        return time.perf_counter() - start
+    start = time.perf_counter()
+    oracle.ldl_of_inverse_lapack(gram)
+    return time.perf_counter() - start
+
+
+def cpu_layer_estimate(args, sample: int, reference, threads: int) -> dict:
+    """Seconds per full-size layer on the host: a sweep sample and a factor-preparation sample, each scaled by its work."""
+    sweep_s = cpu_sweep_sample(sample, reference)
+    sweep_factor = sweep_flops(args.size, args.size) / sweep_flops(sample, sample)
+    prep_size = min(args.size, 4096)
+    prep_s = cpu_prep_sample(prep_size, reference)
+    prep_factor = 2 * (args.size / prep_size) ** 3
+    what = ("the reference's gptq_2d_torch + ldl_of_inverse (PyTorch CPU, float32)" if reference is not None
+            else "oracle port of the reference's PyTorch path (OpenMP sweep, LAPACK factorisation, float32)")
+    note = (f"{what}, {threads} threads: {sample}x{sample} INT4 sweep {sweep_s:.2f} s scaled x{sweep_factor:.1f} by m n (m + n - 2) = {sweep_s * sweep_factor:.1f} s, "
+            f"plus ldl_of_inverse at n={prep_size} {prep_s:.2f} s scaled x{prep_factor:.0f} (two factors, n^3) = {prep_s * prep_factor:.1f} s")
+    return {"per_layer": sweep_s * sweep_factor + prep_s * prep_factor, "sample_seconds": sweep_s + prep_s, "note": note,
+            "kind": "reference" if reference is not None else "port", "sweep_s": sweep_s * sweep_factor, "prep_s": prep_s * prep_factor}
 
 
 def run_reference(args) -> None:
-    """The reference arm: the oracle port of the reference's CPU path, all host threads, bounded sample per step."""
+    """The reference arm: the reference's CPU path (or its oracle port), all host threads, a bounded sample per step."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    times, raw = [], []
+    threads = host_threads()
+    reference = reference_modules()
+    # the sample is sized so that warm-up + steps end within a few minutes: the port takes about 10 s at 4096 and 1.2 s
+    # at 2048 on 16 cores, the reference's PyTorch path about twice that
+    budget = 200.0 / max(1, args.steps)
+    sample = args.cpu_sample or (4096 if budget >= (24 if reference is not None else 12) else 2048)
+    sample = min(sample, args.size)
+    times, raw, last = [], [], None
     for step in range(args.warmup + args.steps):
-        per_layer, sample_seconds, cores, note = cpu_layer_estimate(args)
-        if step >= args.warmup:
-            times.append(per_layer)
-            raw.append(sample_seconds)
+        if step < args.warmup:
+            cpu_sweep_sample(min(512, args.size), reference)  # untimed: library loads, thread pools
+            cpu_prep_sample(min(256, args.size), reference)
+            continue
+        last = cpu_layer_estimate(args, sample, reference, threads)
+        times.append(last["per_layer"])
+        raw.append(last["sample_seconds"])
     per_layer = statistics.mean(times)
     line = {
-        "impl": "reference", "metric": METRIC, "value": per_layer, "unit": "s", "n_gpus": args.gpus, "steps": args.steps,
+        "impl": "reference", "metric": metric(args.size), "value": per_layer, "unit": "s", "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": 1e3 * statistics.mean(raw), "higher_is_better": False, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": f"{args.size}x{args.size} fp32 layer from W, G, H: ldl_of_inverse x2, INT4 symmetric per-row fp16 abs-max scales, two-sided sweep",
-                   "sample": note},
-        "cpu_baseline": {"value": per_layer, "unit": "s", "cores": cores, "kind": "port", "sample": note},
+                   "sample": last["note"], "sweep_s": last["sweep_s"], "prep_s": last["prep_s"]},
+        "cpu_baseline": {"value": per_layer, "unit": "s", "cores": threads, "kind": last["kind"], "sample": last["note"]},
         "e2e": {"value": per_layer, "unit": "s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line))
+
+
+def measure_tf32_peak(device) -> dict:
+    """Dense TF32 matrix-product throughput of this GPU through torch.matmul (cuBLAS), measured the way the bf16 figure of
+    MEASURED_PEAKS.json was: 8192^3, best of 10 (burst) and back to back for about a second (sustained)."""
+    import torch
+
+    n = 8192
+    a, b = torch.randn(n, n, device=device), torch.randn(n, n, device=device)
+    before = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = True
+    try:
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for _ in range(3):
+            a @ b
+        best = float("inf")
+        for _ in range(10):
+            begin.record()
+            a @ b
+            end.record()
+            torch.cuda.synchronize()
+            best = min(best, begin.elapsed_time(end))
+        count = max(10, int(1000.0 / best))
+        begin.record()
+        for _ in range(count):
+            a @ b
+        end.record()
+        torch.cuda.synchronize()
+        sustained = begin.elapsed_time(end) / count
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = before
+    flops = 2.0 * n ** 3
+    return {"burst_tflops": flops / best / 1e9, "sustained_tflops": flops / sustained / 1e9, "how": f"torch.matmul fp32 with TF32 allowed, {n}^3, best of 10 and {count} back to back"}
 
 
 def main() -> None:
@@ -175,8 +288,9 @@ def main() -> None:
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", default="ours", choices=("ours", "reference"))
     parser.add_argument("--size", type=int, default=8192)
-    parser.add_argument("--cpu-sample", type=int, default=2048)
+    parser.add_argument("--cpu-sample", type=int, default=0, help="side of the CPU arm's sweep sample; 0 chooses by the time budget")
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--layer-set-blocks", type=int, default=8, help="blocks of the 70B-shaped layer set run after the timed steps (0: none)")
     args = parser.parse_args()
     if args.impl == "reference":
         run_reference(args)
@@ -289,6 +403,27 @@ def main() -> None:
     e2e_ms /= args.steps
     h2d = (host_w.numel() + host_l.numel() + host_u.numel()) * 4
     d2h = host_z[0].numel() * 4
+    # what the asynchronous calls of the timed regions could not report: a factor that is not positive definite, or a
+    # bounded wait inside a tensor-core kernel that ran out (raises)
+    pipeline.check()
+    del host_w, host_l, host_u, host_z
+
+    # ---- the layer-set half of the metric: a fixed subset of the 70B-shaped set, partitioned by matrix over the ranks ----
+    set_summary = None
+    if args.layer_set_blocks > 0:
+        def gather(obj):
+            if world == 1:
+                return [obj]
+            out = [None] * world if rank == 0 else None
+            dist.gather_object(obj, out, dst=0)
+            return out
+
+        layer_set.quantize_matrix({"block": -1, "name": "warm-up", "m": 384, "n": 512, "seed": 1}, device)
+        set_pipeline = layer_set.LayerPipeline(device)
+        set_summary = layer_set.run(layer_set.layer_list(args.layer_set_blocks), functools.partial(layer_set.quantize_matrix, device=device, pipeline=set_pipeline),
+                                    rank=rank, world=world, gather=gather, barrier=barrier)
+        set_pipeline.check()
+        torch.cuda.empty_cache()
 
     if rank != 0:
         if world > 1:
@@ -315,13 +450,26 @@ def main() -> None:
     pk = peaks()
     tensor_peak = pk["bf16_tflops_sustained"] / 6.0  # fp32-faithful tensor roofline: TF32 = bf16 / 2, three TF32 products per fp32 product
     far_tflops = far_flops / (far_ms * 1e-3) / 1e12 if far_ms > 0 else 0.0
+    near_tflops = near_flops / (near_ms * 1e-3) / 1e12 if near_ms > 0 else 0.0
+    panel_tflops = (near_flops + far_flops) / ((near_ms + far_ms) * 1e-3) / 1e12 if near_ms + far_ms > 0 else 0.0
+    tf32 = measure_tf32_peak(device)
+    measured_peak = tf32["sustained_tflops"] / 3.0
+    rtn = torch.clamp(torch.round(w / scale), -8, 7) * scale
+    objective_vs_rtn = synthetic.objective(z, w, g, h) / synthetic.objective(rtn, w, g, h)
     roofline = {
         "bound": "tensor", "kernel": "macro_update_tc_kernel (tcgen05 kind::tf32, 3xTF32 split; far updates, running beside the tile launches)",
         "achieved": far_tflops, "peak": tensor_peak, "unit": "TFLOP/s", "frac": far_tflops / tensor_peak if tensor_peak else None,
-        # dram bytes read + written of one far-update launch, from the ncu capture of a 4096 x 4096 run (149.7 MB for
-        # 946 target macro tiles, profiles/macro_update_tc_kernel_far_4096.md), scaled by the target tiles of an average launch here
+        # DRAM bytes of one launch are not measured live: an ncu capture of this kernel at 4096 x 4096 read and wrote
+        # 149.7 MB for 946 target macro tiles; that figure scaled by the target tiles of an average launch here
         "traffic": 149.7e6 / 946 * (far_flops / far_n / (2 * 2 * 128 * 128 * 512)) if far_n else None,
+        "traffic_basis": "ncu capture at 4096 x 4096 (dram__bytes_read.sum + dram__bytes_write.sum of one launch), scaled by target macro tiles; not measured in this run",
         "peak_basis": f"{pk['source']} bf16 sustained {pk['bf16_tflops_sustained']} TFLOP/s / 2 (TF32) / 3 (three tf32 products per fp32 product)",
+        "peak_measured_tf32": {**tf32, "fp32_faithful_peak": measured_peak, "frac_of_it": far_tflops / measured_peak if measured_peak else None},
+        "near": {"kernel": "band_tc_kernel (tcgen05 kind::tf32, M 128 x N 64, rank-64 updates on a side stream)", "achieved": near_tflops,
+                 "frac": near_tflops / tensor_peak if tensor_peak else None, "launches": int(near_n), "algorithmic_flops": near_flops},
+        "panel_gemms": {"what": "near + far updates: their algorithmic flops over their summed stream time", "achieved": panel_tflops,
+                        "frac": panel_tflops / tensor_peak if tensor_peak else None, "algorithmic_flops": near_flops + far_flops,
+                        "share_of_sweep_flops": (near_flops + far_flops) / total_flops if total_flops else None},
         "launches": int(far_n), "avg_launch_ms": far_ms / far_n if far_n else None,
         "algorithmic_flops_per_launch": far_flops / far_n if far_n else None,
         "kernel_ms": {"tile_sweep": tile_ms, "near_update": near_ms, "far_update": far_ms},
@@ -336,7 +484,7 @@ def main() -> None:
     }
 
     line = {
-        "metric": METRIC, "value": ms_per_step / 1e3 / world, "unit": "s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "metric": metric(args.size), "value": ms_per_step / 1e3 / world, "unit": "s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_per_step, "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
         "config": {
@@ -346,15 +494,29 @@ def main() -> None:
             "layers_in_flight": 2, "single_layer_ms": parts["single_layer"],
             "sweep_ms": parts["sweep"], "prep_ms": parts["prep"],
             "stages": m + n - 1, "sweep_us_per_stage": parts["sweep"] * 1e3 / (m + n - 1),
+            "objective_vs_round_to_nearest": objective_vs_rtn, "status": "factor pivots and kernel wait flags read after the timed regions: clean",
         },
         "clocks": clocks.summary(),
         "e2e": {"value": e2e_ms / 1e3 / world, "unit": "s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": int(launches),
         "roofline": roofline,
     }
+    if set_summary is not None:
+        blocks = args.layer_set_blocks
+        line["layer_set"] = {
+            "what": f"{blocks} blocks of the 70B-shaped set at full size ({set_summary['matrices']} matrices: q, o 8192^2; k, v 1024x8192; gate, up 28672x8192; down 8192x28672), "
+                    "seeded inputs generated on the owning GPU inside the timed region, INT4, two layers in flight per GPU, longest-first partition, no data-path collective",
+            "blocks": blocks, "matrices": set_summary["matrices"], "n_gpus": world, "wall_s": set_summary["wall_s"], "busy_s": set_summary["busy_s"],
+            "scaling": "strong", "mean_ms_by_shape": set_summary["mean_ms_by_shape"],
+            "extrapolated_80_blocks_s": set_summary["wall_s"] * 80.0 / blocks, "extrapolation": f"wall time x 80 / {blocks}: not measured",
+            "all_finite": set_summary["all_finite"], "all_codes_in_range": set_summary["all_codes_in_range"],
+            "objective_vs_round_to_nearest": set_summary["objective_vs_rtn"],
+        }
     if world == 1 and not args.no_cpu_baseline:
-        per_layer, _, cores, note = cpu_layer_estimate(args)
-        line["cpu_baseline"] = {"value": per_layer, "unit": "s", "cores": cores, "kind": "port", "sample": note}
+        threads = host_threads()
+        estimate = cpu_layer_estimate(args, min(args.size, args.cpu_sample or 4096), reference_modules(), threads)
+        line["cpu_baseline"] = {"value": estimate["per_layer"], "unit": "s", "cores": threads, "kind": estimate["kind"], "sample": estimate["note"],
+                                "sweep_s": estimate["sweep_s"], "prep_s": estimate["prep_s"]}
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

@@ -1,12 +1,13 @@
 """Full-size runs of the benchmark configurations that are not the headline: one JSON line each.
 
-    python gptq-2d_b200/configs.py --config c2        # 8192 x 28672, INT3 affine, scale and zero point per group of 128 columns
-    python gptq-2d_b200/configs.py --config c3        # 4096 x 14336 as [16, 256, 14336], three factors, 2-bit HYB trellis
-    python gptq-2d_b200/configs.py --config c3 --divide 4   # every dimension but the super-entry shrunk (short run)
-    python gptq-2d_b200/configs.py --config pack      # INT4 codes of an 8192 x 28672 matrix packed and unpacked
-    python gptq-2d_b200/configs.py --config prep      # the factor preparation of an 8192 x 8192 layer alone
-    python gptq-2d_b200/configs.py --config gram      # Hessian-factor accumulation, 8192 samples of 8192 channels
-    python gptq-2d_b200/configs.py --config viterbi   # the trellis quantizer alone
+    python configs.py --config c1        # 4096 x 4096 INT4, 0.1 % outliers at 10 sigma, Hessian factors from 8192 samples
+    python configs.py --config c2        # 8192 x 28672, INT3 affine, scale and zero point per group of 128 columns
+    python configs.py --config c3        # 4096 x 14336 as [16, 256, 14336], three factors, 2-bit HYB trellis
+    python configs.py --config c3 --divide 4   # every dimension but the super-entry shrunk (short run)
+    python configs.py --config pack      # INT4 codes of an 8192 x 28672 matrix packed and unpacked
+    python configs.py --config prep      # the factor preparation of an 8192 x 8192 layer alone
+    python configs.py --config gram      # Hessian-factor accumulation, 8192 samples of 8192 channels
+    python configs.py --config viterbi   # the trellis quantizer alone
 
 Seeded synthetic inputs with the shapes and value distributions of the configurations (``synthetic.py``); everything
 goes through the public entry points.  Configuration 3 rounds ``(1, 16, 16)`` super-entries of the three-factor problem,
@@ -31,6 +32,39 @@ def _timed(fn):
     end.record()
     torch.cuda.synchronize()
     return out, begin.elapsed_time(end)
+
+
+def config1(divide: int, device) -> dict:
+    """4096 x 4096 weights with 0.1 % of the entries at 10 sigma, both Hessian factors from 8192 heavy-tailed activation
+    samples (sigma_h = 1, 1 % damping), INT4 symmetric per-row fp16 scales: one layer alone, preparation then sweep."""
+    import torch
+
+    import gptq_2d as G
+    import kron_factors as K
+    import quantizer_int as Q
+    import synthetic
+
+    m = n = 4096 // divide
+    w, g, h = synthetic.make_layer(m, n, seed=1, device=device, samples=8192 // divide, outliers=1e-3)
+    scale = Q.int_abs_max_scale_triton(w, qmin=-8, qmax=7, dtype=torch.float16).expand(m, n)
+    zero = torch.zeros(1, 1, device=device).expand(m, n)
+    quantizer = functools.partial(Q.affine_quantizer_triton, qmin=-8, qmax=7)
+    l, u = K.feedback_factors_from_grams(g, h, check=True)
+    G.gptq_2d(w, l, u, quantizer=quantizer, quantizer_inputs=(scale, zero))  # module load, streams
+    (l, u), prep_ms = _timed(lambda: K.feedback_factors_from_grams(g, h))
+    z, sweep_ms = _timed(lambda: G.gptq_2d(w, l, u, quantizer=quantizer, quantizer_inputs=(scale, zero)))
+    K.check_pending()
+    G.check_status(device)
+    codes = torch.round(z / scale)
+    rtn = torch.clamp(torch.round(w / scale), -8, 7) * scale
+    flops = float(m) * n * (m + n - 2)
+    return {
+        "config": "c1", "shape": [m, n], "quantizer": "INT4 symmetric, per-row fp16 abs-max scales", "outliers": float((w.abs() > 9 * 0.02).float().mean()),
+        "prep_ms": prep_ms, "sweep_ms": sweep_ms, "layer_ms": prep_ms + sweep_ms, "sweep_tflops": flops / sweep_ms / 1e9,
+        "prep_tflops": 2 * (m ** 3 + n ** 3) / 3 / prep_ms / 1e9, "stages": m + n - 1, "us_per_stage": 1e3 * sweep_ms / (m + n - 1),
+        "codes_in_range": bool((codes.min() >= -8) & (codes.max() <= 7)), "finite": bool(torch.isfinite(z).all()),
+        "objective_vs_rtn": synthetic.objective(z, w, g, h) / synthetic.objective(rtn, w, g, h),
+    }
 
 
 def config2(divide: int, device) -> dict:
@@ -164,7 +198,7 @@ def pack(divide: int, device) -> dict:
     unpack_ms = timed(lambda: P.unpack_codes(codes, scale, zero, qmin=-8, bits=4, n=n))
     moved = 4.0 * m * n + 0.5 * m * n + 4.0 * m  # z, codes, one scale per row (either direction)
     peak = 6650.0
-    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")
     source = "fallback"
     if os.path.exists(path):
         with open(path) as f:
@@ -239,16 +273,16 @@ def viterbi(divide: int, device) -> dict:
 
 def main() -> None:
     parser = argparse.ArgumentParser()
-    parser.add_argument("--config", required=True, choices=("c2", "c3", "pack", "prep", "gram", "viterbi"))
+    parser.add_argument("--config", required=True, choices=("c1", "c2", "c3", "pack", "prep", "gram", "viterbi"))
     parser.add_argument("--divide", type=int, default=1, help="shrink the dimensions by this factor")
     args = parser.parse_args()
-    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "gptq-2d_b200"))
     import torch
 
     if not torch.cuda.is_available():
         raise SystemExit("configs.py needs a CUDA device (B200); there is no CPU path")
     device = torch.device("cuda", 0)
-    print(json.dumps({"c2": config2, "c3": config3, "pack": pack, "prep": prep, "gram": gram, "viterbi": viterbi}[args.config](args.divide, device)))
+    print(json.dumps({"c1": config1, "c2": config2, "c3": config3, "pack": pack, "prep": prep, "gram": gram, "viterbi": viterbi}[args.config](args.divide, device)))
 
 
 if __name__ == "__main__":

@@ -14,7 +14,7 @@ import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIBRARY_PATH = os.path.join(_HERE, "csrc", "libgptq2d_b200.so")
-ABI_VERSION = 1
+ABI_VERSION = 2
 
 F32, F64 = 0, 1
 FP16, BF16 = 0, 1
@@ -38,6 +38,7 @@ class SweepDesc(ctypes.Structure):
         ("forced_z", _vp), ("y_pre", _vp),
         ("workspace", _vp), ("workspace_bytes", ctypes.c_size_t),
         ("outer_tiles", _i32), ("reserved", _i32),
+        ("status", _vp),
     ]
 
 
@@ -128,6 +129,28 @@ def ptr(t: torch.Tensor | None):
 
 def stream_of(t: torch.Tensor):
     return torch.cuda.current_stream(t.device).cuda_stream
+
+
+_STATUS_WORDS: dict[int, torch.Tensor] = {}
+
+
+def status_word(device: torch.device) -> torch.Tensor:
+    """The device's persistent ``int32[1]`` status word.  The tensor-core kernels wait on hardware barriers with a
+    time limit; a wait that runs out sets this word to -1 (the sweep also overwrites its output with NaN).  The
+    library only ever sets it, so one read after many asynchronous calls tells whether all of them were sound."""
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    if index not in _STATUS_WORDS:
+        _STATUS_WORDS[index] = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", index))
+    return _STATUS_WORDS[index]
+
+
+def check_status(device: torch.device, what: str = "gptq2d_b200") -> None:
+    """Wait for the device and raise if any call since the last check reported a bounded wait that ran out."""
+    word = status_word(device)
+    value = int(word.item())
+    if value != 0:
+        word.zero_()
+        raise RuntimeError(f"{what}: a bounded wait inside a tensor-core kernel ran out (status {value}); results since the last check are not valid")
 
 
 def batch_offsets(x: torch.Tensor, batch_shape: torch.Size) -> torch.Tensor | None:

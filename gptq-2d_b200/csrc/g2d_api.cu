@@ -7,7 +7,7 @@
 #include <vector>
 
 namespace g2d {
-unsigned long long g_launches = 0;
+std::atomic<unsigned long long> g_launches{0};
 }
 
 using namespace g2d;
@@ -55,6 +55,21 @@ double band_flops(int64_t m, int64_t n, int64_t s0, int64_t s1, int64_t s_end, i
     return flops;
 }
 
+// Last launch of a sweep that used the tensor-core update kernels.  Their waits on hardware barriers are bounded; a
+// wait that ran out made its CTA skip its additions and set `flag`.  Such a result must not pass for a valid one:
+// the whole output is overwritten with NaN and the caller's status word (if any) is set to -1.  Costs one load per
+// thread when all went well.
+__global__ void sweep_finish_kernel(const int *__restrict__ flag, int32_t *status, float *y, int64_t count) {
+    if (*flag == 0) return;
+    if (status != nullptr && blockIdx.x == 0 && threadIdx.x == 0) atomicExch(status, -1);
+    const float poison = __int_as_float(0x7fc00000);
+    for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < count; t += (int64_t)gridDim.x * blockDim.x) y[t] = poison;
+}
+int launch_sweep_finish(const int *flag, int32_t *status, float *y, int64_t count, cudaStream_t stream) {
+    sweep_finish_kernel<<<148, 256, 0, stream>>>(flag, status, y, count);
+    return check_launch();
+}
+
 constexpr int kDefaultOuterTiles = 8;  // tile anti-diagonals gathered into one far update (512 stages)
 
 inline size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
@@ -79,10 +94,10 @@ int check_sweep(const g2d_sweep_desc *d) {
 
 // Feedback between macro tiles: on the tensor cores when the operand planes exist, else the general FFMA update.
 template <typename F>
-int launch_macro_update(const BandArgs<F> &bm, const TcPlanes *planes, cudaStream_t stream) {
+int launch_macro_update(const BandArgs<F> &bm, const TcPlanes *planes, const MacroTcMaps *maps, cudaStream_t stream) {
     if (planes != nullptr) {
         if constexpr (sizeof(F) == sizeof(float))
-            return launch_macro_update_tc(*planes, (float *)bm.y, (float *)bm.c, bm.m, bm.n, (int)bm.s0, (int)bm.s1, (int)bm.s_end, stream);
+            return launch_macro_update_tc(maps, *planes, (float *)bm.y, (float *)bm.c, bm.m, bm.n, (int)bm.s0, (int)bm.s1, (int)bm.s_end, stream);
     }
     return launch_band_update<F>(bm, stream);
 }
@@ -98,6 +113,11 @@ constexpr int kDefaultOuterMacro = 4;    // macro anti-diagonals per far update 
 template <typename F>
 int sweep_macro(const g2d_sweep_desc *d, SweepArgs<F> &a, BandArgs<F> &b64, cudaStream_t stream, LaunchTimer *timer, double *flops,
                 const TcPlanes *planes) {
+    MacroTcMaps maps;
+    if (planes != nullptr) {
+        const int status = macro_tc_prepare(&maps, *planes, d->m, d->n);
+        if (status != G2D_OK) return status;
+    }
     const int nI2 = (int)ceil_div(d->m, MACRO), nJ2 = (int)ceil_div(d->n, MACRO);
     const int waves = nI2 + nJ2 - 1;
     const int outer = d->outer_tiles > 0 ? (d->outer_tiles + 1) / 2 : kDefaultOuterMacro;
@@ -126,14 +146,14 @@ int sweep_macro(const g2d_sweep_desc *d, SweepArgs<F> &a, BandArgs<F> &b64, cuda
             if (status != G2D_OK) return status;
             if (W + 1 < W1) {
                 bm.s0 = W; bm.s1 = W + 1; bm.s_end = W1;
-                status = timed(1, [&] { return launch_macro_update<F>(bm, planes, stream); });
+                status = timed(1, [&] { return launch_macro_update<F>(bm, planes, &maps, stream); });
                 if (flops) flops[1] += band_flops(d->m, d->n, bm.s0, bm.s1, bm.s_end, MACRO) * (double)d->batch;
                 if (status != G2D_OK) return status;
             }
         }
         if (W1 < waves) {
             bm.s0 = W0; bm.s1 = W1; bm.s_end = waves;
-            const int status = timed(2, [&] { return launch_macro_update<F>(bm, planes, stream); });
+            const int status = timed(2, [&] { return launch_macro_update<F>(bm, planes, &maps, stream); });
             if (flops) flops[2] += band_flops(d->m, d->n, bm.s0, bm.s1, bm.s_end, MACRO) * (double)d->batch;
             if (status != G2D_OK) return status;
         }
@@ -141,39 +161,107 @@ int sweep_macro(const g2d_sweep_desc *d, SweepArgs<F> &a, BandArgs<F> &b64, cuda
     return G2D_OK;
 }
 
-// Side streams and events of the pipelined schedule.  Calls take lanes round robin, so sweeps that a caller runs
-// concurrently on several streams do not share one.  Created on first use per device and kept.
+// Side streams and events of the pipelined schedule.  A device has four lanes; calls take them round robin and hold a
+// lane's lock while they enqueue, so sweeps that a caller runs concurrently on several streams (or from several host
+// threads) never interleave their event records on one lane.  All four lanes of a device are built by the first
+// pipelined call on it, which therefore must not run inside a stream capture (stream and event creation is not
+// capturable): during capture, a device whose lanes do not exist yet gets G2D_ERR_UNSUPPORTED.
 struct PipeLane {
     cudaStream_t tiles = nullptr, near = nullptr, far = nullptr;  // in falling priority
     cudaEvent_t swept[8] = {}, near_done[8] = {}, far_done[4] = {}, fork = nullptr, join = nullptr;
+    std::mutex busy;
 };
-PipeLane *acquire_pipe_lane() {
-    static std::mutex mutex;
-    static PipeLane lanes[64][4];
-    static unsigned next[64] = {};
+struct DeviceLanes {
+    std::mutex build;
+    bool ready = false;
+    unsigned next = 0;
+    PipeLane lane[4];
+};
+
+void destroy_lane(PipeLane &l) {
+    for (cudaStream_t *s : {&l.tiles, &l.near, &l.far})
+        if (*s) { cudaStreamDestroy(*s); *s = nullptr; }
+    auto drop = [](cudaEvent_t &e) { if (e) { cudaEventDestroy(e); e = nullptr; } };
+    for (auto &e : l.swept) drop(e);
+    for (auto &e : l.near_done) drop(e);
+    for (auto &e : l.far_done) drop(e);
+    drop(l.fork);
+    drop(l.join);
+}
+
+bool build_lane(PipeLane &l) {
+    // the tile launches are the critical path: their CTAs go first wherever a slot frees up, then the near updates
+    int least = 0, greatest = 0;
+    if (cudaDeviceGetStreamPriorityRange(&least, &greatest) != cudaSuccess) return false;
+    const int middle = greatest + 1 <= least ? greatest + 1 : least;
+    bool ok = cudaStreamCreateWithPriority(&l.tiles, cudaStreamNonBlocking, greatest) == cudaSuccess &&
+              cudaStreamCreateWithPriority(&l.near, cudaStreamNonBlocking, middle) == cudaSuccess &&
+              cudaStreamCreateWithPriority(&l.far, cudaStreamNonBlocking, least) == cudaSuccess &&
+              cudaEventCreateWithFlags(&l.fork, cudaEventDisableTiming) == cudaSuccess &&
+              cudaEventCreateWithFlags(&l.join, cudaEventDisableTiming) == cudaSuccess;
+    for (int k = 0; k < 8 && ok; ++k)
+        ok = cudaEventCreateWithFlags(&l.swept[k], cudaEventDisableTiming) == cudaSuccess &&
+             cudaEventCreateWithFlags(&l.near_done[k], cudaEventDisableTiming) == cudaSuccess;
+    for (int k = 0; k < 4 && ok; ++k) ok = cudaEventCreateWithFlags(&l.far_done[k], cudaEventDisableTiming) == cudaSuccess;
+    return ok;
+}
+
+// Returns a lane of the current device with its lock held (through `held`), or null with *status set.
+PipeLane *acquire_pipe_lane(cudaStream_t caller, std::unique_lock<std::mutex> &held, int *status) {
+    static DeviceLanes devices[64];
     int device = 0;
+    *status = G2D_ERR_CUDA;
     if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return nullptr;
-    std::lock_guard<std::mutex> lock(mutex);
-    PipeLane *lane = &lanes[device][next[device]++ & 3];
-    if (!lane->near) {
-        // the tile launches are the critical path: their CTAs go first wherever a slot frees up, then the near updates
-        int least = 0, greatest = 0;
-        if (cudaDeviceGetStreamPriorityRange(&least, &greatest) != cudaSuccess) return nullptr;
-        const int middle = greatest + 1 <= least ? greatest + 1 : least;
-        if (cudaStreamCreateWithPriority(&lane->tiles, cudaStreamNonBlocking, greatest) != cudaSuccess ||
-            cudaStreamCreateWithPriority(&lane->near, cudaStreamNonBlocking, middle) != cudaSuccess ||
-            cudaStreamCreateWithPriority(&lane->far, cudaStreamNonBlocking, least) != cudaSuccess ||
-            cudaEventCreateWithFlags(&lane->fork, cudaEventDisableTiming) != cudaSuccess ||
-            cudaEventCreateWithFlags(&lane->join, cudaEventDisableTiming) != cudaSuccess)
-            return nullptr;
-        for (int k = 0; k < 8; ++k)
-            if (cudaEventCreateWithFlags(&lane->swept[k], cudaEventDisableTiming) != cudaSuccess ||
-                cudaEventCreateWithFlags(&lane->near_done[k], cudaEventDisableTiming) != cudaSuccess)
+    DeviceLanes &dl = devices[device];
+    unsigned slot;
+    {
+        std::lock_guard<std::mutex> lock(dl.build);
+        if (!dl.ready) {
+            cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+            if (cudaStreamIsCapturing(caller, &capturing) != cudaSuccess) return nullptr;
+            if (capturing != cudaStreamCaptureStatusNone) {
+                *status = G2D_ERR_UNSUPPORTED;
                 return nullptr;
-        for (int k = 0; k < 4; ++k)
-            if (cudaEventCreateWithFlags(&lane->far_done[k], cudaEventDisableTiming) != cudaSuccess) return nullptr;
+            }
+            bool ok = true;
+            for (auto &l : dl.lane) ok = ok && build_lane(l);
+            if (!ok) {
+                for (auto &l : dl.lane) destroy_lane(l);
+                return nullptr;
+            }
+            dl.ready = true;
+        }
+        slot = dl.next++ & 3;
     }
-    return lane;
+    held = std::unique_lock<std::mutex>(dl.lane[slot].busy);
+    *status = G2D_OK;
+    return &dl.lane[slot];
+}
+
+// Algorithmic flops of one near update of the pipelined schedule: the tiles of the tile anti-diagonal s as sources, the
+// tiles of the anti-diagonals t0..t1 as targets, without the (source, target) pairs that the far update of the
+// source's macro group carries (the same rule as band_tc_kernel's).  No padding counted.
+double near_flops(int64_t m, int64_t n, int s, int t0, int t1, int outer_macro, int lag_macro) {
+    const int64_t nI = ceil_div(m, TILE), nJ = ceil_div(n, TILE);
+    auto extent = [](int64_t index, int64_t count, int64_t size) { return (double)(index == count - 1 ? size - index * TILE : TILE); };
+    double flops = 0;
+    for (int64_t TI = 0; TI < nI; ++TI)
+        for (int64_t TJ = 0; TJ < nJ; ++TJ) {
+            if (TI + TJ < t0 || TI + TJ > t1) continue;
+            const double rows = extent(TI, nI, m), cols = extent(TJ, nJ, n);
+            const int64_t w_target = (TI >> 1) + (TJ >> 1);
+            const int64_t kd = s - TJ;  // down: source tile (kd, TJ)
+            if (kd >= 0 && kd < TI) {
+                const int64_t w_source = (kd >> 1) + (TJ >> 1);
+                if (w_target < (w_source / outer_macro + 1) * outer_macro + lag_macro) flops += 2.0 * rows * cols * extent(kd, nI, m);
+            }
+            const int64_t kr = s - TI;  // right: source tile (TI, kr)
+            if (kr >= 0 && kr < TJ) {
+                const int64_t w_source = (TI >> 1) + (kr >> 1);
+                if (w_target < (w_source / outer_macro + 1) * outer_macro + lag_macro) flops += 2.0 * rows * cols * extent(kr, nJ, n);
+            }
+        }
+    return flops;
 }
 
 constexpr int kFarLagMacro = 2;  // a far update reaches the macro anti-diagonals from this many past its group's end
@@ -192,13 +280,17 @@ constexpr int kFarLagMacro = 2;  // a far update reaches the macro anti-diagonal
 // ordered on one stream, so the additions have a fixed order.
 int sweep_pipelined(const g2d_sweep_desc *d, SweepArgs<float> &a, const TcPlanes &planes, float *yf, float *cf, cudaStream_t caller,
                     LaunchTimer *timer, double *flops) {
-    PipeLane *lane = acquire_pipe_lane();
-    if (!lane) return G2D_ERR_CUDA;
+    std::unique_lock<std::mutex> held;
+    int lane_status = G2D_OK;
+    PipeLane *lane = acquire_pipe_lane(caller, held, &lane_status);
+    if (!lane) return lane_status;
     // fork: everything the caller's stream holds so far comes first
     cudaStream_t stream = lane->tiles;
     if (cudaEventRecord(lane->fork, caller) != cudaSuccess || cudaStreamWaitEvent(stream, lane->fork, 0) != cudaSuccess) return G2D_ERR_CUDA;
     BandTcMaps maps;
+    MacroTcMaps far_maps;
     int status = band_tc_prepare(&maps, planes, d->m, d->n);
+    if (status == G2D_OK) status = macro_tc_prepare(&far_maps, planes, d->m, d->n);
     if (status != G2D_OK) return status;
     a.yf = yf; a.cf = cf; a.neighbours = 1;
     const int waves = a.nI + a.nJ - 1;
@@ -230,6 +322,7 @@ int sweep_pipelined(const g2d_sweep_desc *d, SweepArgs<float> &a, const TcPlanes
             status = launch_band_tc(&maps, a.y, a.c, d->m, d->n, s, s + 1, t0, t1, outer, kFarLagMacro, planes.error_flag, lane->near);
             if (timer) timer->end();
             if (status != G2D_OK) return status;
+            if (flops) flops[1] += near_flops(d->m, d->n, s, t0, t1, outer, kFarLagMacro);
             if (cudaEventRecord(lane->near_done[s & 7], lane->near) != cudaSuccess) return G2D_ERR_CUDA;
             last_near = s;
         }
@@ -237,7 +330,7 @@ int sweep_pipelined(const g2d_sweep_desc *d, SweepArgs<float> &a, const TcPlanes
             const int g = W1 / outer - 1;
             if (cudaStreamWaitEvent(lane->far, lane->swept[s & 7], 0) != cudaSuccess) return G2D_ERR_CUDA;
             if (timer) timer->begin_on(2, lane->far);
-            status = launch_macro_update_tc(planes, yf, cf, d->m, d->n, W1 - outer, W1, waves_macro, lane->far, W1 + kFarLagMacro, 2);
+            status = launch_macro_update_tc(&far_maps, planes, yf, cf, d->m, d->n, W1 - outer, W1, waves_macro, lane->far, W1 + kFarLagMacro, 2);
             if (timer) timer->end();
             if (status != G2D_OK) return status;
             if (flops)
@@ -249,6 +342,8 @@ int sweep_pipelined(const g2d_sweep_desc *d, SweepArgs<float> &a, const TcPlanes
     // join: what follows the call on the caller's stream follows everything the call did
     if (last_near >= 0 && cudaStreamWaitEvent(stream, lane->near_done[last_near & 7], 0) != cudaSuccess) return G2D_ERR_CUDA;
     if (last_far >= 0 && cudaStreamWaitEvent(stream, lane->far_done[last_far & 3], 0) != cudaSuccess) return G2D_ERR_CUDA;
+    status = launch_sweep_finish(planes.error_flag, d->status, a.y, d->m * d->n, stream);
+    if (status != G2D_OK) return status;
     if (cudaEventRecord(lane->join, stream) != cudaSuccess || cudaStreamWaitEvent(caller, lane->join, 0) != cudaSuccess) return G2D_ERR_CUDA;
     return G2D_OK;
 }
@@ -302,7 +397,9 @@ int sweep_fused(const g2d_sweep_desc *d, cudaStream_t stream, LaunchTimer *timer
                 return sweep_pipelined(d, a, planes, yf, cf, stream, timer, flops);
             }
         }
-        return sweep_macro<F>(d, a, b, stream, timer, flops, &planes);
+        const int swept = sweep_macro<F>(d, a, b, stream, timer, flops, &planes);
+        if (swept != G2D_OK) return swept;
+        return launch_sweep_finish(planes.error_flag, d->status, (float *)d->y, d->m * d->n, stream);
     }
     if (d->reserved == 2) return sweep_macro<F>(d, a, b, stream, timer, flops, nullptr);
 
@@ -369,7 +466,7 @@ extern "C" const char *g2d_status_string(int status) {
     }
 }
 
-extern "C" int g2d_abi_version(void) { return 1; }
+extern "C" int g2d_abi_version(void) { return 2; }
 
 extern "C" int g2d_sweep_workspace_bytes(const g2d_sweep_desc *desc, size_t *bytes) {
     const int status = check_sweep(desc);
@@ -391,7 +488,7 @@ extern "C" int g2d_sweep_fused(const g2d_sweep_desc *desc, void *stream) {
     return desc->dtype == G2D_F32 ? sweep_fused<float>(desc, st) : sweep_fused<double>(desc, st);
 }
 
-extern "C" unsigned long long g2d_launch_count(void) { return g_launches; }
+extern "C" unsigned long long g2d_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 extern "C" int g2d_sweep_fused_profile(const g2d_sweep_desc *desc, void *stream, double *out) {
     int status = check_sweep(desc);

@@ -181,15 +181,8 @@ int band_tc_prepare(BandTcMaps *opaque, const TcPlanes &pl, int64_t m, int64_t n
         !make_map(&maps->ut_lo, pl.ut_lo, n, n) || !make_map(&maps->et_hi, pl.et_hi, n, m, BN) || !make_map(&maps->et_lo, pl.et_lo, n, m, BN) ||
         !make_map(&maps->c_hi, pl.c_hi, m, n, BN) || !make_map(&maps->c_lo, pl.c_lo, m, n, BN))
         return G2D_ERR_CUDA;
-    static bool configured[64] = {};
-    int device = 0;
-    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return G2D_ERR_CUDA;
-    if (!configured[device]) {
-        if (cudaFuncSetAttribute(band_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BAND_STAGES * BAND_STAGE_BYTES + 1024) != cudaSuccess)
-            return G2D_ERR_CUDA;
-        configured[device] = true;
-    }
-    return G2D_OK;
+    static PerDeviceOnce configured;
+    return configured.run([&] { return cudaFuncSetAttribute(band_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BAND_STAGES * BAND_STAGE_BYTES + 1024) == cudaSuccess; });
 }
 
 int launch_band_tc(const BandTcMaps *opaque, float *y, float *c, int64_t m, int64_t n, int s0, int s1, int t0, int t1, int outer_macro,

@@ -6,6 +6,9 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+#include <mutex>
+
 #include "../../include/gptq2d_b200.h"
 
 namespace g2d {
@@ -70,12 +73,32 @@ __device__ __forceinline__ F absmax_scale_value(F absmax, F divisor, int half_ki
     return s == (F)0 ? (F)1 : s;
 }
 
-// Kernel launches made by this library in this process (read by g2d_launch_count).
-extern unsigned long long g_launches;
+// Kernel launches made by this library in this process (read by g2d_launch_count); any host thread may launch.
+extern std::atomic<unsigned long long> g_launches;
 inline int check_launch() {
-    ++g_launches;
+    g_launches.fetch_add(1, std::memory_order_relaxed);
     return cudaPeekAtLastError() == cudaSuccess ? G2D_OK : G2D_ERR_CUDA;
 }
+
+// One-time set-up per device (a kernel's opt-in to more than 48 KB of dynamic shared memory), safe when several host
+// threads make their first call at the same time: `setup` runs once per device, under a lock, and must return true.
+class PerDeviceOnce {
+    std::mutex mutex_;
+    bool done_[64] = {};
+
+public:
+    template <typename Setup>
+    int run(Setup &&setup) {
+        int device = 0;
+        if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return G2D_ERR_CUDA;
+        std::lock_guard<std::mutex> lock(mutex_);
+        if (!done_[device]) {
+            if (!setup()) return G2D_ERR_CUDA;
+            done_[device] = true;
+        }
+        return G2D_OK;
+    }
+};
 
 // ---- launchers implemented in the .cu files -------------------------------------------------
 
@@ -128,8 +151,12 @@ int band_tc_prepare(BandTcMaps *maps, const TcPlanes &planes, int64_t m, int64_t
 int launch_band_tc(const BandTcMaps *maps, float *y, float *c, int64_t m, int64_t n, int s0, int s1, int t0, int t1, int outer_macro,
                    int lag_macro, int *error_flag, cudaStream_t stream);
 int tc_prepare_operands(const float *l, const float *u, int64_t m, int64_t n, const TcPlanes &planes, cudaStream_t stream);
-int launch_macro_update_tc(const TcPlanes &planes, float *y, float *c, int64_t m, int64_t n, int s0, int s1, int s_end, cudaStream_t stream,
-                           int t_first = 0, int stages = 3);
+struct MacroTcMaps {
+    alignas(64) unsigned char bytes[8 * 128];  // tensor maps of the eight operand planes with 128-row boxes (opaque here)
+};
+int macro_tc_prepare(MacroTcMaps *maps, const TcPlanes &planes, int64_t m, int64_t n);
+int launch_macro_update_tc(const MacroTcMaps *maps, const TcPlanes &planes, float *y, float *c, int64_t m, int64_t n, int s0, int s1, int s_end,
+                           cudaStream_t stream, int t_first = 0, int stages = 3);
 
 // One problem of the tensor-core triangular inverse of the factor preparation (all [n][n] float; see g2d_factors_tc.cu).
 struct FactorPlanes {

@@ -168,14 +168,10 @@ static bool factor_maps(FactorMaps *maps, const FactorPlanes &p) {
 
 // Levels b = 128, 256, ... of the doubling for one or two problems whose 128 x 128 diagonal blocks are finished.
 int launch_trinv_tc(int count, const FactorPlanes *problems, cudaStream_t stream) {
-    static bool configured[64] = {};
+    static PerDeviceOnce configured;
     const size_t smem = (size_t)STAGES * STAGE_BYTES + 1024;
-    int device = 0;
-    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return G2D_ERR_CUDA;
-    if (!configured[device]) {
-        if (cudaFuncSetAttribute(trinv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return G2D_ERR_CUDA;
-        configured[device] = true;
-    }
+    if (configured.run([&] { return cudaFuncSetAttribute(trinv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess; }) != G2D_OK)
+        return G2D_ERR_CUDA;
     TrinvJob job;
     int64_t n_max = 0;
     for (int z = 0; z < 2; ++z) {
@@ -279,14 +275,10 @@ bool syrk_tc_maps(SyrkTcMaps *maps, const float *pt_hi, const float *pt_lo, int6
 }
 
 int launch_syrk_tc(int count, const SyrkTcTarget *targets, cudaStream_t stream) {
-    static bool configured[64] = {};
+    static PerDeviceOnce configured;
     const size_t smem = (size_t)STAGES * STAGE_BYTES + 1024;
-    int device = 0;
-    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return G2D_ERR_CUDA;
-    if (!configured[device]) {
-        if (cudaFuncSetAttribute(syrk_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return G2D_ERR_CUDA;
-        configured[device] = true;
-    }
+    if (configured.run([&] { return cudaFuncSetAttribute(syrk_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess; }) != G2D_OK)
+        return G2D_ERR_CUDA;
     SyrkJob job;
     int64_t most = 0;
     for (int z = 0; z < 2; ++z) {

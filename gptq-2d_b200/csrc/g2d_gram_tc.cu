@@ -235,14 +235,10 @@ extern "C" int g2d_gram_accumulate(int64_t n, int64_t k, const float *x, float a
     const int64_t kp = gram_padded(k), tiles = ceil_div(n, (int64_t)MT);
     if (tiles * (tiles + 1) / 2 > 0x7fffffff || kp > 0x7fffffff) return G2D_ERR_TOO_LARGE;
     cudaStream_t st = (cudaStream_t)stream;
-    static bool configured[64] = {};
+    static PerDeviceOnce configured;
     const size_t smem = (size_t)STAGES * STAGE_BYTES + 1024;
-    int device = 0;
-    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return G2D_ERR_CUDA;
-    if (!configured[device]) {
-        if (cudaFuncSetAttribute(gram_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return G2D_ERR_CUDA;
-        configured[device] = true;
-    }
+    if (configured.run([&] { return cudaFuncSetAttribute(gram_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess; }) != G2D_OK)
+        return G2D_ERR_CUDA;
     float *hi = (float *)workspace, *lo = hi + n * kp;
     gram_split_transposed_kernel<<<148 * 8, dim3(32, 8), 0, st>>>(x, k, n, kp, hi, lo);
     if (check_launch() != G2D_OK) return G2D_ERR_CUDA;

@@ -221,25 +221,28 @@ int tc_prepare_operands(const float *l, const float *u, int64_t m, int64_t n, co
 
 // Sources: the macro anti-diagonals s0..s1-1; targets: t_first..s_end-1 (t_first >= s1).  `stages` 3 is the full pipeline
 // (one CTA per SM); 2 leaves room for a CTA of the tile sweep beside it (pipelined schedule).
-int launch_macro_update_tc(const TcPlanes &pl, float *y, float *c, int64_t m, int64_t n, int s0, int s1, int s_end, cudaStream_t stream,
-                           int t_first, int stages) {
-    static bool configured[64] = {};
-    if (t_first < s1) t_first = s1;
-    const int depth = stages == 2 ? 2 : STAGES;
-    const size_t smem = (size_t)depth * STAGE_BYTES + 1024;
-    int device = 0;
-    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return G2D_ERR_CUDA;
-    if (!configured[device]) {
-        if (cudaFuncSetAttribute(macro_update_tc_kernel<STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, STAGES * STAGE_BYTES + 1024) != cudaSuccess ||
-            cudaFuncSetAttribute(macro_update_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * STAGE_BYTES + 1024) != cudaSuccess)
-            return G2D_ERR_CUDA;
-        configured[device] = true;
-    }
-    TcMaps maps;
+static_assert(sizeof(TcMaps) <= sizeof(MacroTcMaps), "opaque tensor-map storage is too small");
+
+// Tensor maps of one sweep (encoded once, reused by every macro update of the sweep) and the kernels' one-time set-up.
+int macro_tc_prepare(MacroTcMaps *opaque, const TcPlanes &pl, int64_t m, int64_t n) {
+    TcMaps &maps = *reinterpret_cast<TcMaps *>(opaque);
     if (!make_map(&maps.l_hi, pl.l_hi, m, m) || !make_map(&maps.l_lo, pl.l_lo, m, m) || !make_map(&maps.c_hi, pl.c_hi, m, n) ||
         !make_map(&maps.c_lo, pl.c_lo, m, n) || !make_map(&maps.et_hi, pl.et_hi, n, m) || !make_map(&maps.et_lo, pl.et_lo, n, m) ||
         !make_map(&maps.ut_hi, pl.ut_hi, n, n) || !make_map(&maps.ut_lo, pl.ut_lo, n, n))
         return G2D_ERR_CUDA;
+    static PerDeviceOnce configured;
+    return configured.run([&] {
+        return cudaFuncSetAttribute(macro_update_tc_kernel<STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, STAGES * STAGE_BYTES + 1024) == cudaSuccess &&
+               cudaFuncSetAttribute(macro_update_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * STAGE_BYTES + 1024) == cudaSuccess;
+    });
+}
+
+int launch_macro_update_tc(const MacroTcMaps *opaque, const TcPlanes &pl, float *y, float *c, int64_t m, int64_t n, int s0, int s1, int s_end,
+                           cudaStream_t stream, int t_first, int stages) {
+    const TcMaps &maps = *reinterpret_cast<const TcMaps *>(opaque);
+    if (t_first < s1) t_first = s1;
+    const int depth = stages == 2 ? 2 : STAGES;
+    const size_t smem = (size_t)depth * STAGE_BYTES + 1024;
     const int nI2 = (int)ceil_div(m, MT), nJ2 = (int)ceil_div(n, MT);
     if (s_end <= t_first) return G2D_OK;
     const int raster = s_end - t_first > 8 ? 1 : 0;

@@ -501,15 +501,10 @@ __global__ void __launch_bounds__(TTH) tile_sweep_kernel(SweepArgs<F> P, int S, 
 template <typename F, int KIND>
 static int launch_kind(const SweepArgs<F> &args, int S, int parity, cudaStream_t stream) {
     // the opt-in to more than 48 KB of dynamic shared memory is per device
-    static bool configured[64] = {};
+    static PerDeviceOnce configured;
     const size_t smem = sizeof(F) * (4 * TILE * LD + 2 * NSUB * DBLK);
-    int device = 0;
-    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return G2D_ERR_CUDA;
-    if (!configured[device]) {
-        if (cudaFuncSetAttribute(tile_sweep_kernel<F, KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-            return G2D_ERR_CUDA;
-        configured[device] = true;
-    }
+    if (configured.run([&] { return cudaFuncSetAttribute(tile_sweep_kernel<F, KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess; }) != G2D_OK)
+        return G2D_ERR_CUDA;
     const int i_lo = S - args.nJ + 1 > 0 ? S - args.nJ + 1 : 0;
     const int i_hi = S + 1 < args.nI ? S + 1 : args.nI;
     // parity 0: every tile of the anti-diagonal; 1: tiles with even row and column index; 2: odd row and column index

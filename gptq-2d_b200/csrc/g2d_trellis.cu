@@ -254,15 +254,11 @@ __global__ void __launch_bounds__(VT) viterbi_kernel(int64_t rows, int T, const 
 template <typename F, int R>
 static int launch_viterbi(int64_t rows, int T, const void *x, const void *table, int L, int K, int V, int tail, const void *scale,
                           void *out, int64_t *states, void *workspace, cudaStream_t st) {
-    static bool configured[64] = {};
+    static PerDeviceOnce configured;
     const int64_t G = ((int64_t)1 << L) >> (K * V);
     const size_t smem = sizeof(F) * 2 * R * (size_t)G;
-    int device = 0;
-    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return G2D_ERR_CUDA;
-    if (!configured[device]) {
-        if (cudaFuncSetAttribute(viterbi_kernel<F, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) return G2D_ERR_CUDA;
-        configured[device] = true;
-    }
+    if (configured.run([&] { return cudaFuncSetAttribute(viterbi_kernel<F, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) == cudaSuccess; }) != G2D_OK)
+        return G2D_ERR_CUDA;
     int64_t blocks = ceil_div(rows, R);
     if (blocks > 148 * 8) blocks = 148 * 8;
     viterbi_kernel<F, R><<<(unsigned)blocks, VT, smem, st>>>(rows, T, (const F *)x, (const F *)table, L, K * V, V, tail, (const F *)scale,

@@ -145,6 +145,7 @@ def _sweep_fused(y, l, u, batch_shape, options: dict, quantizer_inputs, *, force
         desc.y_pre = y_pre.data_ptr()
     desc.outer_tiles = outer_tiles
     desc.reserved = SWEEP_SCHEDULE
+    desc.status = _abi.status_word(y.device).data_ptr()
     size = ctypes.c_size_t()
     _abi.check(lib.g2d_sweep_workspace_bytes(ctypes.byref(desc), ctypes.byref(size)), "g2d_sweep_workspace_bytes")
     workspace = torch.empty(size.value, dtype=torch.uint8, device=y.device)
@@ -152,6 +153,16 @@ def _sweep_fused(y, l, u, batch_shape, options: dict, quantizer_inputs, *, force
     with torch.cuda.device(y.device):
         _abi.check(lib.g2d_sweep_fused(ctypes.byref(desc), _abi.stream_of(y)), "g2d_sweep_fused")
     return y
+
+
+def check_status(device=None) -> None:
+    """Raise if a sweep on ``device`` since the last check hit a bounded wait that ran out inside a tensor-core kernel.
+
+    The sweeps are asynchronous and never read device memory from the host; a failed wait (which a healthy GPU does
+    not produce) turns the output into NaN and sets the device's status word.  This call waits for the device and
+    reads the word, so a pipeline can run many layers and check once."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    _abi.check_status(device, "gptq_2d")
 
 
 def gptq_2d_forced(x: torch.Tensor, l: torch.Tensor, u: torch.Tensor, z: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:

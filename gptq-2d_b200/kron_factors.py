@@ -63,8 +63,8 @@ def accumulate_gram(h: torch.Tensor, x: torch.Tensor, alpha: float = 1.0) -> tor
     _abi.check(lib.g2d_gram_workspace_bytes(n, k, ctypes.byref(need)), "g2d_gram_workspace_bytes")
     workspace = torch.empty(need.value, dtype=torch.uint8, device=h.device)
     with torch.cuda.device(h.device):
-        _abi.check(lib.g2d_gram_accumulate(n, k, x.data_ptr(), float(alpha), h.data_ptr(), None, workspace.data_ptr(), need.value,
-                                           _abi.stream_of(h)), "g2d_gram_accumulate")
+        _abi.check(lib.g2d_gram_accumulate(n, k, x.data_ptr(), float(alpha), h.data_ptr(), _abi.status_word(h.device).data_ptr(),
+                                           workspace.data_ptr(), need.value, _abi.stream_of(h)), "g2d_gram_accumulate")
     return h
 
 
@@ -133,10 +133,35 @@ def feedback_factors_from_grams(g: torch.Tensor, h: torch.Tensor, super_entry_sh
                                                n, works[1].data_ptr(), q, outs[1].data_ptr(), spaces[1].data_ptr(), spaces[1].numel(),
                                                flags.data_ptr(), _abi.stream_of(g)), "g2d_ldl_of_inverse_pair")
     if check:
-        pivots = flags.tolist()
-        for name, pivot in zip(("G", "H"), pivots):
-            if pivot < 0:
-                raise RuntimeError("feedback_factors_from_grams: a bounded wait inside a tensor-core kernel ran out; the result is not valid")
-            if pivot:
-                raise torch.linalg.LinAlgError(f"feedback_factors_from_grams: {name} is not positive definite (pivot {pivot} is not positive)")
+        _raise_for_flags(flags.tolist())
+    else:
+        _PENDING.append(flags)
+        if len(_PENDING) > _PENDING_LIMIT:  # a long unchecked run: settle the oldest call (it finished long ago)
+            _raise_for_flags(_PENDING.pop(0).tolist())
     return outs[0], outs[1].t()
+
+
+_PENDING: list[torch.Tensor] = []  # status flags of the calls made with check=False, oldest first
+_PENDING_LIMIT = 256
+
+
+def _raise_for_flags(pivots) -> None:
+    for name, pivot in zip(("G", "H"), pivots):
+        if pivot < 0:
+            raise RuntimeError("feedback_factors_from_grams: a bounded wait inside a tensor-core kernel ran out; the result is not valid")
+        if pivot:
+            raise torch.linalg.LinAlgError(f"feedback_factors_from_grams: {name} is not positive definite (pivot {pivot} is not positive)")
+
+
+def last_flags() -> torch.Tensor | None:
+    """The device-side ``int32[2]`` status flags (G, H) of the most recent unchecked pair call, for callers that fold
+    them into statistics of their own instead of raising."""
+    return _PENDING[-1] if _PENDING else None
+
+
+def check_pending() -> None:
+    """Settle every ``feedback_factors_from_grams(..., check=False)`` call made so far: wait for them and raise what
+    ``check=True`` would have raised (``torch.linalg.LinAlgError`` for a Gram that is not positive definite, as the
+    reference's ``torch.linalg.cholesky`` does; ``RuntimeError`` for a bounded wait that ran out)."""
+    while _PENDING:
+        _raise_for_flags(_PENDING.pop(0).tolist())

@@ -108,6 +108,16 @@ class LayerPipeline:
         self.swept = [self.swept[1], event]
         return event
 
+    def check(self) -> None:
+        """Wait for the device and raise if anything since the last check went wrong where the asynchronous calls could
+        not tell: a Hessian factor that is not positive definite (``torch.linalg.LinAlgError``, as the reference's
+        Cholesky raises) or a bounded wait that ran out inside a tensor-core kernel (``RuntimeError``)."""
+        import _abi
+        import kron_factors as K
+
+        K.check_pending()
+        _abi.check_status(self.device, "LayerPipeline")
+
     def _throttle(self):
         # the preparation of this layer may run beside the sweep of the layer before it, not further ahead
         if self.swept[0] is not None:
@@ -172,6 +182,7 @@ def quantize_matrix(item: dict, device, pipeline: LayerPipeline | None = None):
     them (calling it waits for this layer), so that the host can enqueue the next layer first."""
     import torch
 
+    import _abi
     import gptq_2d as G
     import kron_factors as K
     import quantizer_int as Q
@@ -204,26 +215,42 @@ def quantize_matrix(item: dict, device, pipeline: LayerPipeline | None = None):
         events[2].record(main)
         scale = Q.int_abs_max_scale_triton(w, qmin=-8, qmax=7, dtype=torch.float16).expand(m, n)
     codes = torch.round(z / scale)
-    on_device = {"lo": codes.min(), "hi": codes.max(), "finite": torch.isfinite(z).all(), "code_sum": codes.double().sum()}
+    # Statistics stay on the device, packed into one float64 vector, and travel to pinned host memory on a stream of
+    # their own behind this matrix only: the host can enqueue the next matrix before it reads them.  Folded in: what
+    # the asynchronous calls could not report, the pivot flags of this matrix's factor preparation and the device's
+    # status word (set when a bounded wait inside a tensor-core kernel ran out).
+    factor_flags = K.last_flags()
+    parts = [codes.min(), codes.max(), torch.isfinite(z).all(), codes.double().sum(),
+             factor_flags.abs().max() if factor_flags is not None else torch.zeros((), device=device),
+             _abi.status_word(device).abs().max()]
     if m * n <= 4096 * 4096:  # the objective needs two more products; keep it to the smaller matrices
         rtn = torch.clamp(torch.round(w / scale), -8, 7) * scale
         r, r0 = (z - w).double(), (rtn - w).double()
-        on_device["objective"] = ((g.double() @ r) * (r @ h.double())).sum()
-        on_device["objective_rtn"] = ((g.double() @ r0) * (r0 @ h.double())).sum()
-
+        parts += [((g.double() @ r) * (r @ h.double())).sum(), ((g.double() @ r0) * (r0 @ h.double())).sum()]
+    on_device = torch.stack([p.double() for p in parts])
     ready = torch.cuda.Event()
     ready.record(torch.cuda.current_stream(device))
+    on_host = torch.empty(on_device.shape, dtype=torch.float64).pin_memory()
+    fetched = torch.cuda.Event()
+    side = pipeline.out if pipeline is not None else torch.cuda.current_stream(device)
+    side.wait_event(ready)
+    with torch.cuda.stream(side):
+        on_host.copy_(on_device, non_blocking=True)
+        fetched.record(side)
+    on_device.record_stream(side)
 
     def finish() -> dict:
-        ready.synchronize()  # this matrix only: the next one may already be running
+        fetched.synchronize()  # this matrix only: the next one may already be running
+        values = on_host.tolist()
         stats = {
             **item, "prep_ms": events[0].elapsed_time(events[1]) if pipeline is None else None,
             "sweep_ms": events[1].elapsed_time(events[2]),
-            "codes_in_range": bool((on_device["lo"] >= -8) & (on_device["hi"] <= 7)), "finite": bool(on_device["finite"]),
-            "code_sum": float(on_device["code_sum"].item()),
+            "codes_in_range": values[0] >= -8 and values[1] <= 7,
+            "factors_ok": values[4] == 0, "waits_ok": values[5] == 0, "code_sum": values[3],
         }
-        if "objective" in on_device:
-            stats["objective_vs_rtn"] = float(on_device["objective"].item() / on_device["objective_rtn"].item())
+        stats["finite"] = bool(values[2]) and stats["factors_ok"] and stats["waits_ok"]
+        if len(values) > 6:
+            stats["objective_vs_rtn"] = values[6] / values[7]
         return stats
 
     return finish() if pipeline is None else finish

@@ -3,8 +3,14 @@
  *
  * Every entry point is extern "C", takes plain device pointers and sizes,
  * launches its kernels asynchronously on the CUDA stream it is given, never
- * allocates, never synchronizes and never reads device memory from the host,
- * so a call can be captured in a CUDA graph.  Buffers are owned by the caller.
+ * allocates device memory, never synchronizes and never reads device memory
+ * from the host, so a call can be captured in a CUDA graph.  Buffers are owned
+ * by the caller.  Two exceptions, both one-time set-up: the first call of a kernel
+ * on a device sets a function attribute, and the first g2d_sweep_fused call on a
+ * device that takes the pipelined schedule creates the library's side streams and
+ * events; make those first calls outside stream capture (inside a capture the
+ * latter returns G2D_ERR_UNSUPPORTED instead).  Calls are safe from several host
+ * threads; work given to one stream is ordered as issued.
  * Return value: 0 (G2D_OK) or a negative g2d_status; g2d_status_string names it.
  *
  * Each declaration cites the function of the reference (IST-DASLab/GPTQ-2D,
@@ -63,6 +69,9 @@ typedef struct g2d_sweep_desc {
     size_t workspace_bytes;
     int32_t outer_tiles;         /* tile anti-diagonals per far update; 0 selects the default */
     int32_t reserved;            /* launch schedule: 0 library default, 1 tile, 2 macro, 3 pipelined schedule */
+    int32_t *status;             /* optional device int32: set to -1 when a bounded wait inside a tensor-core update kernel
+                                    ran out (the kernels never spin without limit).  Y is then overwritten with NaN as well,
+                                    so such a sweep cannot be mistaken for a result.  Never cleared by the library. */
 } g2d_sweep_desc;
 
 const char *g2d_status_string(int status);
@@ -90,7 +99,10 @@ int g2d_sweep_fused(const g2d_sweep_desc *desc, void *stream);
  *    first call before any stream capture begins.
  *  - All calls on a device share the array, which keeps the previous call's contents (the sweep clears what it
  *    needs cleared).  Two calls that overlap on the GPU, e.g. on different streams, race: serialise them.
- *  - Calls no cudaMalloc / cudaFree and no allocating library routine; same results as g2d_sweep_fused. */
+ *  - Calls no cudaMalloc / cudaFree and no allocating library routine.  It always takes the tile schedule, so its
+ *    results are those of g2d_sweep_fused with desc->reserved = 1, bit for bit (for one fp32 matrix whose sides are
+ *    multiples of 4, g2d_sweep_fused by default takes the pipelined schedule, which sums the feedback in another
+ *    order and may differ at rounding ties). */
 #define G2D_STATIC_SCRATCH_BYTES (32u * 1024u * 1024u)
 int g2d_sweep_fused_static(const g2d_sweep_desc *desc, void *stream);
 

@@ -231,14 +231,49 @@ def d_sided():
     save("d_sided_fp64.npz", **out)
 
 
+def factors_fp32_large():
+    """float32 ``ldl_of_inverse`` of heavy-tailed Grams at n = 1024 and 2048 (the reference's LAPACK path), next to its
+    own float64 result on the same float32-valued matrix.  The Grams come from a recipe whose float32 values are the
+    same bits everywhere (``oracle.dyadic_gram``), so only a sample of rows of each factor is stored."""
+    sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+    from oracle import oracle
+
+    out = {}
+    for n in (1024, 2048):
+        gram = oracle.dyadic_gram(n, seed=n)
+        rows = np.unique(np.concatenate([np.arange(0, n, n // 32), np.arange(n - 8, n)]))
+        l32 = RR.ldl_of_inverse(torch.from_numpy(gram)).numpy()
+        l64 = RR.ldl_of_inverse(torch.from_numpy(gram).double()).numpy()
+        out[f"rows{n}"], out[f"l32_{n}"], out[f"l64_{n}"] = rows, l32[rows], l64[rows]
+        out[f"gram_sum{n}"] = gram.astype(np.float64).sum()
+        out[f"gap{n}"] = np.abs(l32.astype(np.float64) - l64).max()
+        out[f"lmax{n}"] = np.abs(l64).max()
+    save("factors_fp32_large.npz", **out)
+
+
+def config1_small():
+    """The second benchmark configuration's distributions (0.1 % outliers at 10 sigma, sigma_h = 1 Hessian factors) at
+    256 x 384 through the reference's gptq_2d_torch in float64: the INT4 codes, on float32-valued inputs."""
+    sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+    from oracle import oracle
+
+    m, n = 256, 384
+    w, g, h = oracle.config1_layer(m, n, seed=41)
+    l = RR.ldl_of_inverse(torch.from_numpy(g).double()).float().double().contiguous()
+    u = RR.ldl_of_inverse(torch.from_numpy(h).double()).float().double().T.contiguous()
+    scale = QI.int_abs_max_scale_torch(torch.from_numpy(w), qmin=-8, qmax=7, dtype=torch.float16)
+    full = scale.double().expand(m, n).contiguous()
+    zero = torch.zeros(m, n, dtype=torch.float64)
+    quantizer = functools.partial(QI.affine_quantizer_torch, qmin=-8, qmax=7)
+    z = R.gptq_2d_torch(torch.from_numpy(w).double(), l, u, quantizer=quantizer, quantizer_inputs=(full, zero))
+    save("config1_small_fp64.npz", scale=scale, codes=torch.round(z / full).to(torch.int8), l=l.float(), u=u.float(),
+         w_sum=np.float64(w.astype(np.float64).sum()))
+
+
 if __name__ == "__main__":
     torch.set_num_threads(8)
-    sweep_fp64()
-    sweep_batched()
-    quartic_64()
-    config0_fp32()
-    quantizers()
-    trellis()
-    trellis_sweep()
-    factors()
-    d_sided()
+    steps = dict(sweep_fp64=sweep_fp64, sweep_batched=sweep_batched, quartic_64=quartic_64, config0_fp32=config0_fp32,
+                 quantizers=quantizers, trellis=trellis, trellis_sweep=trellis_sweep, factors=factors, d_sided=d_sided,
+                 factors_fp32_large=factors_fp32_large, config1_small=config1_small)
+    for name in sys.argv[1:] or steps:  # name the steps to (re)generate; all of them by default
+        steps[name]()

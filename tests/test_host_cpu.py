@@ -28,7 +28,7 @@ def test_descriptor_layout_matches_header():
     import _abi
 
     # field order and C alignment rules give these sizes for the header's structs on LP64
-    assert ctypes.sizeof(_abi.SweepDesc) == 8 + 3 * 8 + 9 * 8 + 4 * 8 + 2 * 8 + 2 * 8 + 2 * 8 + 8
+    assert ctypes.sizeof(_abi.SweepDesc) == 8 + 3 * 8 + 9 * 8 + 4 * 8 + 2 * 8 + 2 * 8 + 2 * 8 + 8 + 8
     assert ctypes.sizeof(_abi.StageDesc) == 16 + 3 * 8 + 7 * 8
 
 

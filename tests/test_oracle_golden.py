@@ -111,6 +111,38 @@ def test_factors_golden(oracle):
     assert np.abs(d - np.diag(np.diag(d))).max() < 1e-9 * np.abs(np.diag(d)).max()
 
 
+def test_large_float32_factors_golden(oracle):
+    """Heavy-tailed Grams at n = 1024 and 2048: the recipe reproduces the matrices the reference factored, the LAPACK
+    restatement equals the reference's float64 rows, and the reference's own float32 rows lie where the fixture says."""
+    g = load_golden("factors_fp32_large.npz")
+    for n in (1024, 2048):
+        gram = oracle.dyadic_gram(n, seed=n)
+        assert gram.astype(np.float64).sum() == float(g[f"gram_sum{n}"])  # same bits as when the fixture was made
+        rows = g[f"rows{n}"]
+        l64 = oracle.ldl_of_inverse_lapack(gram.astype(np.float64))
+        assert np.abs(l64[rows] - g[f"l64_{n}"]).max() < 1e-10
+        # the stored rows are a sample: their float32-to-float64 distance stays inside the whole factor's
+        assert np.abs(g[f"l32_{n}"].astype(np.float64) - g[f"l64_{n}"]).max() <= float(g[f"gap{n}"]) < 3e-6
+    small = oracle.dyadic_gram(130, seed=5).astype(np.float64)
+    for size in (1, 2, 5):
+        assert np.abs(oracle.ldl_of_inverse_lapack(small, size) - oracle.ldl_of_inverse(small, size)).max() < 1e-12
+
+
+def test_config1_small_golden(oracle):
+    """Outliers at 10 sigma and sigma_h = 1 Hessian factors: the oracle's float64 sweep gives the reference's INT4 codes."""
+    g = load_golden("config1_small_fp64.npz")
+    m, n = 256, 384
+    w, gm, hm = oracle.config1_layer(m, n, seed=41)
+    assert w.astype(np.float64).sum() == float(g["w_sum"])
+    l, u = g["l"].astype(np.float64), g["u"].astype(np.float64)
+    assert np.abs(l - oracle.ldl_of_inverse_lapack(gm.astype(np.float64))).max() < 1e-6  # the stored factors are float32-rounded
+    scale = np.broadcast_to(g["scale"].astype(np.float64), (m, n))
+    assert np.array_equal(oracle.absmax_scale(w, -8, 7, oracle.FP16), g["scale"])
+    z = oracle.sweep(w.astype(np.float64), l, u, kind=oracle.Q_AFFINE, scale=scale, zero_point=np.zeros((m, n)), qmin=-8, qmax=7)
+    assert np.array_equal(np.rint(z / scale).astype(np.int8), g["codes"])
+    assert np.abs(g["codes"]).max() <= 8 and (g["codes"] == -8).any()
+
+
 def test_d_sided_golden(oracle):
     g = load_golden("d_sided_fp64.npz")
     for k in range(int(g["count"])):

@@ -3,8 +3,7 @@
 ``g2d_sweep_fused_static`` serves callers that have no way to allocate device memory (a plugin inside an application
 that owns the whole device, or a running low-latency service that must not trigger cudaMalloc's device-wide
 synchronisation): they pass inputs and outputs only and the scratch planes come from a fixed array inside the
-library.  This file is collected last on purpose, so a failure here cannot hide the other GPU tests in a run that
-stops at the first failure; it passes alone in a fresh process as well as after them.
+library.  The entry point always takes the tile schedule, so the comparison call asks for that schedule too.
 """
 import ctypes
 
@@ -49,14 +48,19 @@ def test_static_scratch_sweep_matches_workspace_sweep():
     x, l, u, scale, zero = _problem(8, 8, 1, torch.float32, 0)
     _abi.check(lib.g2d_sweep_fused_static(ctypes.byref(_descriptor(_abi, x, l, u, scale, zero)), stream), "g2d_sweep_fused_static")
     # two calls in a row on different problems: the second finds the first one's leftovers in the shared array
-    for m, n, batch, dtype, seed in ((300, 500, 2, torch.float32, 1), (130, 97, 3, torch.float64, 2), (300, 500, 2, torch.float32, 3)):
+    # the last case is the most common caller shape (one float32 matrix, sides multiples of 4) at exactly the size limit
+    for m, n, batch, dtype, seed in ((300, 500, 2, torch.float32, 1), (130, 97, 3, torch.float64, 2), (300, 500, 2, torch.float32, 3),
+                                     (2048, 2048, 1, torch.float32, 4)):
         x, l, u, scale, zero = _problem(m, n, batch, dtype, seed)
 
         expected = x.clone()
         desc = _descriptor(_abi, expected, l, u, scale, zero)
+        desc.reserved = 1  # the tile schedule, which the allocation-free entry point always takes
         size = ctypes.c_size_t()
         _abi.check(lib.g2d_sweep_workspace_bytes(ctypes.byref(desc), ctypes.byref(size)), "g2d_sweep_workspace_bytes")
         assert size.value <= STATIC_BYTES
+        if (m, n, batch) == (2048, 2048, 1):
+            assert size.value == STATIC_BYTES
         workspace = torch.empty(size.value, dtype=torch.uint8, device="cuda")
         desc.workspace, desc.workspace_bytes = workspace.data_ptr(), size.value
         _abi.check(lib.g2d_sweep_fused(ctypes.byref(desc), stream), "g2d_sweep_fused")
@@ -67,9 +71,10 @@ def test_static_scratch_sweep_matches_workspace_sweep():
         free_before, reserved_before = torch.cuda.mem_get_info()[0], torch.cuda.memory_reserved()
         _abi.check(lib.g2d_sweep_fused_static(ctypes.byref(desc), stream), "g2d_sweep_fused_static")
         torch.cuda.synchronize()
-        # nothing was allocated, by torch or behind its back
+        # nothing was allocated: not through torch, and not behind its back either (the device-wide figure may move by
+        # what other processes on the same GPU do, so it only has to stay within a small margin)
         assert torch.cuda.memory_reserved() == reserved_before
-        assert torch.cuda.mem_get_info()[0] == free_before
+        assert torch.cuda.mem_get_info()[0] >= free_before - (8 << 20)
         assert torch.equal(actual, expected)  # same kernels, same schedule: identical bits
         assert not torch.equal(actual, x)
 
