@@ -18,7 +18,7 @@ ABI_VERSION = 2
 
 F32, F64 = 0, 1
 FP16, BF16 = 0, 1
-Q_ROUND, Q_AFFINE, Q_FORCED = 0, 1, 4
+Q_ROUND, Q_AFFINE, Q_ABSMAX_DYNAMIC, Q_TRELLIS, Q_FORCED = 0, 1, 2, 3, 4
 
 _vp, _i64, _i32, _dbl = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int32, ctypes.c_double
 
@@ -42,6 +42,27 @@ class SweepDesc(ctypes.Structure):
     ]
 
 
+class SuperDesc(ctypes.Structure):
+    """Mirror of ``g2d_super_desc``."""
+    _fields_ = [
+        ("dtype", _i32), ("quant_kind", _i32), ("p", _i32), ("q", _i32), ("inner_block", _i32), ("outer_block", _i32),
+        ("batch", _i64), ("m", _i64), ("n", _i64),
+        ("y", _vp),
+        ("l", _vp), ("l_offsets", _vp),
+        ("u", _vp), ("u_offsets", _vp),
+        ("lead_count", _i32), ("half", _i32),
+        ("lead_size", _i64 * 4), ("lead_factor", _vp * 4),
+        ("scale", _vp), ("scale_offsets", _vp),
+        ("zero", _vp), ("zero_offsets", _vp),
+        ("scale_row_stride", _i64), ("scale_col_stride", _i64), ("zero_row_stride", _i64), ("zero_col_stride", _i64),
+        ("qmin", _dbl), ("qmax", _dbl),
+        ("table", _vp),
+        ("trellis_L", _i32), ("trellis_K", _i32), ("trellis_V", _i32), ("tail_biting", _i32),
+        ("codes", _vp),
+        ("workspace", _vp), ("workspace_bytes", ctypes.c_size_t),
+    ]
+
+
 class StageDesc(ctypes.Structure):
     """Mirror of ``g2d_stage_desc``."""
     _fields_ = [
@@ -59,6 +80,11 @@ _SIGNATURES = {
     "g2d_sweep_workspace_bytes": (ctypes.c_int, [ctypes.POINTER(SweepDesc), ctypes.POINTER(ctypes.c_size_t)]),
     "g2d_sweep_fused": (ctypes.c_int, [ctypes.POINTER(SweepDesc), _vp]),
     "g2d_sweep_fused_static": (ctypes.c_int, [ctypes.POINTER(SweepDesc), _vp]),
+    "g2d_super_workspace_bytes": (ctypes.c_int, [ctypes.POINTER(SuperDesc), ctypes.POINTER(ctypes.c_size_t)]),
+    "g2d_sweep_super_entry": (ctypes.c_int, [ctypes.POINTER(SuperDesc), _vp]),
+    "g2d_trellis_code_bytes": (ctypes.c_int, [_i32, _i32, _i32, _i32, _i32, ctypes.POINTER(_i64)]),
+    "g2d_trellis_quantize_packed": (ctypes.c_int, [ctypes.c_int, _i64, _i32, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp, ctypes.c_size_t, _vp]),
+    "g2d_trellis_decode": (ctypes.c_int, [ctypes.c_int, _i64, _i32, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp]),
     "g2d_sweep_fused_profile": (ctypes.c_int, [ctypes.POINTER(SweepDesc), _vp, ctypes.POINTER(ctypes.c_double)]),
     "g2d_launch_count": (ctypes.c_ulonglong, []),
     "g2d_stage_push": (ctypes.c_int, [ctypes.POINTER(StageDesc), _vp, _i64, _i64, _vp]),

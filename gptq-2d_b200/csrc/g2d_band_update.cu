@@ -179,27 +179,30 @@ __global__ void __launch_bounds__(BTH) band_update_kernel(BandArgs<F> P, int nTI
     const int64_t m = P.m, n = P.n;
     const int64_t i0 = (int64_t)TI * BT, j0 = (int64_t)TJ * BT;
     const int64_t i1 = min(i0 + BT, m) - 1, j1 = min(j0 + BT, n) - 1;  // last row / column of the tile
-    BandGeom<F, MODE> g{P.P, P.Q, P.s0, P.s1, P.s_end};
-    // does the tile hold any target?
-    if (g.stage(i1, j1) < P.s1 || g.stage(i0, j0) >= P.s_end) return;
-    // k ranges: block rows (down) / block columns (right) that hold sources for this tile
-    const int64_t PP = MODE == BAND_TILE ? TILE : (MODE == BAND_PLAIN ? 1 : P.P);
-    const int64_t QQ = MODE == BAND_TILE ? TILE : (MODE == BAND_PLAIN ? 1 : P.Q);
-    int64_t dk_lo = (P.s0 - g.bcol(j1)) * PP, dk_hi = (P.s1 - g.bcol(j0)) * PP;
-    dk_lo = max(dk_lo, (int64_t)0);
-    dk_hi = min(min(dk_hi, m), g.brow(i1) * PP);  // sources lie in block rows above the targets
-    int64_t rk_lo = (P.s0 - g.brow(i1)) * QQ, rk_hi = (P.s1 - g.brow(i0)) * QQ;
-    rk_lo = max(rk_lo, (int64_t)0);
-    rk_hi = min(min(rk_hi, n), g.bcol(j1) * QQ);
-    if (MODE == BAND_TILE && P.filter == 2 && !((TI & 1) && (TJ & 1))) return;
-    if (MODE == BAND_TILE && P.filter == 1) {
-        // single-stage use: the down source is tile (dk_lo / 64, TJ), the right source tile (TI, rk_lo / 64)
-        if ((TJ & 1) || ((dk_lo / TILE) & 1)) dk_hi = dk_lo;
-        if ((TI & 1) || ((rk_lo / TILE) & 1)) rk_hi = rk_lo;
-    }
     const int tid = threadIdx.x, ty = tid >> 3, tx = tid & 7;
 
     for (int64_t batch = blockIdx.z; batch < P.batch; batch += gridDim.z) {
+        // the band of this batch: the same for every batch unless the batches are the skewed slabs of an N-factor sweep
+        const int64_t behind = (MODE == BAND_GENERAL && P.skew != nullptr) ? P.skew[batch] : 0;
+        const int64_t s0 = P.s0 - behind, s1 = P.s1 - behind, s_end = P.s_end - behind;
+        BandGeom<F, MODE> g{P.P, P.Q, s0, s1, s_end};
+        // does the tile hold any target?
+        if (g.stage(i1, j1) < s1 || g.stage(i0, j0) >= s_end) continue;
+        // k ranges: block rows (down) / block columns (right) that hold sources for this tile
+        const int64_t PP = MODE == BAND_TILE ? TILE : (MODE == BAND_PLAIN ? 1 : P.P);
+        const int64_t QQ = MODE == BAND_TILE ? TILE : (MODE == BAND_PLAIN ? 1 : P.Q);
+        int64_t dk_lo = (s0 - g.bcol(j1)) * PP, dk_hi = (s1 - g.bcol(j0)) * PP;
+        dk_lo = max(dk_lo, (int64_t)0);
+        dk_hi = min(min(dk_hi, m), g.brow(i1) * PP);  // sources lie in block rows above the targets
+        int64_t rk_lo = (s0 - g.brow(i1)) * QQ, rk_hi = (s1 - g.brow(i0)) * QQ;
+        rk_lo = max(rk_lo, (int64_t)0);
+        rk_hi = min(min(rk_hi, n), g.bcol(j1) * QQ);
+        if (MODE == BAND_TILE && P.filter == 2 && !((TI & 1) && (TJ & 1))) continue;
+        if (MODE == BAND_TILE && P.filter == 1) {
+            // single-stage use: the down source is tile (dk_lo / 64, TJ), the right source tile (TI, rk_lo / 64)
+            if ((TJ & 1) || ((dk_lo / TILE) & 1)) dk_hi = dk_lo;
+            if ((TI & 1) || ((rk_lo / TILE) & 1)) rk_hi = rk_lo;
+        }
         F *yg = P.y + batch * m * n, *cg = P.c + batch * m * n;
         const F *eg = P.e + batch * m * n;
         const F *lg = P.l + (P.l_off ? P.l_off[batch] : 0);
@@ -224,7 +227,7 @@ __global__ void __launch_bounds__(BTH) band_update_kernel(BandArgs<F> P, int nTI
                     const int64_t j = j0 + own(tx, y);
                     if (i < m && j < n) {
                         const int64_t st = g.stage(i, j);
-                        if (st >= P.s1 && st < P.s_end) {
+                        if (st >= s1 && st < s_end) {
                             cg[i * n + j] += acc[x][y];
                             if (P.down_into_y) yg[i * n + j] += acc[x][y];
                         }
@@ -248,7 +251,7 @@ __global__ void __launch_bounds__(BTH) band_update_kernel(BandArgs<F> P, int nTI
                     const int64_t j = j0 + own(tx, y);
                     if (i < m && j < n) {
                         const int64_t st = g.stage(i, j);
-                        if (st >= P.s1 && st < P.s_end) yg[i * n + j] += acc[x][y];
+                        if (st >= s1 && st < s_end) yg[i * n + j] += acc[x][y];
                     }
                 }
             }

@@ -178,6 +178,7 @@ struct SyrkTcMaps {
 };
 struct SyrkTcTarget {
     const SyrkTcMaps *maps;
+    const float *pt_hi, *pt_lo;  // the planes the maps describe
     float *a;
     int64_t n;
     int t_lo, t_hi;  // target 128-row tile rows [t_lo, t_hi), tile columns up to the diagonal
@@ -186,6 +187,12 @@ struct SyrkTcTarget {
 };
 bool syrk_tc_maps(SyrkTcMaps *maps, const float *pt_hi, const float *pt_lo, int64_t n);
 int launch_syrk_tc(int count, const SyrkTcTarget *targets, cudaStream_t stream);
+
+// Trellis (Viterbi) search of `rows` sequences (see g2d_trellis.cu); `codes` optional packed paths, code bytes apart.
+int64_t trellis_code_bytes(int T, int L, int K, int V, int tail_biting);
+size_t trellis_scratch_bytes(int dtype, int64_t rows, int T, int L, int K, int V);
+int launch_trellis(int dtype, int64_t rows, int T, const void *x, const void *table, int L, int K, int V, int tail, const void *scale,
+                   void *out, int64_t *states, void *workspace, uint8_t *codes, cudaStream_t st);
 
 template <typename F>
 int launch_tile_sweep(const SweepArgs<F> &args, int S, cudaStream_t stream, int parity = 0);
@@ -203,12 +210,16 @@ struct BandArgs {
     int down_into_y;          // also add the down product into Y (the generic path keeps Y live)
     int mode;                 // BandMode
     int filter;               // tile mode only: 0 none, 1 sources with even tile row and column only, 2 targets with odd tile row and column only
+    const int32_t *skew = nullptr;  // general mode only: batch b takes the stages s0 - skew[b], s1 - skew[b], s_end - skew[b]
 };
 
 template <typename F>
 int launch_band_update(const BandArgs<F> &args, cudaStream_t stream);
 
+// skew (device, one int per batch, may be null): batch b works at stage s - skew[b] (slabs of an N-factor sweep);
+// z_stride: values of z per batch (0: exactly the stage's d p q)
 template <typename F>
-int launch_stage_push(const g2d_stage_desc &d, const F *z, int64_t s, int64_t s1, cudaStream_t stream);
+int launch_stage_push(const g2d_stage_desc &d, const F *z, int64_t s, int64_t s1, cudaStream_t stream, const int32_t *skew = nullptr,
+                      int64_t z_stride = 0);
 
 }  // namespace g2d

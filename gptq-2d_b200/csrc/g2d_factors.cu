@@ -518,7 +518,8 @@ int ldl_run(int count, const int64_t *ns, F *const *as, const int *sizes, F *con
             const int64_t o = (int64_t)kb_lo * FB;
             const int t_all = (int)(o / 128), t_next = t_all - GROUP * FB / 128;  // tile rows above the group; those of the next group start at t_next
             const int kw = (int)(ns[z] - o < GROUP * FB ? ns[z] - o : GROUP * FB);
-            SyrkTcTarget t{&pt_maps[z][(kb_lo / GROUP) & 1], (float *)B.p[z].a, ns[z], t_next, t_all, kw, B.p[z].flag};
+            SyrkTcTarget t{&pt_maps[z][(kb_lo / GROUP) & 1], B.p[z].pt_hi[(kb_lo / GROUP) & 1], B.p[z].pt_lo[(kb_lo / GROUP) & 1],
+                           (float *)B.p[z].a, ns[z], t_next, t_all, kw, B.p[z].flag};
             next[targets] = t;
             t.t_lo = 0;
             t.t_hi = t_next;

@@ -202,6 +202,17 @@ int launch_trinv_tc(int count, const FactorPlanes *problems, cudaStream_t stream
 // one 128 x 128 tile per CTA.  Both operands are the same K-major planes pt[r][k] = a[o + k][r] (hi and lo), which
 // the panel kernel writes as it finishes a block row.  One CTA owns each target entry and no other kernel touches the
 // targets meanwhile, so the result does not depend on scheduling.
+// Accuracy.  The tensor cores add each product into the float accumulator with truncation, which biases long sums of
+// one sign by about 1e-8 of the sum per term, and the diagonal of this update is a sum of squares, subtracted from pivots
+// that a damped, badly conditioned Gram leaves one or two orders of magnitude smaller than the sum.  Two measures keep the
+// factors at the accuracy of a float32 LAPACK factorization: the k range is cut into slices of 64 with one accumulator
+// each in tensor memory (added up in registers, round to nearest), and the diagonal entries are left out here and
+// updated by syrk_diag_kernel with a float64 sum.
+constexpr int SYRK_SLICE_CHUNKS = 2;                      // k = 64 per accumulator
+constexpr int SYRK_SLICES = SYRK_TC_K / (SYRK_SLICE_CHUNKS * KC);
+constexpr uint32_t SYRK_TMEM_COLS = SYRK_SLICES * MT;     // 512: all of tensor memory, one CTA per SM (as its shared memory already requires)
+static_assert(SYRK_TMEM_COLS <= 512, "tensor memory holds 512 columns");
+
 struct SyrkJob {
     CUtensorMap hi[2], lo[2];
     float *a[2];
@@ -232,7 +243,8 @@ __global__ void __launch_bounds__(TC_THREADS) syrk_tc_kernel(const __grid_consta
 
     const uint32_t smem_base = (smem_u32(tc_smem_raw) + 1023u) & ~1023u;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t tmem = tc_ring_setup(ring, TRINV_TMEM_COLS);
+    const uint32_t tmem = tc_ring_setup(ring, SYRK_TMEM_COLS);
+    const int slices = (chunks + SYRK_SLICE_CHUNKS - 1) / SYRK_SLICE_CHUNKS;
     if (warp == 0) {
         if (lane == 0)
             tc_ring_produce(ring, smem_base, chunks, [&](int ch, uint32_t dst, uint64_t *bar) {
@@ -242,30 +254,93 @@ __global__ void __launch_bounds__(TC_THREADS) syrk_tc_kernel(const __grid_consta
                 tma_load_2d(dst + 3 * TILE_BYTES, lo, ch * KC, j0, bar);
             });
     } else if (warp == 1) {
-        if (lane == 0) tc_ring_mma(ring, smem_base, tmem, chunks);
+        if (lane == 0) {
+            // the ring's MMA loop with one accumulator per slice of SYRK_SLICE_CHUNKS chunks
+            for (int ch = 0; ch < chunks; ++ch) {
+                const int stage = ch % STAGES, round = ch / STAGES;
+                if (!mbar_wait(&ring.full[stage], round & 1)) {
+                    ring.failed = 1;
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t acc = tmem + (uint32_t)(ch / SYRK_SLICE_CHUNKS) * MT;
+                const bool first = ch % SYRK_SLICE_CHUNKS == 0;
+                const uint32_t a_hi = smem_base + stage * STAGE_BYTES, a_lo = a_hi + TILE_BYTES, b_hi = a_hi + 2 * TILE_BYTES, b_lo = a_hi + 3 * TILE_BYTES;
+#pragma unroll
+                for (int ks = 0; ks < KC / 8; ++ks) {
+                    const uint32_t off = ks * 32;
+                    umma_tf32(acc, umma_desc(a_hi + off), umma_desc(b_hi + off), IDESC, (first && ks == 0) ? 0u : 1u);
+                    umma_tf32(acc, umma_desc(a_lo + off), umma_desc(b_hi + off), IDESC, 1u);
+                    umma_tf32(acc, umma_desc(a_hi + off), umma_desc(b_lo + off), IDESC, 1u);
+                }
+                umma_commit(&ring.empty[stage]);
+            }
+            umma_commit(&ring.accum);
+        }
     } else {
         const int q = warp & 3;
         const bool go = tc_ring_accumulator_ready(ring);
         if (go) {
             const int64_t gi = (int64_t)i0 + q * 32 + lane;  // always a row of the matrix: the targets lie above the group
             for (int cb = 0; cb < MT / 32; ++cb) {
-                uint32_t v[32];
-                tmem_load_32(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(cb * 32), v);
+                float sum[32];
+#pragma unroll
+                for (int x = 0; x < 32; ++x) sum[x] = 0.f;
+                for (int sl = 0; sl < slices; ++sl) {
+                    uint32_t v[32];
+                    tmem_load_32(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(sl * MT + cb * 32), v);
+#pragma unroll
+                    for (int x = 0; x < 32; ++x) sum[x] += __uint_as_float(v[x]);
+                }
                 const int64_t gj0 = (int64_t)j0 + cb * 32;
                 float *dst = a + gi * n + gj0;
 #pragma unroll
                 for (int x = 0; x < 32; x += 4) {
                     if (gj0 + x <= gi) {  // groups that start right of the diagonal are never read
-                        asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + x), "f"(-__uint_as_float(v[x])),
-                                     "f"(-__uint_as_float(v[x + 1])), "f"(-__uint_as_float(v[x + 2])), "f"(-__uint_as_float(v[x + 3]))
+                        if (gi - (gj0 + x) < 4) {  // the diagonal entry belongs to syrk_diag_kernel
+#pragma unroll
+                            for (int c = 0; c < 4; ++c)
+                                if (gj0 + x + c == gi) sum[x + c] = 0.f;
+                        }
+                        asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + x), "f"(-sum[x]), "f"(-sum[x + 1]),
+                                     "f"(-sum[x + 2]), "f"(-sum[x + 3])
                                      : "memory");
                     }
                 }
             }
         }
     }
-    const bool failed = tc_ring_teardown(ring, tmem, TRINV_TMEM_COLS);
+    const bool failed = tc_ring_teardown(ring, tmem, SYRK_TMEM_COLS);
     if (threadIdx.x == 0 && failed && flag) atomicExch(flag, -1);
+}
+
+// The diagonal of the same update: a[r][r] -= sum_k p[r][k]^2 with p = hi + lo (the float32 panel value, exactly), the sum
+// in float64.  One warp per row.
+struct SyrkDiagJob {
+    const float *hi[2], *lo[2];
+    float *a[2];
+    int64_t n[2];
+    int64_t r_lo[2], r_hi[2];
+    int kw[2];
+};
+__global__ void syrk_diag_kernel(const SyrkDiagJob job) {
+    const int z = blockIdx.y, lane = threadIdx.x & 31;
+    const int64_t r_lo = z ? job.r_lo[1] : job.r_lo[0], r_hi = z ? job.r_hi[1] : job.r_hi[0];
+    const float *hi = z ? job.hi[1] : job.hi[0], *lo = z ? job.lo[1] : job.lo[0];
+    float *a = z ? job.a[1] : job.a[0];
+    const int64_t n = z ? job.n[1] : job.n[0];
+    const int kw = z ? job.kw[1] : job.kw[0];
+    const int64_t warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    for (int64_t r = r_lo + (((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5); r < r_hi; r += warps) {
+        double sum = 0.0;
+        for (int k = lane; k < kw; k += 32) {
+            const double p = (double)hi[r * SYRK_TC_K + k] + (double)lo[r * SYRK_TC_K + k];
+            sum += p * p;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        if (lane == 0) a[r * n + r] = (float)((double)a[r * n + r] - sum);
+    }
 }
 
 bool syrk_tc_maps(SyrkTcMaps *maps, const float *pt_hi, const float *pt_lo, int64_t n) {
@@ -280,9 +355,14 @@ int launch_syrk_tc(int count, const SyrkTcTarget *targets, cudaStream_t stream) 
     if (configured.run([&] { return cudaFuncSetAttribute(syrk_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess; }) != G2D_OK)
         return G2D_ERR_CUDA;
     SyrkJob job;
-    int64_t most = 0;
+    SyrkDiagJob diag;
+    int64_t most = 0, most_rows = 0;
     for (int z = 0; z < 2; ++z) {
         const SyrkTcTarget &t = targets[z < count ? z : 0];
+        diag.hi[z] = t.pt_hi; diag.lo[z] = t.pt_lo; diag.a[z] = t.a; diag.n[z] = t.n; diag.kw[z] = t.kw;
+        diag.r_lo[z] = (int64_t)t.t_lo * MT;
+        diag.r_hi[z] = (int64_t)t.t_hi * MT;  // whole tile rows above the group: every one a row of the matrix
+        most_rows = diag.r_hi[z] - diag.r_lo[z] > most_rows ? diag.r_hi[z] - diag.r_lo[z] : most_rows;
         memcpy(&job.hi[z], t.maps->hi, sizeof(CUtensorMap));
         memcpy(&job.lo[z], t.maps->lo, sizeof(CUtensorMap));
         job.a[z] = t.a;
@@ -297,6 +377,11 @@ int launch_syrk_tc(int count, const SyrkTcTarget *targets, cudaStream_t stream) 
     if (most <= 0) return G2D_OK;
     if (most > 0x7fffffff) return G2D_ERR_TOO_LARGE;
     syrk_tc_kernel<<<dim3((unsigned)most, count), TC_THREADS, smem, stream>>>(job);
+    if (check_launch() != G2D_OK) return G2D_ERR_CUDA;
+    if (most_rows > 0) {
+        int64_t blocks = ceil_div(most_rows * 32, 256);
+        syrk_diag_kernel<<<dim3((unsigned)(blocks < 1184 ? blocks : 1184), count), 256, 0, stream>>>(diag);
+    }
     return check_launch();
 }
 

@@ -18,13 +18,39 @@ struct StageArgs {
     const int64_t *l_off, *u_off;
     int64_t batch, m, n, s, s1;
     int p, q;
+    // N-factor sweeps run their slabs as batches that are `skew[batch]` stages behind (null: none); z then holds
+    // z_stride values per batch (0: the stage's own d p q)
+    const int32_t *skew;
+    int64_t z_stride;
 };
 
 template <typename F>
 __global__ void stage_error_kernel(StageArgs<F> A) {
     const int64_t mbar = A.m / A.p, nbar = A.n / A.q;
+    const int64_t pq = (int64_t)A.p * A.q;
+    if (A.skew != nullptr) {
+        // every batch at a stage of its own: z_stride values per batch, the first d p q of them in use
+        const int64_t total = A.z_stride * A.batch;
+        for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (int64_t)gridDim.x * blockDim.x) {
+            const int64_t batch = t / A.z_stride, rest = t % A.z_stride;
+            const int64_t s = A.s - A.skew[batch];
+            if (s < 0 || s >= mbar + nbar - 1) continue;
+            const int64_t i_lo = max((int64_t)0, s - nbar + 1), i_hi = min(s + 1, mbar);
+            const int64_t k = rest / pq;
+            if (k >= i_hi - i_lo) continue;
+            const int a = (int)(rest % pq) / A.q, b = (int)(rest % pq) % A.q;
+            const int64_t i = (i_lo + k) * A.p + a, j = (s - i_lo - k) * A.q + b;
+            const int64_t at = batch * A.m * A.n + i * A.n + j;
+            const F zv = A.z[t];
+            const F ev = zv - A.y[at];
+            A.e[at] = ev;
+            A.c[at] += ev;
+            A.y[at] = zv;
+        }
+        return;
+    }
     const int64_t i_lo = max((int64_t)0, A.s - nbar + 1), i_hi = min(A.s + 1, mbar);
-    const int64_t d = i_hi - i_lo, pq = (int64_t)A.p * A.q, per_batch = d * pq;
+    const int64_t d = i_hi - i_lo, per_batch = d * pq;
     const int64_t total = per_batch * A.batch;
     for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (int64_t)gridDim.x * blockDim.x) {
         const int64_t batch = t / per_batch, rest = t % per_batch;
@@ -32,7 +58,7 @@ __global__ void stage_error_kernel(StageArgs<F> A) {
         const int a = (int)(rest % pq) / A.q, b = (int)(rest % pq) % A.q;
         const int64_t i = (i_lo + k) * A.p + a, j = (A.s - i_lo - k) * A.q + b;
         const int64_t at = batch * A.m * A.n + i * A.n + j;
-        const F zv = A.z[t];
+        const F zv = A.z[batch * (A.z_stride ? A.z_stride : per_batch) + rest];
         const F ev = zv - A.y[at];
         A.e[at] = ev;
         A.c[at] += ev;
@@ -46,10 +72,11 @@ __global__ void stage_push_kernel(StageArgs<F> A) {
     const int p = A.p, q = A.q;
     const int64_t pq = (int64_t)p * q;
     const int64_t dd = 1 + blockIdx.y;  // receivers on coarse anti-diagonal s + dd
-    const int64_t sr = A.s + dd;
-    const int64_t r_lo = max((int64_t)0, sr - nbar + 1), r_hi = min(sr + 1, mbar);
-    const int64_t count = (r_hi - r_lo) * pq;
     for (int64_t batch = blockIdx.z; batch < A.batch; batch += gridDim.z) {
+        const int64_t s = A.s - (A.skew ? A.skew[batch] : 0), sr = s + dd;
+        if (s < 0 || sr >= mbar + nbar - 1) continue;
+        const int64_t r_lo = max((int64_t)0, sr - nbar + 1), r_hi = min(sr + 1, mbar);
+        const int64_t count = (r_hi - r_lo) * pq;
         F *yg = A.y + batch * A.m * A.n, *cg = A.c + batch * A.m * A.n;
         const F *eg = A.e + batch * A.m * A.n;
         const F *lg = A.l + (A.l_off ? A.l_off[batch] : 0);
@@ -79,18 +106,21 @@ __global__ void stage_push_kernel(StageArgs<F> A) {
 }
 
 template <typename F>
-int launch_stage_push(const g2d_stage_desc &d, const F *z, int64_t s, int64_t s1, cudaStream_t stream) {
+int launch_stage_push(const g2d_stage_desc &d, const F *z, int64_t s, int64_t s1, cudaStream_t stream, const int32_t *skew, int64_t z_stride) {
     StageArgs<F> A;
+    A.skew = skew; A.z_stride = z_stride;
     A.y = (F *)d.y; A.c = (F *)d.c; A.e = (F *)d.e;
     A.l = (const F *)d.l; A.u = (const F *)d.u; A.z = z;
     A.l_off = d.l_offsets; A.u_off = d.u_offsets;
     A.batch = d.batch; A.m = d.m; A.n = d.n; A.s = s; A.s1 = s1;
     A.p = d.p; A.q = d.q;
     const int64_t mbar = d.m / d.p, nbar = d.n / d.q, stages = mbar + nbar - 1;
-    if (s < 0 || s >= stages || s1 <= s) return G2D_ERR_BAD_ARGUMENT;
-    if (s1 > stages) s1 = stages;
+    if (skew == nullptr && (s < 0 || s >= stages)) return G2D_ERR_BAD_ARGUMENT;
+    if (s1 <= s) return G2D_ERR_BAD_ARGUMENT;
+    if (skew == nullptr && s1 > stages) s1 = stages;
     const int64_t i_lo = s - nbar + 1 > 0 ? s - nbar + 1 : 0, i_hi = s + 1 < mbar ? s + 1 : mbar;
-    const int64_t total = (i_hi - i_lo) * d.p * d.q * d.batch;
+    const int64_t total = skew != nullptr ? z_stride * d.batch : (i_hi - i_lo) * d.p * d.q * d.batch;
+    if (total <= 0) return G2D_OK;
     {
         const int threads = 128;
         int64_t blocks = ceil_div(total, threads);
@@ -112,7 +142,7 @@ int launch_stage_push(const g2d_stage_desc &d, const F *z, int64_t s, int64_t s1
     return G2D_OK;
 }
 
-template int launch_stage_push<float>(const g2d_stage_desc &, const float *, int64_t, int64_t, cudaStream_t);
-template int launch_stage_push<double>(const g2d_stage_desc &, const double *, int64_t, int64_t, cudaStream_t);
+template int launch_stage_push<float>(const g2d_stage_desc &, const float *, int64_t, int64_t, cudaStream_t, const int32_t *, int64_t);
+template int launch_stage_push<double>(const g2d_stage_desc &, const double *, int64_t, int64_t, cudaStream_t, const int32_t *, int64_t);
 
 }  // namespace g2d

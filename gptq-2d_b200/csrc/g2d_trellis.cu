@@ -12,6 +12,13 @@
 // One CTA runs R sequences at once: B_t and B_{t-1} of each live in shared memory (2 R G values), every
 // table entry is loaded once per step for all R sequences, and one barrier separates the steps.  The
 // arg-min h of every (step, group) goes to global scratch (one byte each) for the walk back.
+//
+// Packed paths.  A path is also emitted as its bit string, the storage format of a trellis code (T K bits per sequence
+// when tail-biting; the reference only notes that "the T K-bit code can be recovered", quantizer_trellis.py:11-14).
+// The string is the sequence of the K V bits that every step shifts into the state, most significant bit first,
+// preceded, when the path is not tail-biting, by the L - K V upper bits of the first state (tail-biting paths need no
+// header: their first state continues the end of the string).  State t is then the L bits of the string that end
+// with step t's symbol, read circularly for a tail-biting path.  Bit i of the string is bit i % 8 of byte i / 8.
 #include "g2d_common.cuh"
 
 namespace g2d {
@@ -45,7 +52,8 @@ __device__ __forceinline__ void load_pair(const double *p, double &a, double &b)
 template <typename F, int R>
 __global__ void __launch_bounds__(VT) viterbi_kernel(int64_t rows, int T, const F *__restrict__ x, const F *__restrict__ table,
                                                      int Lbits, int shift, int V, int tail_biting, const F *__restrict__ scale,
-                                                     F *__restrict__ out, int64_t *__restrict__ states, uint8_t *__restrict__ choices) {
+                                                     F *__restrict__ out, int64_t *__restrict__ states, uint8_t *__restrict__ choices,
+                                                     uint8_t *__restrict__ codes, int64_t code_bytes) {
     extern __shared__ __align__(16) unsigned char g2d_vsmem[];
     const int64_t S = (int64_t)1 << Lbits, G = S >> shift;
     const int H = 1 << shift;
@@ -234,10 +242,24 @@ __global__ void __launch_bounds__(VT) viterbi_kernel(int64_t rows, int T, const 
                 const int64_t row = row0 + tid;
                 long long state = seq_state[tid];
                 const F sc = scale ? scale[row] : (F)1;
+                uint8_t *code = (pass == 1 && codes) ? codes + row * code_bytes : nullptr;
+                const int header = tail_biting ? 0 : Lbits - shift;
+                if (code)
+                    for (int64_t b = 0; b < code_bytes; ++b) code[b] = 0;
                 for (int t = steps - 1; t >= stop; --t) {
                     if (pass == 1) {
                         for (int v = 0; v < V; ++v) out[row * T + (int64_t)t * V + v] = mul_rn(table[state * V + v], sc);
                         if (states) states[row * steps + t] = state;
+                        if (code) {
+                            // this step's symbol, most significant bit first; the first state's upper bits when a header is kept
+                            for (int b = 0; b < shift; ++b) {
+                                const int64_t at = header + (int64_t)t * shift + b;
+                                if ((state >> (shift - 1 - b)) & 1) code[at >> 3] |= (uint8_t)(1u << (at & 7));
+                            }
+                            if (t == 0)
+                                for (int b = 0; b < header; ++b)
+                                    if ((state >> (Lbits - 1 - b)) & 1) code[b >> 3] |= (uint8_t)(1u << (b & 7));
+                        }
                     }
                     if (t > stop) {
                         const long long low = state >> shift;
@@ -251,9 +273,35 @@ __global__ void __launch_bounds__(VT) viterbi_kernel(int64_t rows, int T, const 
     }
 }
 
+// Values (and optionally states) of stored bit strings: one thread per (sequence, step) rebuilds the state from the L
+// bits of the string that end with the step's symbol.
+template <typename F>
+__global__ void trellis_decode_kernel(int64_t rows, int T, const uint8_t *__restrict__ codes, int64_t code_bytes, const F *__restrict__ table,
+                                      int Lbits, int shift, int V, int tail_biting, const F *__restrict__ scale, F *__restrict__ out,
+                                      int64_t *__restrict__ states) {
+    const int steps = T / V;
+    const int header = tail_biting ? 0 : Lbits - shift;
+    const int64_t bits = header + (int64_t)steps * shift, total = rows * steps;
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t row = idx / steps;
+        const int t = (int)(idx % steps);
+        const uint8_t *code = codes + row * code_bytes;
+        const int64_t end = header + (int64_t)(t + 1) * shift;  // one past the last bit of the state
+        long long state = 0;
+        for (int b = 0; b < Lbits; ++b) {
+            int64_t at = end - Lbits + b;
+            if (at < 0) at += bits;  // tail-biting only: a string with a header always reaches back far enough
+            state = (state << 1) | ((code[at >> 3] >> (at & 7)) & 1);
+        }
+        const F sc = scale ? scale[row] : (F)1;
+        for (int v = 0; v < V; ++v) out[row * T + (int64_t)t * V + v] = mul_rn(table[state * V + v], sc);
+        if (states) states[row * steps + t] = state;
+    }
+}
+
 template <typename F, int R>
 static int launch_viterbi(int64_t rows, int T, const void *x, const void *table, int L, int K, int V, int tail, const void *scale,
-                          void *out, int64_t *states, void *workspace, cudaStream_t st) {
+                          void *out, int64_t *states, void *workspace, uint8_t *codes, int64_t code_bytes, cudaStream_t st) {
     static PerDeviceOnce configured;
     const int64_t G = ((int64_t)1 << L) >> (K * V);
     const size_t smem = sizeof(F) * 2 * R * (size_t)G;
@@ -262,13 +310,13 @@ static int launch_viterbi(int64_t rows, int T, const void *x, const void *table,
     int64_t blocks = ceil_div(rows, R);
     if (blocks > 148 * 8) blocks = 148 * 8;
     viterbi_kernel<F, R><<<(unsigned)blocks, VT, smem, st>>>(rows, T, (const F *)x, (const F *)table, L, K * V, V, tail, (const F *)scale,
-                                                             (F *)out, states, (uint8_t *)workspace);
+                                                             (F *)out, states, (uint8_t *)workspace, codes, code_bytes);
     return check_launch();
 }
 
 template <typename F>
 static int trellis_dispatch(int64_t rows, int T, const void *x, const void *table, int L, int K, int V, int tail, const void *scale,
-                            void *out, int64_t *states, void *workspace, cudaStream_t st) {
+                            void *out, int64_t *states, void *workspace, uint8_t *codes, int64_t code_bytes, cudaStream_t st) {
     const int64_t G = ((int64_t)1 << L) >> (K * V);
     const size_t per_seq = sizeof(F) * 2 * (size_t)G;
     const size_t budget = 200 * 1024;
@@ -280,10 +328,28 @@ static int trellis_dispatch(int64_t rows, int T, const void *x, const void *tabl
     if (rows > 148 && 2 * per_seq <= budget) R = 2;
     if (rows > 2 * 148 && 4 * per_seq <= budget) R = 4;
     switch (R) {
-    case 4: return launch_viterbi<F, 4>(rows, T, x, table, L, K, V, tail, scale, out, states, workspace, st);
-    case 2: return launch_viterbi<F, 2>(rows, T, x, table, L, K, V, tail, scale, out, states, workspace, st);
-    default: return launch_viterbi<F, 1>(rows, T, x, table, L, K, V, tail, scale, out, states, workspace, st);
+    case 4: return launch_viterbi<F, 4>(rows, T, x, table, L, K, V, tail, scale, out, states, workspace, codes, code_bytes, st);
+    case 2: return launch_viterbi<F, 2>(rows, T, x, table, L, K, V, tail, scale, out, states, workspace, codes, code_bytes, st);
+    default: return launch_viterbi<F, 1>(rows, T, x, table, L, K, V, tail, scale, out, states, workspace, codes, code_bytes, st);
     }
+}
+
+int64_t trellis_code_bytes(int T, int L, int K, int V, int tail_biting) {
+    const int64_t bits = (tail_biting ? 0 : L - K * V) + (int64_t)(T / V) * K * V;
+    return (bits + 7) / 8;
+}
+
+size_t trellis_scratch_bytes(int dtype, int64_t rows, int T, int L, int K, int V) {
+    const int64_t steps = T / V, slots = steps > 1 ? steps - 1 : 1, G = ((int64_t)1 << L) >> (K * V);
+    (void)dtype;
+    return ((size_t)rows * slots * G + 255) & ~(size_t)255;
+}
+
+int launch_trellis(int dtype, int64_t rows, int T, const void *x, const void *table, int L, int K, int V, int tail, const void *scale,
+                   void *out, int64_t *states, void *workspace, uint8_t *codes, cudaStream_t st) {
+    const int64_t code_bytes = trellis_code_bytes(T, L, K, V, tail);
+    return dtype == G2D_F32 ? trellis_dispatch<float>(rows, T, x, table, L, K, V, tail, scale, out, states, workspace, codes, code_bytes, st)
+                            : trellis_dispatch<double>(rows, T, x, table, L, K, V, tail, scale, out, states, workspace, codes, code_bytes, st);
 }
 
 }  // namespace g2d
@@ -299,8 +365,7 @@ static int trellis_check(int dtype, int64_t rows, int32_t T, int32_t L, int32_t 
 extern "C" int g2d_trellis_workspace_bytes(int dtype, int64_t rows, int32_t T, int32_t L, int32_t K, int32_t V, size_t *bytes) {
     const int status = trellis_check(dtype, rows, T, L, K, V);
     if (status != G2D_OK || !bytes) return status != G2D_OK ? status : G2D_ERR_BAD_ARGUMENT;
-    const int64_t steps = T / V, slots = steps > 1 ? steps - 1 : 1, G = ((int64_t)1 << L) >> (K * V);
-    *bytes = ((size_t)rows * slots * G + 255) & ~(size_t)255;
+    *bytes = trellis_scratch_bytes(dtype, rows, T, L, K, V);
     return G2D_OK;
 }
 
@@ -314,7 +379,44 @@ extern "C" int g2d_trellis_quantize(int dtype, int64_t rows, int32_t T, const vo
     size_t need = 0;
     g2d_trellis_workspace_bytes(dtype, rows, T, L, K, V, &need);
     if (!workspace || workspace_bytes < need) return G2D_ERR_WORKSPACE;
+    return launch_trellis(dtype, rows, T, x, table, L, K, V, tail_biting, scale, out, states, workspace, nullptr, (cudaStream_t)stream);
+}
+
+extern "C" int g2d_trellis_code_bytes(int32_t T, int32_t L, int32_t K, int32_t V, int32_t tail_biting, int64_t *bytes) {
+    const int status = trellis_check(G2D_F32, 0, T, L, K, V);
+    if (status != G2D_OK || !bytes) return status != G2D_OK ? status : G2D_ERR_BAD_ARGUMENT;
+    *bytes = trellis_code_bytes(T, L, K, V, tail_biting);
+    return G2D_OK;
+}
+
+extern "C" int g2d_trellis_quantize_packed(int dtype, int64_t rows, int32_t T, const void *x, const void *table, int32_t L, int32_t K,
+                                           int32_t V, int32_t tail_biting, const void *scale, void *out, uint8_t *codes,
+                                           void *workspace, size_t workspace_bytes, void *stream) {
+    const int status = trellis_check(dtype, rows, T, L, K, V);
+    if (status != G2D_OK) return status;
+    if (rows == 0) return G2D_OK;
+    if (!x || !table || !out || !codes) return G2D_ERR_BAD_ARGUMENT;
+    if (!tail_biting && (int64_t)(T / V) * K * V + L - K * V < L) return G2D_ERR_BAD_ARGUMENT;
+    if (!workspace || workspace_bytes < trellis_scratch_bytes(dtype, rows, T, L, K, V)) return G2D_ERR_WORKSPACE;
+    return launch_trellis(dtype, rows, T, x, table, L, K, V, tail_biting, scale, out, nullptr, workspace, codes, (cudaStream_t)stream);
+}
+
+extern "C" int g2d_trellis_decode(int dtype, int64_t rows, int32_t T, const uint8_t *codes, const void *table, int32_t L, int32_t K,
+                                  int32_t V, int32_t tail_biting, const void *scale, void *out, int64_t *states, void *stream) {
+    const int status = trellis_check(dtype, rows, T, L, K, V);
+    if (status != G2D_OK) return status;
+    if (rows == 0) return G2D_OK;
+    if (!codes || !table || !out) return G2D_ERR_BAD_ARGUMENT;
+    if (tail_biting && (int64_t)(T / V) * K * V < L) return G2D_ERR_UNSUPPORTED;  // a string shorter than one state does not determine it
+    const int64_t bytes = trellis_code_bytes(T, L, K, V, tail_biting), total = rows * (T / V);
+    int64_t blocks = ceil_div(total, 256);
+    if (blocks > 148 * 32) blocks = 148 * 32;
     cudaStream_t st = (cudaStream_t)stream;
-    return dtype == G2D_F32 ? trellis_dispatch<float>(rows, T, x, table, L, K, V, tail_biting, scale, out, states, workspace, st)
-                            : trellis_dispatch<double>(rows, T, x, table, L, K, V, tail_biting, scale, out, states, workspace, st);
+    if (dtype == G2D_F32)
+        trellis_decode_kernel<float><<<(unsigned)blocks, 256, 0, st>>>(rows, T, codes, bytes, (const float *)table, L, K * V, V, tail_biting,
+                                                                      (const float *)scale, (float *)out, states);
+    else
+        trellis_decode_kernel<double><<<(unsigned)blocks, 256, 0, st>>>(rows, T, codes, bytes, (const double *)table, L, K * V, V, tail_biting,
+                                                                       (const double *)scale, (double *)out, states);
+    return check_launch();
 }

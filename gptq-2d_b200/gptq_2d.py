@@ -96,20 +96,34 @@ _AFFINE_SUPER = (quantizer_int.affine_quantizer_super_entry_cuda,)
 
 
 def _fusable(quantizer: Callable, quantizer_inputs, super_entry_shape) -> dict | None:
-    """Recognise a quantizer of this package and return the fused engine's options, or None."""
+    """Recognise a quantizer of this package and return the options of the engine that has it inside its kernels, or
+    None.  Plain entries (and 1 x 1 super-entries) under the round and affine quantizers go to the fused tile engine;
+    larger super-entries, the dynamic abs-max quantizer and the trellis quantizer to the library's super-entry sweep
+    (``super=True`` in the options), whose whole stage loop runs inside one C call."""
+    import quantizer_trellis
+
     func, keywords = quantizer, {}
     while isinstance(func, functools.partial):
         if func.args:
             return None
         keywords = {**func.keywords, **keywords}
         func = func.func
-    if super_entry_shape is not None and tuple(super_entry_shape) != (1, 1):
-        return None
     plain = super_entry_shape is None
+    single = plain or tuple(super_entry_shape) == (1, 1)
     if func is (round_quantizer if plain else round_quantizer_super_entry) and not keywords and not quantizer_inputs:
-        return dict(kind=_abi.Q_ROUND)
+        return dict(kind=_abi.Q_ROUND, super=not single)
     if func in (_AFFINE_PLAIN if plain else _AFFINE_SUPER) and len(quantizer_inputs) == 2 and set(keywords) <= {"qmin", "qmax"}:
-        return dict(kind=_abi.Q_AFFINE, qmin=keywords.get("qmin", -torch.inf), qmax=keywords.get("qmax", torch.inf))
+        return dict(kind=_abi.Q_AFFINE, qmin=keywords.get("qmin", -torch.inf), qmax=keywords.get("qmax", torch.inf), super=not single)
+    if plain:
+        return None
+    if func is quantizer_int.int_abs_max_quantizer_cuda and not quantizer_inputs and set(keywords) == {"qmin", "qmax", "dtype"}:
+        if keywords["dtype"] in (torch.float16, torch.bfloat16) and keywords["qmin"] < keywords["qmax"]:
+            return dict(kind=_abi.Q_ABSMAX_DYNAMIC, qmin=keywords["qmin"], qmax=keywords["qmax"], half=_abi.half_code(keywords["dtype"]), super=True)
+    if (func is quantizer_trellis.trellis_quantizer_super_entry_cuda and len(quantizer_inputs) == 1
+            and {"table", "K"} <= set(keywords) <= {"table", "K", "tail_biting"}):
+        table, K, (p, q) = keywords["table"], keywords["K"], super_entry_shape
+        if table.dim() == 2 and table.size(1) <= 2 and K * table.size(1) <= 8 and (p * q) % table.size(1) == 0 and table.size(0) & (table.size(0) - 1) == 0:
+            return dict(kind=_abi.Q_TRELLIS, table=table, K=K, tail_biting=keywords.get("tail_biting", True), super=True)
     return None
 
 
@@ -152,6 +166,67 @@ def _sweep_fused(y, l, u, batch_shape, options: dict, quantizer_inputs, *, force
     desc.workspace, desc.workspace_bytes = workspace.data_ptr(), size.value
     with torch.cuda.device(y.device):
         _abi.check(lib.g2d_sweep_fused(ctypes.byref(desc), _abi.stream_of(y)), "g2d_sweep_fused")
+    return y
+
+
+def _sweep_super(y, l, u, batch_shape, options: dict, quantizer_inputs, super_entry_shape, inner_block_size, outer_block_size, *,
+                 lead_factors=(), codes: torch.Tensor | None = None):
+    """The library's super-entry sweep (``g2d_sweep_super_entry``): the stage loop, the quantizer and the pushes in one C
+    call.  ``lead_factors``: the leading modes' factors of an N-factor sweep, y then being ``[*lead sizes, m, n]``.
+    Returns None when the inputs have a form the library does not take (the caller then uses the per-stage engine)."""
+    m, n = y.shape[-2:]
+    p, q = super_entry_shape or (1, 1)
+    lib = _abi.library()
+    l, u = _row_major(l), _row_major(u)
+    desc = _abi.SuperDesc()
+    desc.dtype, desc.quant_kind, desc.p, desc.q = _abi.dtype_code(y.dtype), options["kind"], p, q
+    desc.inner_block, desc.outer_block = inner_block_size, outer_block_size
+    desc.batch, desc.m, desc.n = batch_shape.numel(), m, n
+    keep = [l, u, _abi.batch_offsets(l, batch_shape), _abi.batch_offsets(u, batch_shape)]
+    desc.y, desc.l, desc.u = y.data_ptr(), l.data_ptr(), u.data_ptr()
+    desc.l_offsets, desc.u_offsets = _abi.ptr(keep[2]), _abi.ptr(keep[3])
+    desc.lead_count = len(lead_factors)
+    for k, factor in enumerate(lead_factors):
+        factor = factor.contiguous()
+        keep.append(factor)
+        desc.lead_size[k], desc.lead_factor[k] = factor.size(0), factor.data_ptr()
+    kind = options["kind"]
+    if kind == _abi.Q_AFFINE:
+        scale, zero = quantizer_inputs
+        y_flat = y.flatten(start_dim=-2)
+        quantizer_int._validate_affine_inputs(y_flat, scale, zero, y_flat, options["qmin"], options["qmax"])
+        so, zo = _abi.batch_offsets(scale, batch_shape), _abi.batch_offsets(zero, batch_shape)
+        keep += [scale, zero, so, zo]
+        desc.scale, desc.zero, desc.scale_offsets, desc.zero_offsets = scale.data_ptr(), zero.data_ptr(), _abi.ptr(so), _abi.ptr(zo)
+        desc.scale_row_stride, desc.scale_col_stride = _matrix_strides(scale, m, n)
+        desc.zero_row_stride, desc.zero_col_stride = _matrix_strides(zero, m, n)
+        desc.qmin, desc.qmax = float(options["qmin"]), float(options["qmax"])
+    elif kind == _abi.Q_ABSMAX_DYNAMIC:
+        desc.qmin, desc.qmax, desc.half = float(options["qmin"]), float(options["qmax"]), options["half"]
+    elif kind == _abi.Q_TRELLIS:
+        (scale,) = quantizer_inputs
+        assert scale.device == y.device, "the CUDA trellis quantizer requires Y, scale, and table on one CUDA device"
+        # one scale per matrix of the batch, or one for all: anything finer goes through the per-stage engine
+        per_batch, offsets = scale.to(y.dtype).reshape(-1), None
+        if per_batch.numel() != 1:
+            try:
+                per_batch = scale.to(y.dtype).broadcast_to(*batch_shape, 1, 1, 1).reshape(-1).contiguous()
+            except RuntimeError:
+                return None
+            offsets = torch.arange(per_batch.numel(), dtype=torch.int64, device=y.device)
+        table = options["table"].to(y).contiguous()
+        keep += [per_batch, table, offsets]
+        desc.scale, desc.scale_offsets, desc.table = per_batch.data_ptr(), _abi.ptr(offsets), table.data_ptr()
+        desc.trellis_L, desc.trellis_K, desc.trellis_V = table.size(0).bit_length() - 1, options["K"], table.size(1)
+        desc.tail_biting = int(bool(options["tail_biting"]))
+        if codes is not None:
+            desc.codes = codes.data_ptr()
+    size = ctypes.c_size_t()
+    _abi.check(lib.g2d_super_workspace_bytes(ctypes.byref(desc), ctypes.byref(size)), "g2d_super_workspace_bytes")
+    workspace = torch.empty(size.value, dtype=torch.uint8, device=y.device)
+    desc.workspace, desc.workspace_bytes = workspace.data_ptr(), size.value
+    with torch.cuda.device(y.device):
+        _abi.check(lib.g2d_sweep_super_entry(ctypes.byref(desc), _abi.stream_of(y)), "g2d_sweep_super_entry")
     return y
 
 
@@ -232,8 +307,10 @@ def _run(x, l, u, quantizer, super_entry_shape, inner_block_size, outer_block_si
     if y.numel() == 0:
         return y
     options = _fusable(quantizer, quantizer_inputs, super_entry_shape)
-    if options is not None:
+    if options is not None and not options["super"]:
         return _sweep_fused(y, l, u, batch_shape, options, quantizer_inputs)
+    if options is not None and _sweep_super(y, l, u, batch_shape, options, quantizer_inputs, super_entry_shape, inner_block_size, outer_block_size) is not None:
+        return y
     return _sweep_generic(y, l, u, batch_shape, quantizer, quantizer_inputs, super_entry_shape, inner_block_size, outer_block_size)
 
 

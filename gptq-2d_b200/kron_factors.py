@@ -43,6 +43,8 @@ def ldl_of_inverse(M: torch.Tensor, size: int = 1, check: bool = True) -> torch.
             raise RuntimeError("ldl_of_inverse: a bounded wait inside a tensor-core kernel ran out; the result is not valid")
         if pivot:
             raise torch.linalg.LinAlgError(f"ldl_of_inverse: the matrix is not positive definite (pivot {pivot} is not positive)")
+    else:
+        _PENDING.append((flag, ("the matrix",)))  # settled by check_pending(), like the pair call's flags
     return out
 
 
@@ -76,32 +78,81 @@ def feedback_factors(A: torch.Tensor, B: torch.Tensor, super_entry_shape: tuple[
 
 
 @torch.no_grad()
-def gptq_d_sided(x: torch.Tensor, factors, *, quantizer=None, quantizer_inputs=(), **sweep_options) -> torch.Tensor:
+def gptq_d_sided(x: torch.Tensor, factors, *, quantizer=None, quantizer_inputs=(), super_entry_shape=(1, 1),
+                 inner_block_size: int = 8, outer_block_size: int = 64, dense_row_factor: bool = False, **sweep_options) -> torch.Tensor:
     """N-factor (D-sided) rounding of an ``n_1 x ... x n_D`` tensor under one unit lower triangular factor per mode
     (Algorithm 4 of the paper; the reference's slow ``alg4``, gptq_2d_reference.py:269-294).
 
-    The D-sided sweep on ``[n_1, ..., n_D]`` equals the two-sided sweep on the row-major reshape
-    ``[n_1 ... n_{D-1}, n_D]`` with the row factor ``kron(L_1, ..., L_{D-1})`` and the column factor ``L_D^T``, so it
-    runs on the same fused engine.  The Kronecker row factor is formed explicitly here (``(n_1 ... n_{D-1})^2`` values);
-    ``quantizer`` and ``quantizer_inputs`` follow ``gptq_2d`` on the reshaped matrix.
+    The tensor is swept as ``n_1 ... n_{D-2}`` slabs ``[n_{D-1}, n_D]`` under ``(L_{D-1}, L_D^T)``; the leading modes
+    couple the slabs through scaled additions of the finished slabs' residuals, mode by mode, so no factor larger than
+    ``n_d x n_d`` is ever formed, and all slabs advance together along the hyper-anti-diagonals ``i_1 + ... + i_D = s``.
+    ``quantizer`` is one of this package's quantizers as ``gptq_2d_super_entry`` takes it (default: rounding), applied to
+    ``(1, ..., 1, p, q)`` super-entries of the last two modes; ``quantizer_inputs`` are its tensors for the
+    ``[n_1 ... n_{D-2}, n_{D-1}, n_D]`` view (an affine scale is ``[..., n_{D-1}, n_D]``).
+
+    ``dense_row_factor=True`` (or a quantizer the library does not know, or more than six modes) takes the other route:
+    the two-sided sweep on ``[n_1 ... n_{D-1}, n_D]`` with the explicit Kronecker row factor
+    ``kron(L_1, ..., L_{D-1})``, where ``quantizer`` follows ``gptq_2d`` on that matrix and ``sweep_options`` are passed on.
     """
     import functools
 
     import gptq_2d as engine
+    from quantizer_int import round_quantizer, round_quantizer_super_entry
 
     factors = list(factors)
     assert x.dim() == len(factors) >= 1, "expected one factor per mode"
     assert all(f.shape == (k, k) for f, k in zip(factors, x.shape)), "factor d must be n_d x n_d"
-    rows = x.numel() // x.size(-1) if x.numel() else 0
+    assert x.is_cuda and all(f.device == x.device and f.dtype == x.dtype for f in factors), "X and the factors must share a CUDA device and dtype"
     if x.numel() == 0:
         return x.clone()
+    p, q = super_entry_shape
+    structured = not dense_row_factor and not sweep_options and 3 <= x.dim() <= 6  # two modes: the two-sided engines below
+    options = None
+    if structured:
+        chosen = quantizer if quantizer is not None else round_quantizer_super_entry
+        if chosen is round_quantizer:
+            chosen = round_quantizer_super_entry
+        options = engine._fusable(chosen, quantizer_inputs, (p, q))
+    if options is not None:
+        lead = factors[:-2]
+        m, n = x.shape[-2:]
+        assert m % p == 0 and n % q == 0, "the super-entry shape must divide the last two modes"
+        y = x.clone(memory_format=torch.contiguous_format)
+        batch_shape = y.shape[:-2]
+        options = {**options, "super": True}
+        l, u = factors[-2].contiguous(), factors[-1].t().contiguous()
+        if engine._sweep_super(y, l, u, batch_shape, options, quantizer_inputs, (p, q), inner_block_size, outer_block_size,
+                               lead_factors=lead) is not None:
+            return y
+    # the explicit Kronecker row factor on the two-sided engines
+    rows = x.numel() // x.size(-1)
     row_factor = functools.reduce(torch.kron, [f.contiguous() for f in factors[:-1]]) if len(factors) > 1 else torch.ones(1, 1, dtype=x.dtype, device=x.device)
     options = dict(sweep_options)
     if quantizer is not None:
         options["quantizer"] = quantizer
-    z = engine.gptq_2d(x.reshape(rows, x.size(-1)), row_factor.contiguous(), factors[-1].t().contiguous(),
-                       quantizer_inputs=quantizer_inputs, **options)
+    run = engine.gptq_2d
+    if tuple(super_entry_shape) != (1, 1):
+        run, options["super_entry_shape"] = engine.gptq_2d_super_entry, tuple(super_entry_shape)
+    z = run(x.reshape(rows, x.size(-1)), row_factor.contiguous(), factors[-1].t().contiguous(), quantizer_inputs=quantizer_inputs, **options)
     return z.reshape(x.shape)
+
+
+@torch.no_grad()
+def alg4(X: torch.Tensor, L, Q=None) -> torch.Tensor:
+    """The reference's ``alg4(X, L, Q)`` by name and positional signature (gptq_2d_reference.py:269-294): ``L`` holds one
+    unit lower triangular factor per mode, ``Q(values, *indices)`` rounds the entries of a stage given their index
+    tensors (default: nearest integer).  Rounding runs on the mode-by-mode engine; any other ``Q`` is called stage by
+    stage on the two-sided per-stage engine over the ``[n_1 ... n_{D-1}, n_D]`` view."""
+    if Q is None:
+        return gptq_d_sided(X, L)
+    shape, n_last = X.shape, X.size(-1)
+
+    def quantizer(y_flat, selection, *, out):
+        flat = torch.arange(*selection.indices(y_flat.size(-1)), device=y_flat.device)
+        indices = torch.unravel_index(flat, shape)
+        out.copy_(Q(y_flat[..., selection], *indices))
+
+    return gptq_d_sided(X, L, quantizer=quantizer, dense_row_factor=True)
 
 
 @torch.no_grad()
@@ -133,30 +184,31 @@ def feedback_factors_from_grams(g: torch.Tensor, h: torch.Tensor, super_entry_sh
                                                n, works[1].data_ptr(), q, outs[1].data_ptr(), spaces[1].data_ptr(), spaces[1].numel(),
                                                flags.data_ptr(), _abi.stream_of(g)), "g2d_ldl_of_inverse_pair")
     if check:
-        _raise_for_flags(flags.tolist())
+        _raise_for_flags(flags.tolist(), ("G", "H"))
     else:
-        _PENDING.append(flags)
+        _PENDING.append((flags, ("G", "H")))
         if len(_PENDING) > _PENDING_LIMIT:  # a long unchecked run: settle the oldest call (it finished long ago)
-            _raise_for_flags(_PENDING.pop(0).tolist())
+            oldest, names = _PENDING.pop(0)
+            _raise_for_flags(oldest.tolist(), names)
     return outs[0], outs[1].t()
 
 
-_PENDING: list[torch.Tensor] = []  # status flags of the calls made with check=False, oldest first
+_PENDING: list[tuple[torch.Tensor, tuple[str, ...]]] = []  # status flags of the calls made with check=False, oldest first
 _PENDING_LIMIT = 256
 
 
-def _raise_for_flags(pivots) -> None:
-    for name, pivot in zip(("G", "H"), pivots):
+def _raise_for_flags(pivots, names) -> None:
+    for name, pivot in zip(names, pivots):
         if pivot < 0:
-            raise RuntimeError("feedback_factors_from_grams: a bounded wait inside a tensor-core kernel ran out; the result is not valid")
+            raise RuntimeError("factor preparation: a bounded wait inside a tensor-core kernel ran out; the result is not valid")
         if pivot:
-            raise torch.linalg.LinAlgError(f"feedback_factors_from_grams: {name} is not positive definite (pivot {pivot} is not positive)")
+            raise torch.linalg.LinAlgError(f"factor preparation: {name} is not positive definite (pivot {pivot} is not positive)")
 
 
 def last_flags() -> torch.Tensor | None:
-    """The device-side ``int32[2]`` status flags (G, H) of the most recent unchecked pair call, for callers that fold
-    them into statistics of their own instead of raising."""
-    return _PENDING[-1] if _PENDING else None
+    """The device-side ``int32`` status flags of the most recent unchecked factor preparation (G, H of a pair call),
+    for callers that fold them into statistics of their own instead of raising."""
+    return _PENDING[-1][0] if _PENDING else None
 
 
 def check_pending() -> None:
@@ -164,4 +216,5 @@ def check_pending() -> None:
     ``check=True`` would have raised (``torch.linalg.LinAlgError`` for a Gram that is not positive definite, as the
     reference's ``torch.linalg.cholesky`` does; ``RuntimeError`` for a bounded wait that ran out)."""
     while _PENDING:
-        _raise_for_flags(_PENDING.pop(0).tolist())
+        flags, names = _PENDING.pop(0)
+        _raise_for_flags(flags.tolist(), names)

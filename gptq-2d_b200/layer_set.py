@@ -27,29 +27,56 @@ MATRICES_70B = (
 )
 
 
-def layer_list(blocks: int = 80, divide: int = 1, matrices=MATRICES_70B) -> list[dict]:
-    """The matrices of the set; ``divide`` shrinks every dimension (for tests and short runs)."""
+# Matrices of a decoder block that read the same activations and therefore share their input-side Hessian factor.
+INPUT_GROUPS_70B = {"q": "attention input", "k": "attention input", "v": "attention input", "gate": "mlp input", "up": "mlp input"}
+
+
+def layer_list(blocks: int = 80, divide: int = 1, matrices=MATRICES_70B, shared_inputs: bool = False) -> list[dict]:
+    """The matrices of the set; ``divide`` shrinks every dimension (for tests and short runs).
+
+    With ``shared_inputs`` the matrices of ``INPUT_GROUPS_70B`` carry a ``group`` key and a common ``input_seed``: one
+    input-side factor (and one ``U``) serves the whole group, which then stays together on one rank."""
     items = []
     for block in range(blocks):
         for index, (name, m, n) in enumerate(matrices):
-            items.append({"block": block, "name": name, "m": m // divide, "n": n // divide, "seed": 7919 * block + 101 * index + 1})
+            item = {"block": block, "name": name, "m": m // divide, "n": n // divide, "seed": 7919 * block + 101 * index + 1}
+            if shared_inputs and name in INPUT_GROUPS_70B:
+                item["group"] = f"{block}:{INPUT_GROUPS_70B[name]}"
+                item["input_seed"] = 15485863 + 7919 * block + (1 if name in ("gate", "up") else 0)
+            items.append(item)
     return items
 
 
-def work(m: int, n: int) -> float:
-    """Algorithmic flops of one matrix: sweep ``m n (m + n - 2)`` plus both factor preparations ``2 k^3 / 3``."""
-    return float(m) * n * (m + n - 2) + 2.0 * (float(m) ** 3 + float(n) ** 3) / 3.0
+def work(m: int, n: int, input_factor_ready: bool = False) -> float:
+    """Algorithmic flops of one matrix: sweep ``m n (m + n - 2)`` plus its factor preparations ``2 k^3 / 3`` each (the
+    input-side one only where it is not shared with a matrix counted before)."""
+    prep = float(m) ** 3 + (0.0 if input_factor_ready else float(n) ** 3)
+    return float(m) * n * (m + n - 2) + 2.0 * prep / 3.0
+
+
+def _units(items: list[dict]) -> list[list[dict]]:
+    """The indivisible pieces of a set: single matrices, and the groups that share an input-side factor."""
+    units: dict = {}
+    for k, item in enumerate(items):
+        units.setdefault(item.get("group", ("single", k)), []).append(item)
+    return list(units.values())
+
+
+def _unit_work(unit: list[dict]) -> float:
+    return sum(work(item["m"], item["n"], input_factor_ready=k > 0) for k, item in enumerate(unit))
 
 
 def partition(items: list[dict], world: int) -> list[list[dict]]:
-    """Longest-processing-time-first assignment of the matrices to ``world`` ranks (deterministic)."""
+    """Longest-processing-time-first assignment of the matrices to ``world`` ranks (deterministic).  Matrices that share
+    an input-side factor are dealt out as one piece and stay next to each other in their rank's order."""
     shares: list[list[dict]] = [[] for _ in range(world)]
     load = [0.0] * world
-    order = sorted(range(len(items)), key=lambda k: (-work(items[k]["m"], items[k]["n"]), k))
+    units = _units(items)
+    order = sorted(range(len(units)), key=lambda k: (-_unit_work(units[k]), k))
     for k in order:
         rank = min(range(world), key=lambda r: (load[r], r))
-        shares[rank].append(items[k])
-        load[rank] += work(items[k]["m"], items[k]["n"])
+        shares[rank].extend(units[k])
+        load[rank] += _unit_work(units[k])
     return shares
 
 
@@ -72,6 +99,7 @@ class LayerPipeline:
         self.swept = [None, None]  # events: the sweeps of the last two layers have finished (the older bounds the run-ahead)
         self.slots = {}        # device buffers of quantize_from_host, two per shape
         self.count = 0
+        self.shared = None     # (group, H, U, event) of the input-side factor that the current group of matrices shares
 
     def _sweep(self, w, l, u):
         import torch
@@ -99,6 +127,29 @@ class LayerPipeline:
         l.record_stream(main)
         u.record_stream(main)
         return l, u
+
+    def _prepare_shared(self, g, group, input_factor, main):
+        """The same for a matrix whose input-side factor is shared with its group: ``U`` is prepared once, by the
+        group's first matrix (``input_factor()`` makes H, on the front stream), and kept for the others; only ``L``
+        is prepared per matrix."""
+        import torch
+
+        import kron_factors as K
+
+        with torch.cuda.stream(self.front):
+            if self.shared is None or self.shared[0] != group:
+                h = input_factor()
+                l, u = K.feedback_factors_from_grams(g, h)
+                self.shared = (group, h, u)
+            else:
+                _, h, u = self.shared
+                l = K.ldl_of_inverse(g, check=False)
+            ready = torch.cuda.Event()
+            ready.record(self.front)
+        main.wait_event(ready)
+        for t in (l, u, h):
+            t.record_stream(main)
+        return l, u, h
 
     def _after_sweep(self, main):
         import torch
@@ -191,8 +242,24 @@ def quantize_matrix(item: dict, device, pipeline: LayerPipeline | None = None):
     m, n = item["m"], item["n"]
     samples = min(8192, max(m, n))
     events = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
-    if pipeline is None:
-        w, g, h = synthetic.make_layer(m, n, seed=item["seed"], device=device, samples=samples)
+    if pipeline is not None and "group" in item:
+        # the input-side factor H and its U come from the group's first matrix on this rank
+        main = torch.cuda.current_stream(device)
+        pipeline._throttle()
+        with torch.cuda.stream(pipeline.front):
+            w, g, _ = synthetic.make_layer(m, n, seed=item["seed"], device=device, samples=samples, without_input_factor=True)
+            events[0].record(pipeline.front)
+        make_h = lambda: synthetic.shared_input_factor(n, item["input_seed"], device, samples=samples)
+        l, u, h = pipeline._prepare_shared(g, item["group"], make_h, main)
+        for t in (w, g):
+            t.record_stream(main)
+        events[1].record(main)
+        z = pipeline._sweep(w, l, u)
+        pipeline._after_sweep(main)
+        events[2].record(main)
+        scale = Q.int_abs_max_scale_triton(w, qmin=-8, qmax=7, dtype=torch.float16).expand(m, n)
+    elif pipeline is None:
+        w, g, h = synthetic.make_layer(m, n, seed=item["seed"], device=device, samples=samples, input_seed=item.get("input_seed"))
         events[0].record()
         l, u = K.feedback_factors_from_grams(g, h)
         events[1].record()
@@ -204,7 +271,7 @@ def quantize_matrix(item: dict, device, pipeline: LayerPipeline | None = None):
         main = torch.cuda.current_stream(device)
         pipeline._throttle()
         with torch.cuda.stream(pipeline.front):
-            w, g, h = synthetic.make_layer(m, n, seed=item["seed"], device=device, samples=samples)
+            w, g, h = synthetic.make_layer(m, n, seed=item["seed"], device=device, samples=samples, input_seed=item.get("input_seed"))
             events[0].record(pipeline.front)
         l, u = pipeline._prepare(g, h, main)
         for t in (w, g, h):
@@ -359,6 +426,8 @@ def main() -> None:
     parser.add_argument("--blocks", type=int, default=80)
     parser.add_argument("--divide", type=int, default=1, help="shrink every dimension by this factor")
     parser.add_argument("--serial", action="store_true", help="one layer at a time (per-part timings) instead of two in flight")
+    parser.add_argument("--shared-inputs", action="store_true",
+                        help="q, k, v of a block share one input-side Hessian factor, and so do gate and up (prepared once per group)")
     parser.add_argument("--journal", default=None, help="path prefix of the per-rank journals: finished matrices are written down and skipped on a rerun")
     args = parser.parse_args()
     sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
@@ -384,7 +453,7 @@ def main() -> None:
     # to the first (largest) matrix of every rank
     quantize_matrix({"block": -1, "name": "warm-up", "m": 384, "n": 512, "seed": 1}, device)
     pipeline = None if args.serial else LayerPipeline(device)
-    summary = run(layer_list(args.blocks, args.divide), functools.partial(quantize_matrix, device=device, pipeline=pipeline), rank=rank,
+    summary = run(layer_list(args.blocks, args.divide, shared_inputs=args.shared_inputs), functools.partial(quantize_matrix, device=device, pipeline=pipeline), rank=rank,
                   world=world, gather=gather, barrier=barrier, journal=args.journal)
     if summary is not None:
         print(json.dumps(summary))

@@ -33,8 +33,13 @@ def hessian_factor(dim: int, samples: int, sigma_h: float, damp: float, generato
 
 
 def make_layer(m: int, n: int, seed: int, device, *, sigma_w: float = 0.02, sigma_h: float = 1.0, damp: float = 0.01,
-               samples: int = 8192, outliers: float = 0.0, dtype=torch.float32):
-    """Return ``(W [m, n], G [m, m], H [n, n])`` for one seeded synthetic layer."""
+               samples: int = 8192, outliers: float = 0.0, dtype=torch.float32, input_seed: int | None = None,
+               without_input_factor: bool = False):
+    """Return ``(W [m, n], G [m, m], H [n, n])`` for one seeded synthetic layer.
+
+    Matrices that read the same activations (the q, k, v projections of a block; gate and up) share their input-side
+    factor: give them the same ``input_seed``, which then seeds H alone (``shared_input_factor`` makes just that
+    matrix); ``without_input_factor`` returns None in its place."""
     generator = torch.Generator(device=device).manual_seed(seed)
     w = sigma_w * torch.randn(m, n, generator=generator, device=device, dtype=dtype)
     if outliers > 0:
@@ -42,8 +47,19 @@ def make_layer(m: int, n: int, seed: int, device, *, sigma_w: float = 0.02, sigm
         signs = torch.where(torch.rand(m, n, generator=generator, device=device) < 0.5, -1.0, 1.0).to(dtype)
         w = torch.where(mask, 10 * sigma_w * signs, w)
     g = hessian_factor(m, samples, sigma_h, damp, generator, device, dtype)
+    if without_input_factor:
+        return w, g, None
+    if input_seed is not None:
+        return w, g, shared_input_factor(n, input_seed, device, sigma_h=sigma_h, damp=damp, samples=samples, dtype=dtype)
     h = hessian_factor(n, samples, sigma_h, damp, generator, device, dtype)
     return w, g, h
+
+
+def shared_input_factor(n: int, input_seed: int, device, *, sigma_h: float = 1.0, damp: float = 0.01, samples: int = 8192,
+                        dtype=torch.float32) -> torch.Tensor:
+    """The input-side factor ``H [n, n]`` that every matrix with this ``input_seed`` uses."""
+    generator = torch.Generator(device=device).manual_seed(input_seed)
+    return hessian_factor(n, samples, sigma_h, damp, generator, device, dtype)
 
 
 def objective(z: torch.Tensor, x: torch.Tensor, g: torch.Tensor, h: torch.Tensor) -> float:

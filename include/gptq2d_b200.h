@@ -41,6 +41,8 @@ typedef enum g2d_half { G2D_FP16 = 0, G2D_BF16 = 1 } g2d_half;
 typedef enum g2d_quant_kind {
     G2D_Q_ROUND = 0,   /* quantizer_int.py:18-35  round half to even */
     G2D_Q_AFFINE = 1,  /* quantizer_int.py:63-107 (clamp(rint(y/scale + zp), qmin, qmax) - zp) * scale */
+    G2D_Q_ABSMAX_DYNAMIC = 2, /* quantizer_int.py:120-134 every row of a super-entry rounded under its own abs-max scale (g2d_sweep_super_entry) */
+    G2D_Q_TRELLIS = 3, /* quantizer_trellis.py:344-391 every super-entry a bitshift-trellis sequence (g2d_sweep_super_entry) */
     G2D_Q_FORCED = 4   /* commit the given values (teacher-forced replay for parity checks) */
 } g2d_quant_kind;
 
@@ -105,6 +107,47 @@ int g2d_sweep_fused(const g2d_sweep_desc *desc, void *stream);
  *    order and may differ at rounding ties). */
 #define G2D_STATIC_SCRATCH_BYTES (32u * 1024u * 1024u)
 int g2d_sweep_fused_static(const g2d_sweep_desc *desc, void *stream);
+
+/* A sweep over p x q super-entries, or an N-factor sweep, with the quantizer inside the library: the whole loop over the
+ * coarse anti-diagonals runs inside the call (quantizer kernel, commit and in-block pushes, block-end updates), where the
+ * reference's Python driver makes several launches per stage from the host.
+ * Replaces gptq_2d_super_entry (gptq_2d.py:1422-1447) = _gptq_2d_blocked (:1295-1375) with _push_down_super_entry_kernel
+ * (:428-505), _push_right_super_entry_kernel (:536-601) and _flush_block (:1090-1119), for the quantizers
+ * round_quantizer_super_entry (quantizer_int.py:28), affine_quantizer_super_entry_* (:86, :302), int_abs_max_quantizer_*
+ * (:120, :442) and trellis_quantizer_super_entry_* (quantizer_trellis.py:344, :372); and, with lead_count > 0,
+ * alg4 (gptq_2d_reference.py:269-294): the tensor [lead_size[0], .., lead_size[lead_count-1], m, n] with one unit lower
+ * triangular factor per leading mode (lead_factor[k], row-major [size, size], read strictly below the diagonal), l for
+ * mode m and u (upper, = the last mode's factor transposed) for mode n.  The leading factors are applied mode by mode;
+ * no Kronecker product is formed.  y is then [batch = product of lead_size, m, n] and the super-entry is (1, .., 1, p, q). */
+typedef struct g2d_super_desc {
+    int32_t dtype;               /* g2d_dtype */
+    int32_t quant_kind;          /* ROUND, AFFINE, ABSMAX_DYNAMIC or TRELLIS */
+    int32_t p, q;                /* super-entry shape; must divide m and n */
+    int32_t inner_block, outer_block; /* coarse stages per inner / outer block, clamped as gptq_2d.py:1327-1329 does (<= 0: one block) */
+    int64_t batch, m, n;
+    void *y;                     /* [batch, m, n]: X on entry, Z on return */
+    const void *l;               /* [.., m, m]: read only below the p x p diagonal blocks */
+    const int64_t *l_offsets;    /* per-batch element offsets as in g2d_sweep_desc; NULL = 0 */
+    const void *u;               /* [.., n, n]: read only above the q x q diagonal blocks */
+    const int64_t *u_offsets;
+    int32_t lead_count;          /* 0 for a two-sided sweep; else the number of leading modes (<= 4) */
+    int32_t half;                /* ABSMAX_DYNAMIC: g2d_half of the scale */
+    int64_t lead_size[4];
+    const void *lead_factor[4];
+    const void *scale;           /* AFFINE: [.., m, n] through the strides below; TRELLIS: one value per batch (scale_offsets) */
+    const int64_t *scale_offsets;
+    const void *zero;            /* AFFINE */
+    const int64_t *zero_offsets;
+    int64_t scale_row_stride, scale_col_stride, zero_row_stride, zero_col_stride;
+    double qmin, qmax;           /* AFFINE, ABSMAX_DYNAMIC */
+    const void *table;           /* TRELLIS: [2^L, V] in dtype; a super-entry read row by row is one sequence of p q values */
+    int32_t trellis_L, trellis_K, trellis_V, tail_biting;
+    uint8_t *codes;              /* TRELLIS, optional: packed paths, [batch, m / p, n / q, g2d_trellis_code_bytes] */
+    void *workspace;             /* g2d_super_workspace_bytes() bytes, 256-byte aligned */
+    size_t workspace_bytes;
+} g2d_super_desc;
+int g2d_super_workspace_bytes(const g2d_super_desc *desc, size_t *bytes);
+int g2d_sweep_super_entry(const g2d_super_desc *desc, void *stream);
 
 /* Profiling variant of g2d_sweep_fused (no counterpart in the reference): the same launches, each
  * bracketed by a CUDA event pair on `stream`; synchronizes the stream before returning, so it cannot be
@@ -179,6 +222,19 @@ int g2d_trellis_workspace_bytes(int dtype, int64_t rows, int32_t T, int32_t L, i
 int g2d_trellis_quantize(int dtype, int64_t rows, int32_t T, const void *x, const void *table, int32_t L, int32_t K,
                          int32_t V, int32_t tail_biting, const void *scale, void *out, int64_t *states,
                          void *workspace, size_t workspace_bytes, void *stream);
+
+/* The same search that also stores every path as its bit string, the storage format of a trellis code (the reference
+ * only notes that "the T K-bit code can be recovered" from the values, quantizer_trellis.py:11-14).  The string holds the
+ * K V bits that each step shifts into the state, most significant bit first, preceded, unless the path is tail-biting,
+ * by the L - K V upper bits of the first state; bit i of the string is bit i % 8 of byte i / 8, and a sequence takes
+ * g2d_trellis_code_bytes bytes (T K / 8 when tail-biting).  g2d_trellis_decode turns strings back into scale * values
+ * (and the int64 states, optional), bit for bit what the search returned. */
+int g2d_trellis_code_bytes(int32_t T, int32_t L, int32_t K, int32_t V, int32_t tail_biting, int64_t *bytes);
+int g2d_trellis_quantize_packed(int dtype, int64_t rows, int32_t T, const void *x, const void *table, int32_t L, int32_t K,
+                                int32_t V, int32_t tail_biting, const void *scale, void *out, uint8_t *codes,
+                                void *workspace, size_t workspace_bytes, void *stream);
+int g2d_trellis_decode(int dtype, int64_t rows, int32_t T, const uint8_t *codes, const void *table, int32_t L, int32_t K,
+                       int32_t V, int32_t tail_biting, const void *scale, void *out, int64_t *states, void *stream);
 
 /* Unit (block) lower triangular factor of the inverse of a symmetric positive definite matrix:
  * a^{-1} = out Lambda out^T with size x size identity diagonal blocks.  a is [n, n] and is overwritten

@@ -82,6 +82,9 @@ def test_config3_trellis_three_factors(oracle):
     expected = oracle.sweep(x.reshape(n1 * n2, n3), row_factor.cpu().numpy(), l3.T.cpu().numpy(), kind=oracle.Q_TRELLIS,
                             super_entry_shape=(16, 16), scale=1.1, table=table.cpu().numpy(), K=2)
     assert torch.equal(z.cpu(), torch.from_numpy(expected))
+    # the same problem mode by mode: three factors of 3^2, 32^2 and 48^2 values, no Kronecker product
+    z3 = K.gptq_d_sided(cuda(x), [l1, l2, l3], quantizer=quantizer, quantizer_inputs=(scale,), super_entry_shape=(16, 16))
+    assert torch.equal(z3.cpu(), torch.from_numpy(expected).reshape(n1, n2, n3))
 
 
 def test_layer_pipeline_equals_plain_calls():
@@ -112,3 +115,32 @@ def test_layer_pipeline_equals_plain_calls():
     for event, out, want in zip(done, outs, expected):
         event.synchronize()
         assert torch.equal(out, want.cpu())
+
+
+def test_shared_input_factors_equal_separate_calls():
+    """A group of matrices that shares its input-side factor (q, k, v of a block) gets U once; every member's result is
+    what the plain per-matrix calls give with the same Hessian factors."""
+    import functools
+
+    import gptq_2d as G
+    import kron_factors as K
+    import layer_set
+    import quantizer_int as Q
+    import synthetic
+
+    device = torch.device("cuda", 0)
+    items = [i for i in layer_set.layer_list(1, divide=16, shared_inputs=True) if i["name"] in ("q", "k", "v")]
+    assert len({i["group"] for i in items}) == 1
+    pipeline = layer_set.LayerPipeline(device)
+    fetch = [layer_set.quantize_matrix(item, device, pipeline) for item in items]
+    stats = [f() for f in fetch]
+    pipeline.check()
+    assert all(s["finite"] and s["codes_in_range"] and s["factors_ok"] for s in stats)
+    for item, got in zip(items, stats):
+        m, n = item["m"], item["n"]
+        w, g, h = synthetic.make_layer(m, n, seed=item["seed"], device=device, samples=min(8192, max(m, n)), input_seed=item["input_seed"])
+        l, u = K.feedback_factors_from_grams(g, h, check=True)
+        scale = Q.int_abs_max_scale_triton(w, qmin=-8, qmax=7, dtype=torch.float16).expand(m, n)
+        zero = torch.zeros(1, 1, device=device).expand(m, n)
+        z = G.gptq_2d(w, l, u, quantizer=functools.partial(Q.affine_quantizer_triton, qmin=-8, qmax=7), quantizer_inputs=(scale, zero))
+        assert got["code_sum"] == torch.round(z / scale).double().sum().item()

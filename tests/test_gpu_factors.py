@@ -113,6 +113,62 @@ def test_d_sided_golden(K):
         assert torch.equal(z.cpu(), torch.from_numpy(g[f"z{k}"])), k
 
 
+def _unit_lower(rng, n, scale=0.3):
+    return np.tril(rng.standard_normal((n, n)) * (scale / np.sqrt(n)), -1) + np.eye(n)
+
+
+@pytest.mark.parametrize("shape", [(3, 5, 7), (4, 8, 16), (2, 3, 4, 6), (5, 1, 9), (2, 2, 2, 3, 4)])
+def test_d_sided_mode_by_mode_equals_reference_algorithm(K, oracle, shape):
+    """The mode-by-mode engine (leading modes applied as scaled additions of finished slabs' residuals, all slabs on the
+    hyper-anti-diagonal schedule) against the restated alg4 and against the explicit Kronecker row factor, bit for bit."""
+    rng = np.random.default_rng(sum(shape))
+    x = 4 * rng.standard_normal(shape)
+    factors = [_unit_lower(rng, k) for k in shape]
+    want = oracle.alg4(x, factors)
+    got = K.gptq_d_sided(cuda(x), [cuda(f) for f in factors])
+    assert torch.equal(got.cpu(), torch.from_numpy(want))
+    dense = K.gptq_d_sided(cuda(x), [cuda(f) for f in factors], dense_row_factor=True)
+    assert torch.equal(dense, got)
+    assert torch.equal(K.alg4(cuda(x), [cuda(f) for f in factors]), got)
+    # the reference's positional form with a quantizer of its protocol: values and one index tensor per mode
+    grid = lambda values, *indices: torch.round(values * 2 + indices[0]) / 2
+    want = oracle.alg4(x, factors, quantize=lambda values, *indices: np.rint(values * 2 + indices[0]) / 2)
+    assert torch.equal(K.alg4(cuda(x), [cuda(f) for f in factors], grid).cpu(), torch.from_numpy(want))
+
+
+def test_d_sided_affine_and_blocks(K, oracle):
+    """An affine grid per entry through the mode-by-mode engine, under several block sizes of the stage loop."""
+    import functools
+
+    import quantizer_int as Q
+
+    rng = np.random.default_rng(17)
+    shape = (4, 6, 10)
+    x = rng.standard_normal(shape)
+    factors = [_unit_lower(rng, k) for k in shape]
+    scale, zero = 0.05 + 0.1 * rng.random(shape), np.rint(rng.standard_normal(shape))
+    affine = lambda values, *idx: (np.clip(np.rint(values / scale[idx] + zero[idx]), -8, 7) - zero[idx]) * scale[idx]
+    want = oracle.alg4(x, factors, quantize=affine)
+    quantizer = functools.partial(Q.affine_quantizer_super_entry_triton, qmin=-8, qmax=7)
+    for inner, outer in ((0, 0), (1, 0), (2, 7), (3, 11)):
+        got = K.gptq_d_sided(cuda(x), [cuda(f) for f in factors], quantizer=quantizer, quantizer_inputs=(cuda(scale), cuda(zero)),
+                             inner_block_size=inner, outer_block_size=outer)
+        assert torch.equal(got.cpu(), torch.from_numpy(want)), (inner, outer)
+
+
+def test_d_sided_large_float32_agrees_with_kronecker_route(K):
+    """16 x 256 x 1024 in float32: the mode-by-mode engine keeps factors of 16^2 + 256^2 + 1024^2 values where the
+    Kronecker route forms a 4096^2 row factor; with well-conditioned factors both give the same codes."""
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    shape = (16, 256, 1024)
+    x = 4 * torch.randn(shape, generator=gen, device="cuda")
+    factors = [torch.tril(torch.randn(k, k, generator=gen, device="cuda") * (0.3 / k ** .5), -1) + torch.eye(k, device="cuda") for k in shape]
+    got = K.gptq_d_sided(x, factors)
+    dense = K.gptq_d_sided(x, factors, dense_row_factor=True)
+    assert (got == dense).double().mean().item() >= 0.9999
+    assert (got - x).abs().max().item() < 4.0
+
+
 @pytest.mark.parametrize("k, n", [(1000, 512), (37, 132), (4096, 1100), (64, 4)])
 def test_gram_accumulation(K, k, n):
     """h += alpha x^T x on the tensor cores stays at float32 fidelity (3xTF32) and is symmetric bit for bit."""

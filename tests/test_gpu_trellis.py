@@ -122,3 +122,63 @@ def test_trellis_inside_the_sweep(T):
     assert torch.equal(replay(x, l, u, scale).cpu(), expected)
     again = replay(x + .375, 1.5 * l, .5 * u, 2 * scale)
     assert torch.equal(again, G.gptq_2d_super_entry(x + .375, 1.5 * l, .5 * u, quantizer_inputs=(2 * scale,), **options))
+
+
+def test_stored_paths_match_the_oracle_and_decode_back(T, oracle):
+    """The search's packed output: the bytes are the oracle's packing of the golden states, and decoding them gives back
+    the values and the states bit for bit (fp32 and fp64, tail-biting strings and strings with a header, scaled)."""
+    import packed_codes as P
+
+    g = load_golden("trellis.npz")
+    checked = 0
+    for k in range(int(g["count"])):
+        x, table, K = cuda(g[f"x{k}"]), cuda(g[f"table{k}"]), int(g[f"K{k}"])
+        L, V = table.size(0).bit_length() - 1, table.size(1)
+        for tb in (0, 1):
+            states = g[f"states{k}_{tb}"]
+            if tb and states.shape[-1] * K * V < L:
+                continue
+            scale = torch.linspace(0.5, 2.0, x.shape[:-1].numel(), device="cuda", dtype=x.dtype).reshape(x.shape[:-1])
+            values, codes = P.trellis_quantize_packed(x, table, K, bool(tb), scale=scale)
+            assert torch.equal(values, cuda(g[f"values{k}_{tb}"]) * scale[..., None])
+            assert np.array_equal(codes.cpu().numpy(), oracle.trellis_pack(states, L, K, V, bool(tb))), (k, tb)
+            back, back_states = P.trellis_decode(codes, table, K, x.size(-1), bool(tb), scale=scale, dtype=x.dtype, return_states=True)
+            assert torch.equal(back, values) and torch.equal(back_states.cpu(), torch.from_numpy(states))
+            checked += 1
+    assert checked >= 6
+    # the benchmark's code: HYB, L = 16, 2 bits per weight, 256-weight tail-biting sequences -> 64 bytes each
+    table = T.hyb(device="cuda")
+    x = torch.randn(40, 256, device="cuda", generator=torch.Generator(device="cuda").manual_seed(3))
+    values, codes = P.trellis_quantize_packed(x, table, 2)
+    assert codes.shape == (40, 64)
+    want, states = T._trellis_quantize(x, table, 2, True)
+    assert torch.equal(values, want)
+    assert torch.equal(P.trellis_decode(codes, table, 2, 256), values)
+    assert np.array_equal(codes.cpu().numpy(), oracle.trellis_pack(states.cpu().numpy(), 16, 2, 2, True))
+
+
+def test_sweep_stores_its_trellis_paths(T):
+    """A trellis sweep that also returns the stored paths: the result is the plain sweep's, and every super-entry of Z is
+    recovered from its 8 bytes (16 x 4 super-entries of 2-bit weights)."""
+    import gptq_2d as G
+    import packed_codes as P
+
+    g = load_golden("trellis_sweep_fp64.npz")
+    x, l, u, table = cuda(g["x"]), cuda(g["l"]), cuda(g["u"]), cuda(g["table"])
+    scale = cuda(g["scale"])
+    z, codes = P.gptq_2d_trellis_packed(x, l, u, scale, table=table, K=int(g["K"]), super_entry_shape=(16, 16))
+    assert torch.equal(z.cpu(), torch.from_numpy(g["z"]))
+    m, n = x.shape
+    blocks = z.reshape(m // 16, 16, n // 16, 16).permute(0, 2, 1, 3).reshape(m // 16, n // 16, 256)
+    assert torch.equal(P.trellis_decode(codes, table, int(g["K"]), 256, scale=scale, dtype=x.dtype), blocks)
+    # a batch with one scale per matrix
+    xb = torch.stack([x, 0.5 * x])
+    scales = torch.tensor([1.1, 0.7], dtype=x.dtype, device="cuda").reshape(2, 1, 1, 1)
+    zb, cb = P.gptq_2d_trellis_packed(xb, l, u, scales, table=table, K=int(g["K"]), super_entry_shape=(16, 16))
+    quantizer = functools.partial(T.trellis_quantizer_super_entry_triton, table=table, K=int(g["K"]))
+    for b in range(2):
+        want = G.gptq_2d_super_entry(xb[b], l, u, quantizer=lambda *a, **k: quantizer(*a, **k), super_entry_shape=(16, 16), quantizer_inputs=(scales[b, 0, 0, 0],))
+        assert torch.equal(zb[b], want)
+    blocks = zb.reshape(2, m // 16, 16, n // 16, 16).permute(0, 1, 3, 2, 4).reshape(2, m // 16, n // 16, 256)
+    per_entry = scales.reshape(2, 1, 1).expand(2, m // 16, n // 16)
+    assert torch.equal(P.trellis_decode(cb, table, int(g["K"]), 256, scale=per_entry, dtype=x.dtype), blocks)

@@ -30,6 +30,7 @@ def test_descriptor_layout_matches_header():
     # field order and C alignment rules give these sizes for the header's structs on LP64
     assert ctypes.sizeof(_abi.SweepDesc) == 8 + 3 * 8 + 9 * 8 + 4 * 8 + 2 * 8 + 2 * 8 + 2 * 8 + 8 + 8
     assert ctypes.sizeof(_abi.StageDesc) == 16 + 3 * 8 + 7 * 8
+    assert ctypes.sizeof(_abi.SuperDesc) == 6 * 4 + 3 * 8 + 5 * 8 + 2 * 4 + 4 * 8 + 4 * 8 + 4 * 8 + 4 * 8 + 2 * 8 + 8 + 4 * 4 + 8 + 2 * 8
 
 
 def test_cpu_tensors_are_rejected_not_emulated():
@@ -82,12 +83,27 @@ def test_fused_dispatch_recognition():
     import gptq_2d as G
     import quantizer_int as Q
 
+    import quantizer_trellis as T
+
     t = torch.zeros(2, 2)
-    assert G._fusable(Q.round_quantizer, (), None) == {"kind": 0}
-    assert G._fusable(functools.partial(Q.affine_quantizer_triton, qmin=-8, qmax=7), (t, t), None) == {"kind": 1, "qmin": -8, "qmax": 7}
+    # plain entries under the round and affine quantizers: the fused tile engine
+    assert G._fusable(Q.round_quantizer, (), None) == {"kind": 0, "super": False}
+    assert G._fusable(functools.partial(Q.affine_quantizer_triton, qmin=-8, qmax=7), (t, t), None) == {"kind": 1, "qmin": -8, "qmax": 7, "super": False}
     assert G._fusable(functools.partial(functools.partial(Q.affine_quantizer_torch, qmin=-8), qmax=7), (t, t), None)["qmax"] == 7
-    assert G._fusable(Q.affine_quantizer_super_entry_triton, (t, t), (1, 1))["kind"] == 1
-    assert G._fusable(Q.affine_quantizer_super_entry_triton, (t, t), (2, 2)) is None
+    assert G._fusable(Q.affine_quantizer_super_entry_triton, (t, t), (1, 1)) == {"kind": 1, "qmin": -torch.inf, "qmax": torch.inf, "super": False}
+    # larger super-entries and the joint quantizers: the library's super-entry sweep
+    assert G._fusable(Q.affine_quantizer_super_entry_triton, (t, t), (2, 2))["super"] is True
+    assert G._fusable(Q.round_quantizer_super_entry, (), (2, 4)) == {"kind": 0, "super": True}
+    absmax = functools.partial(Q.int_abs_max_quantizer_triton, qmin=-8, qmax=7, dtype=torch.bfloat16)
+    assert G._fusable(absmax, (), (1, 32)) == {"kind": 2, "qmin": -8, "qmax": 7, "half": 1, "super": True}
+    assert G._fusable(absmax, (), None) is None
+    assert G._fusable(functools.partial(Q.int_abs_max_quantizer_triton, qmin=-8, qmax=7, dtype=torch.float32), (), (1, 32)) is None
+    table = torch.zeros(256, 2)
+    trellis = G._fusable(functools.partial(T.trellis_quantizer_super_entry_triton, table=table, K=2), (t,), (16, 16))
+    assert trellis["kind"] == 3 and trellis["K"] == 2 and trellis["tail_biting"] is True and trellis["super"] is True
+    assert G._fusable(functools.partial(T.trellis_quantizer_super_entry_triton, table=table, K=2), (t,), (3, 5)) is None  # T % V
+    assert G._fusable(functools.partial(T.trellis_quantizer_super_entry_triton, table=torch.zeros(256, 3), K=2), (t,), (3, 4)) is None
+    # anything else: the per-stage engine calls it
     assert G._fusable(Q.affine_quantizer_triton, (t,), None) is None
     assert G._fusable(lambda *a, **k: None, (), None) is None
     assert G._fusable(functools.partial(Q.affine_quantizer_triton, t), (t, t), None) is None

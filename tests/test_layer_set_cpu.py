@@ -21,6 +21,32 @@ def test_layer_list_and_partition():
     assert layer_set.partition(items[:3], 8)[3:] == [[]] * 5
 
 
+def test_shared_input_factors_stay_together():
+    """q, k, v of a block share one input-side factor and gate, up another: a group is dealt out as one piece, its
+    matrices follow each other on their rank, and its cost counts the shared factor once."""
+    import layer_set
+
+    items = layer_set.layer_list(6, shared_inputs=True)
+    groups = {}
+    for item in items:
+        if "group" in item:
+            groups.setdefault(item["group"], []).append(item)
+    assert len(groups) == 12 and sorted(len(g) for g in groups.values()) == [2] * 6 + [3] * 6
+    for members in groups.values():
+        assert len({i["input_seed"] for i in members}) == 1 and len({i["n"] for i in members}) == 1
+    assert all("group" not in i for i in items if i["name"] in ("o", "down"))
+    assert abs(layer_set.work(1024, 8192, input_factor_ready=True) - (layer_set.work(1024, 8192) - 2 * 8192.0 ** 3 / 3)) < 1e3
+    for world in (1, 2, 4):
+        shares = layer_set.partition(items, world)
+        assert sorted((i["block"], i["name"]) for s in shares for i in s) == sorted((i["block"], i["name"]) for i in items)
+        for share in shares:
+            names = [i.get("group") for i in share]
+            for group in set(names) - {None}:
+                where = [k for k, name in enumerate(names) if name == group]
+                assert where == list(range(where[0], where[0] + len(groups[group])))  # whole and contiguous
+    assert "group" not in layer_set.layer_list(1)[0]
+
+
 def _rank(rank, world, store_path, out_path):
     import sys
 

@@ -171,3 +171,26 @@ def test_packed_codes_known_answers(oracle):
     rng = np.random.default_rng(0)
     z = (rng.integers(0, 32, (7, 21)) * 0.125).astype(np.float32)
     assert np.array_equal(oracle.unpack_codes(oracle.pack_codes(z, 0.125, 0.0, 0, 5), 0.125, 0.0, 0, 5, 21), z)
+
+
+def test_trellis_paths_known_answers(oracle):
+    """The stored form of a trellis path is this library's own format: pinned by a hand-computed byte and by the round
+    trip through the states of the golden searches (tail-biting strings are read circularly, others carry a header)."""
+    # L = 4, one bit per step, not tail-biting: header 101 (upper bits of 1011), then the low bit of 1011, 0110, 1101
+    assert oracle.trellis_pack(np.array([[0b1011, 0b0110, 0b1101]]), 4, 1, 1, False).tolist() == [[0b101101]]
+    assert oracle.trellis_unpack(np.array([[0b101101]], dtype=np.uint8), 3, 4, 1, 1, False).tolist() == [[0b1011, 0b0110, 0b1101]]
+    g = load_golden("trellis.npz")
+    checked = 0
+    for k in range(int(g["count"])):
+        table, K = g[f"table{k}"], int(g[f"K{k}"])
+        L, V = table.shape[0].bit_length() - 1, table.shape[1]
+        for tail in (0, 1):
+            states = g[f"states{k}_{tail}"]
+            steps = states.shape[-1]
+            if tail and steps * K * V < L:
+                continue  # a tail-biting string shorter than one state does not determine it
+            codes = oracle.trellis_pack(states, L, K, V, bool(tail))
+            assert codes.shape[-1] == ((0 if tail else L - K * V) + steps * K * V + 7) // 8
+            assert np.array_equal(oracle.trellis_unpack(codes, steps, L, K, V, bool(tail)), states)
+            checked += 1
+    assert checked >= 6
