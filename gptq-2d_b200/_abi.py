@@ -101,6 +101,7 @@ _SIGNATURES = {
     "g2d_gram_accumulate": (ctypes.c_int, [_i64, _i64, _vp, ctypes.c_float, _vp, _vp, _vp, ctypes.c_size_t, _vp]),
     "g2d_pack_codes": (ctypes.c_int, [ctypes.c_int, _i64, _i64, _vp, _vp, _i64, _i64, _vp, _i64, _i64, ctypes.c_double, _i32, _vp, _i64, _vp]),
     "g2d_unpack_codes": (ctypes.c_int, [ctypes.c_int, _i64, _i64, _vp, _i64, _vp, _i64, _i64, _vp, _i64, _i64, ctypes.c_double, _i32, _vp, _vp]),
+    "g2d_symmetric_from_packed": (ctypes.c_int, [ctypes.c_int, _i64, _vp, _vp, _vp]),
     "g2d_ldl_of_inverse_pair": (ctypes.c_int, [ctypes.c_int, _i64, _vp, _i32, _vp, _vp, ctypes.c_size_t,
                                                _i64, _vp, _i32, _vp, _vp, ctypes.c_size_t, _vp, _vp]),
 }

@@ -134,6 +134,19 @@ __device__ __forceinline__ void split_tf32(float a, float &hi, float &lo) {
     lo = a - hi;
 }
 
+// fp32 -> three tf32 values with a = hi + mid + lo exactly (11 + 11 + the last 2 significant bits).  The six products
+// hi hi' + hi mid' + mid hi' + mid mid' + hi lo' + lo hi' then carry the fp32 product to about 2^-32: used where the
+// 2^-21 of the two-plane split is not enough (the triangular inverse, whose error the condition number amplifies).
+__device__ __forceinline__ void split_tf32_3(float a, float &hi, float &mid, float &lo) {
+    uint32_t h, m;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(a));
+    hi = __uint_as_float(h);
+    const float r = a - hi;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(m) : "f"(r));
+    mid = __uint_as_float(m);
+    lo = r - mid;
+}
+
 // Operand planes of the tensor-core macro updates (all float; see g2d_macro_update_tc.cu).
 struct TcPlanes {
     float *et_hi, *et_lo, *c_hi, *c_lo;  // written by the tile sweep
@@ -162,9 +175,10 @@ int launch_macro_update_tc(const MacroTcMaps *maps, const TcPlanes &planes, floa
 struct FactorPlanes {
     const float *a;            // Cholesky factor T in its lower triangle
     float *out;                // the inverse being built
-    float *out_hi, *out_lo;    // its tf32 split, and the split of its transpose
-    float *outt_hi, *outt_lo;
-    float *tw_hi, *tw_lo;      // lower triangle: split of T; upper triangle: split of the transposed intermediate product
+    // every operand as three tf32 planes hi + mid + lo = the float32 value exactly (see split_tf32_3):
+    float *out_hi, *out_mid, *out_lo;      // the inverse
+    float *outt_hi, *outt_mid, *outt_lo;   // its transpose
+    float *tw_hi, *tw_mid, *tw_lo;         // lower triangle: T; upper triangle: the transposed intermediate product
     int64_t n;
     int *flag;                 // receives -1 when a bounded wait inside a kernel ran out (may be null)
 };

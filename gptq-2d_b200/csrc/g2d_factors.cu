@@ -452,7 +452,7 @@ int ldl_run(int count, const int64_t *ns, F *const *as, const int *sizes, F *con
         // float problems whose rows are 16-byte multiples use the tensor cores; the choice depends on the problem alone,
         // never on its partner in the batch, so that a pair gives the results of two single calls
         if (std::is_same<F, float>::value && n % 4 == 0) {
-            float *base = (float *)P.w + 7 * n * n;  // behind the scratch and the six planes of the triangular inverse
+            float *base = (float *)P.w + 10 * n * n;  // behind the scratch and the nine planes of the triangular inverse
             for (int k = 0; k < 2; ++k) {
                 P.pt_hi[k] = base + (2 * k) * n * (GROUP * FB);
                 P.pt_lo[k] = base + (2 * k + 1) * n * (GROUP * FB);
@@ -570,9 +570,10 @@ int ldl_run(int count, const int64_t *ns, F *const *as, const int *sizes, F *con
     for (int z = 0; z < count; ++z) {
         const int64_t n = ns[z];
         if (std::is_same<F, float>::value && n % 4 == 0) {
-            float *base = (float *)B.p[z].w + n * n;  // six [n][n] planes behind the scratch of the 64-level
+            float *base = (float *)B.p[z].w + n * n;  // nine [n][n] planes behind the scratch of the 64-level
             planes[tensor_count++] = FactorPlanes{(const float *)as[z], (float *)outs[z], base, base + n * n, base + 2 * n * n,
-                                                  base + 3 * n * n, base + 4 * n * n, base + 5 * n * n, n, flags ? flags + z : nullptr};
+                                                  base + 3 * n * n, base + 4 * n * n, base + 5 * n * n, base + 6 * n * n, base + 7 * n * n,
+                                                  base + 8 * n * n, n, flags ? flags + z : nullptr};
         } else {
             rest.p[rest_count++] = B.p[z];
             rest_max = n > rest_max ? n : rest_max;
@@ -608,8 +609,8 @@ using namespace g2d;
 static size_t ldl_bytes(int dtype, int64_t n) {
     const size_t elem = dtype == G2D_F32 ? 4 : 8;
     const size_t nb = (size_t)ceil_div(n, FB);
-    // float: six operand planes of the tensor-core triangular inverse and two pairs of transposed split panels
-    const size_t planes = dtype == G2D_F32 ? 6 * (size_t)n * n + 4 * (size_t)n * GROUP * FB : 0;
+    // float: nine operand planes of the tensor-core triangular inverse and two pairs of transposed split panels
+    const size_t planes = dtype == G2D_F32 ? 9 * (size_t)n * n + 4 * (size_t)n * GROUP * FB : 0;
     return ((nb * FB * FB + (size_t)n * FB + (size_t)n * n + planes) * elem + 255) & ~(size_t)255;
 }
 

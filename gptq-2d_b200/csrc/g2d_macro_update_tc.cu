@@ -30,7 +30,7 @@ __global__ void __launch_bounds__(TC_THREADS) macro_update_tc_kernel(const __gri
                                                                      int64_t n, int nI2, int nJ2, int s0, int s1, int t_first, int s_end,
                                                                      int raster, int *error_flag) {
     extern __shared__ unsigned char tc_smem_raw[];
-    __shared__ __align__(8) uint64_t full_bar[NSTAGES], empty_bar[NSTAGES], accum_bar;
+    __shared__ __align__(8) uint64_t full_bar[NSTAGES], empty_bar[NSTAGES], accum_bar[2];  // one accumulator barrier per product
     __shared__ uint32_t tmem_slot;
     __shared__ int failed;
     // Target macro tile.  With gridDim.y > 1, blockIdx.y selects the macro anti-diagonal and blockIdx.x the tile on it
@@ -65,7 +65,8 @@ __global__ void __launch_bounds__(TC_THREADS) macro_update_tc_kernel(const __gri
             mbar_init(&full_bar[s], 1);
             mbar_init(&empty_bar[s], 1);
         }
-        mbar_init(&accum_bar, 1);
+        mbar_init(&accum_bar[0], 1);
+        mbar_init(&accum_bar[1], 1);
         failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -114,20 +115,25 @@ __global__ void __launch_bounds__(TC_THREADS) macro_update_tc_kernel(const __gri
                     umma_tf32(d_addr, umma_desc(a_hi + off), umma_desc(b_lo + off), IDESC, 1u);
                 }
                 umma_commit(&empty_bar[stage]);  // arrives when the MMAs above have read the stage
+                // the down product is complete with its last chunk: its accumulator is read out and added to C by the
+                // epilogue warps while the MMAs of the right product run into the other accumulator
+                if (ch == chunks_d - 1) umma_commit(&accum_bar[0]);
             }
-            umma_commit(&accum_bar);             // arrives when every MMA issued so far has completed
+            if (ok && chunks_r > 0) umma_commit(&accum_bar[1]);  // arrives when every MMA issued so far has completed
         }
     } else {
         // epilogue warps: lanes 32 q .. 32 q + 31 of tensor memory, q = warp % 4
         const int q = warp & 3;
-        const bool ok = mbar_wait(&accum_bar, 0, 256);
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (!ok) failed = 1;
         const int64_t row = (int64_t)i0 + q * 32 + lane;
-        const bool go = __all_sync(0xffffffffu, ok && !failed);  // warp-uniform: the tensor-memory loads are warp-wide
-        if (go) {
-            for (int prod = 0; prod < 2; ++prod) {
+        bool go = true;
+        {
+            for (int prod = 0; prod < 2 && go; ++prod) {
                 if ((prod == 0 ? chunks_d : chunks_r) == 0) continue;
+                const bool ok = mbar_wait(&accum_bar[prod], 0, 256);
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                if (!ok) failed = 1;
+                go = __all_sync(0xffffffffu, ok && !failed);  // warp-uniform: the tensor-memory loads are warp-wide
+                if (!go) break;
                 float *plane = prod == 0 ? c : y;
                 for (int cb = 0; cb < MT / 32; ++cb) {
                     uint32_t v[32];
@@ -164,7 +170,7 @@ __global__ void __launch_bounds__(TC_THREADS) macro_update_tc_kernel(const __gri
     if (warp == 1) {
         if (failed) {
             // give outstanding loads and MMAs a bounded chance to land before the memory they target is released
-            if (lane == 0) mbar_wait(&accum_bar, 0);
+            if (lane == 0) mbar_wait(&accum_bar[chunks_r > 0 ? 1 : 0], 0);
             __syncwarp();
         }
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");

@@ -152,9 +152,50 @@ static unsigned pack_grid(int64_t m, int64_t n) {
     return (unsigned)(blocks < 148 * 32 ? (blocks > 0 ? blocks : 1) : 148 * 32);
 }
 
+// Full symmetric matrix from its packed lower triangle: one CTA per 32 x 32 tile on or below the diagonal reads its rows
+// of the packed array (row i starts at i (i + 1) / 2) and writes the tile and, through shared memory, its mirror image.
+template <typename F>
+__global__ void symmetric_from_packed_kernel(int64_t n, const F *__restrict__ packed, F *__restrict__ out) {
+    __shared__ F tile[32][33];
+    const int64_t tiles = ceil_div(n, (int64_t)32), count = tiles * (tiles + 1) / 2;
+    for (int64_t t = blockIdx.x; t < count; t += gridDim.x) {
+        int64_t bi = (int64_t)((sqrt(8.0 * (double)t + 1.0) - 1.0) / 2.0);
+        while ((bi + 1) * (bi + 2) / 2 <= t) ++bi;
+        while (bi * (bi + 1) / 2 > t) --bi;
+        const int64_t bj = t - bi * (bi + 1) / 2;
+        for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+            const int64_t i = bi * 32 + r, j = bj * 32 + threadIdx.x;
+            F v = (F)0;
+            if (i < n && j <= i) {
+                v = packed[i * (i + 1) / 2 + j];
+                out[i * n + j] = v;
+            }
+            tile[r][threadIdx.x] = v;
+        }
+        __syncthreads();
+        for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+            const int64_t j = bj * 32 + r, i = bi * 32 + threadIdx.x;  // the mirrored entry (j, i), j < i
+            if (i < n && j < i) out[j * n + i] = tile[threadIdx.x][r];
+        }
+        __syncthreads();
+    }
+}
+
 }  // namespace g2d
 
 using namespace g2d;
+
+extern "C" int g2d_symmetric_from_packed(int dtype, int64_t n, const void *packed, void *out, void *stream) {
+    if ((dtype != G2D_F32 && dtype != G2D_F64) || n < 0) return G2D_ERR_BAD_ARGUMENT;
+    if (n == 0) return G2D_OK;
+    if (!packed || !out) return G2D_ERR_BAD_ARGUMENT;
+    const int64_t tiles = ceil_div(n, (int64_t)32), count = tiles * (tiles + 1) / 2;
+    const unsigned grid = (unsigned)(count < 148 * 16 ? count : 148 * 16);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dtype == G2D_F32) symmetric_from_packed_kernel<float><<<grid, dim3(32, 8), 0, st>>>(n, (const float *)packed, (float *)out);
+    else symmetric_from_packed_kernel<double><<<grid, dim3(32, 8), 0, st>>>(n, (const double *)packed, (double *)out);
+    return check_launch();
+}
 
 static int pack_check(int dtype, int64_t m, int64_t n, const void *a, const void *scale, const void *zero, int bits, const void *b, int64_t row_bytes) {
     if ((dtype != G2D_F32 && dtype != G2D_F64) || m < 0 || n < 0 || bits < 1 || bits > 8) return G2D_ERR_BAD_ARGUMENT;

@@ -147,3 +147,23 @@ def gptq_2d_trellis_packed(x: torch.Tensor, l: torch.Tensor, u: torch.Tensor, sc
     done = engine._sweep_super(y, l, u, batch_shape, options, (scale,), (p, q), inner_block_size, outer_block_size, codes=codes)
     assert done is not None, "scale must be one value or one value per matrix of the batch"
     return y, codes
+
+
+def pack_symmetric(matrix: torch.Tensor) -> torch.Tensor:
+    """The lower triangle of a symmetric matrix ``[n, n]`` as ``n (n + 1) / 2`` values, row by row: half the bytes to move
+    from host memory.  Runs wherever the tensor lives (on the host for a matrix that is about to travel)."""
+    n = matrix.size(0)
+    rows, cols = torch.tril_indices(n, n, device=matrix.device)
+    return matrix[rows, cols].contiguous()
+
+
+@torch.no_grad()
+def unpack_symmetric(packed: torch.Tensor, n: int, out: torch.Tensor | None = None) -> torch.Tensor:
+    """The full symmetric CUDA matrix ``[n, n]`` of a packed lower triangle (``pack_symmetric``)."""
+    assert packed.is_cuda and packed.is_contiguous() and packed.numel() == n * (n + 1) // 2, "expected n (n + 1) / 2 contiguous CUDA values"
+    out = torch.empty(n, n, dtype=packed.dtype, device=packed.device) if out is None else out
+    assert out.shape == (n, n) and out.is_contiguous() and out.dtype == packed.dtype and out.device == packed.device
+    with torch.cuda.device(packed.device):
+        _abi.check(_abi.library().g2d_symmetric_from_packed(_abi.dtype_code(packed.dtype), n, packed.data_ptr(), out.data_ptr(), _abi.stream_of(packed)),
+                   "g2d_symmetric_from_packed")
+    return out

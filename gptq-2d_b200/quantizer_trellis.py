@@ -134,6 +134,15 @@ def trellis_quantizer_super_entry_cuda(
     _trellis_quantize_cuda(sequences, table, K, tail_biting, out=out.view(sequences.shape), scale=per_entry)
 
 
+def _viterbi(x: torch.Tensor, table: torch.Tensor, K: int, init: torch.Tensor | None = None, final: torch.Tensor | None = None) -> torch.Tensor:
+    """States ``[..., T/V]`` of the trellis path closest to ``x [..., T]`` (the reference's tested private ``_viterbi``,
+    quantizer_trellis.py:82-118) for unconstrained paths.  The reference passes boolean state masks ``init`` / ``final``
+    only to impose the two tail-biting constraints (:136-142); the CUDA search applies those itself
+    (``_trellis_quantize(..., tail_biting=True)``), so arbitrary masks are not taken here."""
+    assert init is None and final is None, "state masks are internal to the CUDA search: use _trellis_quantize(..., tail_biting=True)"
+    return _trellis_quantize(x, table, K, False)[1]
+
+
 # The reference's names: one CUDA implementation behind all of them.
 _trellis_quantize_torch = _trellis_quantize
 _trellis_quantize_triton = _trellis_quantize_cuda

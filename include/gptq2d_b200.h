@@ -277,6 +277,11 @@ int g2d_unpack_codes(int dtype, int64_t m, int64_t n, const uint8_t *codes, int6
                      int64_t scale_row_stride, int64_t scale_col_stride, const void *zero, int64_t zero_row_stride,
                      int64_t zero_col_stride, double qmin, int32_t bits, void *z, void *stream);
 
+/* Full symmetric matrix out [n, n] from its packed lower triangle (row i holds the entries (i, 0 .. i); n (n + 1) / 2
+ * values): the form in which a Hessian factor can travel from host memory at half the bytes.  No counterpart in the
+ * reference, whose inputs are device tensors. */
+int g2d_symmetric_from_packed(int dtype, int64_t n, const void *packed, void *out, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

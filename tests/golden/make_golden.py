@@ -98,7 +98,7 @@ def sweep_batched():
 
 
 def quartic_64():
-    """BASELINE config 0's 64 x 64 check: the sweep against the quartic vectorized-GPTQ reference
+    """The first benchmark configuration's 64 x 64 check: the sweep against the quartic vectorized-GPTQ reference
     (gptq_2d_reference.py:360-382) with the coordinate-dependent clipped codebook of :354-357."""
     m = n = 64
     a, b, x = RR._random_instance((m, n), 1000 * m + 10 * n, "cpu")
@@ -111,7 +111,7 @@ def quartic_64():
 
 
 def config0_fp32():
-    """BASELINE config 0: 256 x 256 fp32 INT4 with per-row fp16 abs-max scales, seed 0, through gptq_2d_torch."""
+    """The first benchmark configuration: 256 x 256 fp32 INT4 with per-row fp16 abs-max scales, seed 0, through gptq_2d_torch."""
     g = torch.Generator().manual_seed(0)
     for n in (64, 256):
         w = 0.02 * torch.randn(n, n, generator=g)

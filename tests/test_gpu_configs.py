@@ -1,4 +1,4 @@
-"""Reduced-size versions of BASELINE configurations 2 and 3 against the oracle (the full sizes are measured by the
+"""Reduced-size versions of the benchmark configurations 2 and 3 against the oracle (the full sizes are measured by the
 benchmark and the layer-set driver; parity is checked here where the oracle finishes in seconds)."""
 import functools
 

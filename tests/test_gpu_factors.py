@@ -61,7 +61,7 @@ def test_against_oracle_and_properties(K, oracle, n, size):
     assert off.abs().max().item() < 1e-9 * d.diagonal().abs().max().item()
     # float32 stays close to the float64 factor
     l32 = K.ldl_of_inverse(cuda(gram.astype(np.float32)), size)
-    assert (l32.double() - l).abs().max().item() < 2e-3
+    assert (l32.double() - l).abs().max().item() < 2e-5 * max(1.0, l.abs().max().item())
     check_structure(l32, size)
 
 
@@ -156,17 +156,26 @@ def test_d_sided_affine_and_blocks(K, oracle):
         assert torch.equal(got.cpu(), torch.from_numpy(want)), (inner, outer)
 
 
-def test_d_sided_large_float32_agrees_with_kronecker_route(K):
-    """16 x 256 x 1024 in float32: the mode-by-mode engine keeps factors of 16^2 + 256^2 + 1024^2 values where the
-    Kronecker route forms a 4096^2 row factor; with well-conditioned factors both give the same codes."""
+def test_d_sided_large_agrees_with_kronecker_route(K):
+    """16 x 256 x 1024: the mode-by-mode engine keeps factors of 16^2 + 256^2 + 1024^2 values where the Kronecker route
+    forms a 4096^2 row factor.  In float64 (a quarter of the size) both routes give the same values bit for bit; in
+    float32 the two routes add the feedback in different orders, and a rounding that flips at a near-tie changes the
+    entries after it, so the codes agree on about 99 % of the entries (measured: 99.2 %), not on all."""
     gen = torch.Generator(device="cuda").manual_seed(5)
-    shape = (16, 256, 1024)
-    x = 4 * torch.randn(shape, generator=gen, device="cuda")
-    factors = [torch.tril(torch.randn(k, k, generator=gen, device="cuda") * (0.3 / k ** .5), -1) + torch.eye(k, device="cuda") for k in shape]
+
+    def problem(shape, dtype):
+        x = 4 * torch.randn(shape, generator=gen, device="cuda", dtype=dtype)
+        factors = [torch.tril(torch.randn(k, k, generator=gen, device="cuda", dtype=dtype) * (0.3 / k ** .5), -1) + torch.eye(k, device="cuda", dtype=dtype)
+                   for k in shape]
+        return x, factors
+
+    x, factors = problem((8, 64, 512), torch.float64)
+    assert torch.equal(K.gptq_d_sided(x, factors), K.gptq_d_sided(x, factors, dense_row_factor=True))
+    x, factors = problem((16, 256, 1024), torch.float32)
     got = K.gptq_d_sided(x, factors)
     dense = K.gptq_d_sided(x, factors, dense_row_factor=True)
-    assert (got == dense).double().mean().item() >= 0.9999
-    assert (got - x).abs().max().item() < 4.0
+    assert (got == dense).double().mean().item() >= 0.98
+    assert torch.equal(got, torch.round(got)) and (got - x).abs().max().item() < 4.0
 
 
 @pytest.mark.parametrize("k, n", [(1000, 512), (37, 132), (4096, 1100), (64, 4)])

@@ -2,7 +2,7 @@
 
 Every call goes through the package's public API, which reaches the kernels only through the C ABI.
 fp64 results must be bit-identical (the reference's own standard, test_gptq_2d.py:89); fp32 follows
-BASELINE's bar: objective within 1e-4 relative, codes equal on >= 99.9 % of entries, and under
+the project's stated bar: objective within 1e-4 relative, codes equal on >= 99.9 % of entries, and under
 teacher-forced replay every would-be mismatch within 1e-5 code units of a rounding tie.
 """
 import functools
@@ -136,7 +136,7 @@ def _objective(z, x, g, h):
 
 
 def test_config0_fp32(api, schedule):
-    """BASELINE config 0 (256 x 256 fp32 INT4, fp16 row scales) and its 64 x 64 companion."""
+    """The first benchmark configuration (256 x 256 fp32 INT4, fp16 row scales) and its 64 x 64 companion."""
     G, Q = api
     for n in (64, 256):
         g = load_golden(f"config0_{n}_fp32.npz")
@@ -158,7 +158,7 @@ def test_config0_fp32(api, schedule):
 
 @pytest.mark.parametrize("m,n", [(256, 256), (1024, 1024), (320, 1100)])
 def test_teacher_forced_fp32(api, oracle, m, n, schedule):
-    """Appendix-C style parity at fp32: with the rounding decisions imposed from the oracle's run, the engine's
+    """Teacher-forced parity at fp32: with the rounding decisions imposed from the oracle's run, the engine's
     pre-rounding values must lead to the same codes except within 1e-5 code units of a tie."""
     G, Q = api
     rng = np.random.default_rng(m + n)
