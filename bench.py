@@ -376,37 +376,58 @@ def main() -> None:
         torch.cuda.synchronize()
         parts[name] = begin.elapsed_time(end) / args.steps
 
-    # ---- end to end through the public call with HOST buffers: H2D of W, L, U and D2H of Z inside the timed region ----
-    host_w, host_l, host_u = (t.cpu().pin_memory() for t in (w, g, h))
+    # ---- end to end through the public call with HOST buffers, every step, inside the timed region.  Two transfer
+    # formats: the compact one (the headline `e2e`: W and the packed lower triangles of the symmetric G and H in, packed
+    # INT4 codes and fp16 row scales out) and plain float matrices both ways (`e2e_float_io`) ----
+    import packed_codes as P
+
+    host_w, host_g, host_h = (t.cpu().pin_memory() for t in (w, g, h))
+    host_gp, host_hp = (P.pack_symmetric(t).pin_memory() for t in (host_g, host_h))
     host_z = [torch.empty_like(host_w).pin_memory() for _ in range(2)]
+    host_codes = [torch.empty(m, (n * 4 + 7) // 8, dtype=torch.uint8).pin_memory() for _ in range(2)]
+    host_scales = [torch.empty(m, dtype=torch.float16).pin_memory() for _ in range(2)]
     e2e_count = [0]
 
-    def e2e_step():
-        # host buffers in, host buffer out, every step: G and H then the factors on the front stream, W on a copy stream,
-        # Z back on an output stream behind the sweep; two layers in flight
+    def e2e_step_packed():
+        # G and H triangles, their unpacking and the factors on the front stream, W on a copy stream, codes and scales
+        # back on an output stream behind the sweep; two layers in flight
         e2e_count[0] += 1
-        return pipeline.quantize_from_host(host_w, host_l, host_u, host_z[e2e_count[0] % 2])
+        k = e2e_count[0] % 2
+        return pipeline.quantize_from_host_packed(host_w, host_gp, host_hp, host_codes[k], host_scales[k])
 
-    e2e_step()
-    barrier()
-    begin.record()
-    for _ in range(args.steps):
-        arrived = e2e_step()
-    torch.cuda.current_stream(device).wait_event(arrived)  # the last result has reached the host buffer
-    end.record()
-    barrier()
-    e2e_ms = begin.elapsed_time(end)
-    if world > 1:
-        t = torch.tensor([e2e_ms], device=device, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = t.item()
-    e2e_ms /= args.steps
-    h2d = (host_w.numel() + host_l.numel() + host_u.numel()) * 4
-    d2h = host_z[0].numel() * 4
+    def e2e_step_float():
+        e2e_count[0] += 1
+        return pipeline.quantize_from_host(host_w, host_g, host_h, host_z[e2e_count[0] % 2])
+
+    def time_e2e(one_step):
+        one_step()
+        barrier()
+        begin.record()
+        for _ in range(args.steps):
+            arrived = one_step()
+        torch.cuda.current_stream(device).wait_event(arrived)  # the last result has reached the host buffer
+        end.record()
+        barrier()
+        ms = begin.elapsed_time(end)
+        if world > 1:
+            t = torch.tensor([ms], device=device, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = t.item()
+        return ms / args.steps
+
+    e2e_ms = time_e2e(e2e_step_packed)
+    last = e2e_count[0] % 2  # the buffers the last packed step wrote (the device is idle: time_e2e ends with a synchronisation)
+    decoded = P.unpack_codes(host_codes[last].to(device), host_scales[last].to(device).float()[:, None], torch.zeros((), device=device),
+                             qmin=-8, bits=4, n=n)
+    assert torch.equal(decoded, z), "the codes that reached the host must decode to the device-timed result"
+    e2e_float_ms = time_e2e(e2e_step_float)
+    h2d = host_w.numel() * 4 + (host_gp.numel() + host_hp.numel()) * 4
+    d2h = host_codes[0].numel() + host_scales[0].numel() * 2
+    h2d_float, d2h_float = (host_w.numel() + host_g.numel() + host_h.numel()) * 4, host_z[0].numel() * 4
     # what the asynchronous calls of the timed regions could not report: a factor that is not positive definite, or a
     # bounded wait inside a tensor-core kernel that ran out (raises)
     pipeline.check()
-    del host_w, host_l, host_u, host_z
+    del host_w, host_g, host_h, host_gp, host_hp, host_z
 
     # ---- the layer-set half of the metric: a fixed subset of the 70B-shaped set, partitioned by matrix over the ranks ----
     set_summary = None
@@ -497,7 +518,10 @@ def main() -> None:
             "objective_vs_round_to_nearest": objective_vs_rtn, "status": "factor pivots and kernel wait flags read after the timed regions: clean",
         },
         "clocks": clocks.summary(),
-        "e2e": {"value": e2e_ms / 1e3 / world, "unit": "s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "e2e": {"value": e2e_ms / 1e3 / world, "unit": "s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "format": "LayerPipeline.quantize_from_host_packed: W float32, G and H as packed lower triangles in; INT4 codes and fp16 row scales out"},
+        "e2e_float_io": {"value": e2e_float_ms / 1e3 / world, "unit": "s", "h2d_bytes_per_step": h2d_float, "d2h_bytes_per_step": d2h_float,
+                         "format": "LayerPipeline.quantize_from_host: W, G, H as float32 matrices in, Z as a float32 matrix out"},
         "gpu_launches": int(launches),
         "roofline": roofline,
     }

@@ -60,6 +60,7 @@ class SuperDesc(ctypes.Structure):
         ("trellis_L", _i32), ("trellis_K", _i32), ("trellis_V", _i32), ("tail_biting", _i32),
         ("codes", _vp),
         ("workspace", _vp), ("workspace_bytes", ctypes.c_size_t),
+        ("table_distinct", _vp), ("table_ids", _vp), ("table_distinct_count", _i32), ("reserved", _i32),
     ]
 
 
@@ -84,6 +85,8 @@ _SIGNATURES = {
     "g2d_sweep_super_entry": (ctypes.c_int, [ctypes.POINTER(SuperDesc), _vp]),
     "g2d_trellis_code_bytes": (ctypes.c_int, [_i32, _i32, _i32, _i32, _i32, ctypes.POINTER(_i64)]),
     "g2d_trellis_quantize_packed": (ctypes.c_int, [ctypes.c_int, _i64, _i32, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp, ctypes.c_size_t, _vp]),
+    "g2d_trellis_quantize_indexed": (ctypes.c_int, [ctypes.c_int, _i64, _i32, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _vp, _vp,
+                                                    ctypes.c_size_t, _vp]),
     "g2d_trellis_decode": (ctypes.c_int, [ctypes.c_int, _i64, _i32, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp]),
     "g2d_sweep_fused_profile": (ctypes.c_int, [ctypes.POINTER(SweepDesc), _vp, ctypes.POINTER(ctypes.c_double)]),
     "g2d_launch_count": (ctypes.c_ulonglong, []),

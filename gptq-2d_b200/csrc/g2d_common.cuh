@@ -205,8 +205,15 @@ int launch_syrk_tc(int count, const SyrkTcTarget *targets, cudaStream_t stream);
 // Trellis (Viterbi) search of `rows` sequences (see g2d_trellis.cu); `codes` optional packed paths, code bytes apart.
 int64_t trellis_code_bytes(int T, int L, int K, int V, int tail_biting);
 size_t trellis_scratch_bytes(int dtype, int64_t rows, int T, int L, int K, int V);
+// An optional index of the code table: its distinct rows ([count, V], in the table's dtype) and, per state, the number of
+// its row among them.  Tables with few distinct rows are searched from shared memory with it (same results).
+struct TrellisIndex {
+    const void *distinct;
+    const uint16_t *ids;
+    int count;
+};
 int launch_trellis(int dtype, int64_t rows, int T, const void *x, const void *table, int L, int K, int V, int tail, const void *scale,
-                   void *out, int64_t *states, void *workspace, uint8_t *codes, cudaStream_t st);
+                   void *out, int64_t *states, void *workspace, uint8_t *codes, cudaStream_t st, const TrellisIndex *index = nullptr);
 
 template <typename F>
 int launch_tile_sweep(const SweepArgs<F> &args, int S, cudaStream_t stream, int parity = 0);

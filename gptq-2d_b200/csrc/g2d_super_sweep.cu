@@ -336,8 +336,10 @@ int sweep_super(const g2d_super_desc *d, const Plan &plan, cudaStream_t st) {
                 if (check_launch() != G2D_OK) return G2D_ERR_CUDA;
                 if (d->quant_kind == G2D_Q_TRELLIS) {
                     uint8_t *stage_codes = d->codes ? (uint8_t *)(ws + plan.stage_codes) : nullptr;
+                    const TrellisIndex index{d->table_distinct, d->table_ids, d->table_distinct_count};
                     const int status = launch_trellis(d->dtype, d->batch * dmax, T, A.xs, d->table, d->trellis_L, d->trellis_K, d->trellis_V,
-                                                      d->tail_biting, A.row_scale, z, nullptr, ws + plan.viterbi, stage_codes, st);
+                                                      d->tail_biting, A.row_scale, z, nullptr, ws + plan.viterbi, stage_codes, st,
+                                                      d->table_ids != nullptr ? &index : nullptr);
                     if (status != G2D_OK) return status;
                     if (stage_codes) {
                         scatter_codes_kernel<F><<<blocks_for(d->batch * dmax * plan.code_bytes, 256), 256, 0, st>>>(A, stage_codes, d->codes, plan.code_bytes);
@@ -388,6 +390,8 @@ extern "C" int g2d_sweep_super_entry(const g2d_super_desc *desc, void *stream) {
     if (!desc->y || !desc->l || !desc->u) return G2D_ERR_BAD_ARGUMENT;
     if (desc->quant_kind == G2D_Q_AFFINE && (!desc->scale || !desc->zero)) return G2D_ERR_BAD_ARGUMENT;
     if (desc->quant_kind == G2D_Q_TRELLIS && (!desc->scale || !desc->table)) return G2D_ERR_BAD_ARGUMENT;
+    if (desc->table_ids != nullptr && (!desc->table_distinct || desc->table_distinct_count <= 0 || ((uintptr_t)desc->table_ids & 15) != 0))
+        return G2D_ERR_BAD_ARGUMENT;
     if (desc->quant_kind == G2D_Q_ABSMAX_DYNAMIC && desc->half != G2D_FP16 && desc->half != G2D_BF16) return G2D_ERR_BAD_ARGUMENT;
     for (int k = 0; k < desc->lead_count; ++k)
         if (!desc->lead_factor[k]) return G2D_ERR_BAD_ARGUMENT;

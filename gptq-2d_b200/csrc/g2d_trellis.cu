@@ -273,6 +273,183 @@ __global__ void __launch_bounds__(VT) viterbi_kernel(int64_t rows, int T, const 
     }
 }
 
+// The same search for a code table with few distinct rows.  The shipped codes map 2^16 states onto about a thousand
+// distinct value tuples (HYB: 2^9 lookup rows times a sign; 1MAD: a sum of four bytes), and the local cost of a state
+// depends on its tuple only.  With the states' tuple numbers (`ids`, 16 bits each, the whole array in shared memory) and
+// the distinct tuples, a step first forms the D local costs of every sequence (the same subtractions, products and sum
+// as above, so the same bits), then every state costs one shared-memory lookup and one addition instead of a table load
+// from L2 and five arithmetic instructions.  A thread takes eight neighbouring groups at a time: their tuple numbers are
+// one 16-byte load and they share their predecessors' group minimum.  Results are bit for bit those of viterbi_kernel.
+template <typename F, int R>
+__global__ void __launch_bounds__(VT) viterbi_indexed_kernel(int64_t rows, int T, const F *__restrict__ x, const F *__restrict__ table,
+                                                             const F *__restrict__ distinct, int D, const uint16_t *__restrict__ ids,
+                                                             int Lbits, int shift, int V, int tail_biting, const F *__restrict__ scale,
+                                                             F *__restrict__ out, int64_t *__restrict__ states, uint8_t *__restrict__ choices,
+                                                             uint8_t *__restrict__ codes, int64_t code_bytes) {
+    extern __shared__ __align__(16) unsigned char g2d_vsmem[];
+    const int S = 1 << Lbits, G = S >> shift, H = 1 << shift;
+    const int steps = T / V;
+    uint16_t *id_s = reinterpret_cast<uint16_t *>(g2d_vsmem);                        // [S]
+    F *B = reinterpret_cast<F *>(g2d_vsmem + (size_t)S * sizeof(uint16_t));          // [2][R][G]
+    F *dist = B + (size_t)2 * R * G;                                                 // [R][D]
+    __shared__ F red_val[VT / 32][R];
+    __shared__ int red_arg[VT / 32][R];
+    __shared__ int seq_state[R], seq_overlap[R];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int64_t slots = steps > 1 ? steps - 1 : 1;
+    for (int i = tid; i < S / 8; i += VT) reinterpret_cast<uint4 *>(id_s)[i] = reinterpret_cast<const uint4 *>(ids)[i];
+
+    for (int64_t row0 = (int64_t)blockIdx.x * R; row0 < rows; row0 += (int64_t)gridDim.x * R) {
+        if (tid < R) seq_overlap[tid] = -1;
+        __syncthreads();
+        for (int pass = tail_biting ? 0 : 1; pass < 2; ++pass) {
+            const int half = steps / 2;
+            const int roll = pass == 0 ? steps - half : 0;
+            const int stop = pass == 0 ? half : 0;
+            for (int t = 0; t < steps; ++t) {
+                const bool last = t == steps - 1;
+                const F *prev = B + (size_t)((t + 1) & 1) * R * G;
+                F *next = B + (size_t)(t & 1) * R * G;
+                F x0[R], x1[R];
+                int ov[R];
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    const int64_t row = row0 + r < rows ? row0 + r : rows - 1;
+                    const F *xt = x + row * T + (int64_t)((t + roll) % steps) * V;
+                    x0[r] = xt[0];
+                    x1[r] = V == 2 ? xt[1] : (F)0;
+                    ov[r] = seq_overlap[r];
+                }
+                // the local cost of every distinct tuple, for every sequence of the CTA
+                for (int d = tid; d < D; d += VT) {
+                    const F t0 = distinct[(int64_t)d * V], t1 = V == 2 ? distinct[(int64_t)d * V + 1] : (F)0;
+#pragma unroll
+                    for (int r = 0; r < R; ++r) {
+                        const F d0 = sub_rn(t0, x0[r]);
+                        F c = mul_rn(d0, d0);
+                        if (V == 2) {
+                            const F d1 = sub_rn(t1, x1[r]);
+                            c = add_rn(c, mul_rn(d1, d1));
+                        }
+                        dist[r * D + d] = c;
+                    }
+                }
+                __syncthreads();
+                if (!last) {
+                    // group minima of this step: eight neighbouring groups per thread and round
+                    for (int g0 = tid * 8; g0 < G; g0 += VT * 8) {
+                        F best[R][8];
+                        int arg[R][8];
+                        for (int h = 0; h < H; ++h) {
+                            const uint4 packed = *reinterpret_cast<const uint4 *>(id_s + (size_t)h * G + g0);
+                            const uint32_t word[4] = {packed.x, packed.y, packed.z, packed.w};
+                            const int low = (h * G + g0) >> shift;  // shared by the eight groups when shift >= 3
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) {
+                                const int id = (word[e >> 1] >> ((e & 1) * 16)) & 0xFFFF;
+                                const int low_e = shift >= 3 ? low : (h * G + g0 + e) >> shift;
+#pragma unroll
+                                for (int r = 0; r < R; ++r) {
+                                    F c = dist[r * D + id];
+                                    if (t == 0) {
+                                        if (ov[r] >= 0 && low_e != ov[r]) c = pos_inf<F>();
+                                    } else {
+                                        c = add_rn(prev[r * G + low_e], c);
+                                    }
+                                    if (h == 0 || c < best[r][e]) { best[r][e] = c; arg[r][e] = h; }
+                                }
+                            }
+                        }
+#pragma unroll
+                        for (int r = 0; r < R; ++r)
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) {
+                                next[r * G + g0 + e] = best[r][e];
+                                if (row0 + r < rows) choices[((row0 + r) * slots + t) * G + g0 + e] = (uint8_t)arg[r][e];
+                            }
+                    }
+                    __syncthreads();
+                } else {
+                    // last step: first arg-min over all states, with the final mask
+                    F best[R];
+                    int arg[R];
+#pragma unroll
+                    for (int r = 0; r < R; ++r) { best[r] = pos_inf<F>(); arg[r] = S; }
+                    for (int s = tid; s < S; s += VT) {
+                        const int id = id_s[s], low = s >> shift;
+#pragma unroll
+                        for (int r = 0; r < R; ++r) {
+                            F c = dist[r * D + id];
+                            if (t == 0) {
+                                if (ov[r] >= 0 && low != ov[r]) c = pos_inf<F>();
+                            } else {
+                                c = add_rn(prev[r * G + low], c);
+                            }
+                            if (ov[r] >= 0 && (s & (G - 1)) != ov[r]) c = pos_inf<F>();
+                            if (arg[r] == S || c < best[r]) { best[r] = c; arg[r] = s; }  // ascending s: strict < keeps the first minimum
+                        }
+                    }
+#pragma unroll
+                    for (int r = 0; r < R; ++r) {
+                        F b = best[r];
+                        int a = arg[r];
+#pragma unroll
+                        for (int o = 16; o > 0; o >>= 1) {
+                            const F ob = __shfl_xor_sync(0xffffffffu, b, o);
+                            const int oa = __shfl_xor_sync(0xffffffffu, a, o);
+                            if (oa < S && (a >= S || ob < b || (ob == b && oa < a))) { b = ob; a = oa; }
+                        }
+                        if (lane == 0) { red_val[warp][r] = b; red_arg[warp][r] = a; }
+                    }
+                    __syncthreads();
+                    if (tid < R) {
+                        F b = red_val[0][tid];
+                        int a = red_arg[0][tid];
+                        for (int w = 1; w < VT / 32; ++w) {
+                            const F ob = red_val[w][tid];
+                            const int oa = red_arg[w][tid];
+                            if (oa < S && (a >= S || ob < b || (ob == b && oa < a))) { b = ob; a = oa; }
+                        }
+                        seq_state[tid] = a;
+                    }
+                    __syncthreads();
+                }
+            }
+            // ---- walk back: thread r follows sequence r ----
+            if (tid < R && row0 + tid < rows) {
+                const int64_t row = row0 + tid;
+                long long state = seq_state[tid];
+                const F sc = scale ? scale[row] : (F)1;
+                uint8_t *code = (pass == 1 && codes) ? codes + row * code_bytes : nullptr;
+                const int header = tail_biting ? 0 : Lbits - shift;
+                if (code)
+                    for (int64_t b = 0; b < code_bytes; ++b) code[b] = 0;
+                for (int t = steps - 1; t >= stop; --t) {
+                    if (pass == 1) {
+                        for (int v = 0; v < V; ++v) out[row * T + (int64_t)t * V + v] = mul_rn(table[state * V + v], sc);
+                        if (states) states[row * steps + t] = state;
+                        if (code) {
+                            for (int b = 0; b < shift; ++b) {
+                                const int64_t at = header + (int64_t)t * shift + b;
+                                if ((state >> (shift - 1 - b)) & 1) code[at >> 3] |= (uint8_t)(1u << (at & 7));
+                            }
+                            if (t == 0)
+                                for (int b = 0; b < header; ++b)
+                                    if ((state >> (Lbits - 1 - b)) & 1) code[b >> 3] |= (uint8_t)(1u << (b & 7));
+                        }
+                    }
+                    if (t > stop) {
+                        const long long low = state >> shift;
+                        state = (long long)choices[(row * slots + (t - 1)) * G + low] * G + low;
+                    }
+                }
+                if (pass == 0) seq_overlap[tid] = (int)(state >> shift);
+            }
+            __syncthreads();
+        }
+    }
+}
+
 // Values (and optionally states) of stored bit strings: one thread per (sequence, step) rebuilds the state from the L
 // bits of the string that end with the step's symbol.
 template <typename F>
@@ -345,9 +522,42 @@ size_t trellis_scratch_bytes(int dtype, int64_t rows, int T, int L, int K, int V
     return ((size_t)rows * slots * G + 255) & ~(size_t)255;
 }
 
+template <typename F, int R>
+static int launch_viterbi_indexed(int64_t rows, int T, const void *x, const void *table, const TrellisIndex &index, int L, int K, int V, int tail,
+                                  const void *scale, void *out, int64_t *states, void *workspace, uint8_t *codes, int64_t code_bytes, cudaStream_t st) {
+    static PerDeviceOnce configured;
+    const int64_t S = (int64_t)1 << L, G = S >> (K * V);
+    const size_t smem = (size_t)S * sizeof(uint16_t) + sizeof(F) * (2 * R * (size_t)G + (size_t)R * index.count);
+    if (configured.run([&] { return cudaFuncSetAttribute(viterbi_indexed_kernel<F, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024) == cudaSuccess; }) != G2D_OK)
+        return G2D_ERR_CUDA;
+    int64_t blocks = ceil_div(rows, R);
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    viterbi_indexed_kernel<F, R><<<(unsigned)blocks, VT, smem, st>>>(rows, T, (const F *)x, (const F *)table, (const F *)index.distinct, index.count,
+                                                                     index.ids, L, K * V, V, tail, (const F *)scale, (F *)out, states,
+                                                                     (uint8_t *)workspace, codes, code_bytes);
+    return check_launch();
+}
+
+// The indexed search serves tables of up to 2^16 states whose distinct rows fit shared memory beside the group minima.
+template <typename F>
+static int indexed_sequences_per_cta(const TrellisIndex *index, int64_t rows, int L, int K, int V) {
+    if (index == nullptr || index->ids == nullptr || index->distinct == nullptr || index->count <= 0) return 0;
+    const int64_t S = (int64_t)1 << L, G = S >> (K * V);
+    if (L > 16 || G < 8 || S < 8) return 0;
+    auto bytes = [&](int R) { return (size_t)S * 2 + sizeof(F) * (2 * R * (size_t)G + (size_t)R * index->count); };
+    const size_t budget = 216 * 1024;
+    if (rows > 148 && bytes(2) <= budget) return 2;
+    return bytes(1) <= budget ? 1 : 0;
+}
+
 int launch_trellis(int dtype, int64_t rows, int T, const void *x, const void *table, int L, int K, int V, int tail, const void *scale,
-                   void *out, int64_t *states, void *workspace, uint8_t *codes, cudaStream_t st) {
+                   void *out, int64_t *states, void *workspace, uint8_t *codes, cudaStream_t st, const TrellisIndex *index) {
     const int64_t code_bytes = trellis_code_bytes(T, L, K, V, tail);
+    const int R = dtype == G2D_F32 ? indexed_sequences_per_cta<float>(index, rows, L, K, V) : indexed_sequences_per_cta<double>(index, rows, L, K, V);
+    if (R == 2 && dtype == G2D_F32) return launch_viterbi_indexed<float, 2>(rows, T, x, table, *index, L, K, V, tail, scale, out, states, workspace, codes, code_bytes, st);
+    if (R == 1 && dtype == G2D_F32) return launch_viterbi_indexed<float, 1>(rows, T, x, table, *index, L, K, V, tail, scale, out, states, workspace, codes, code_bytes, st);
+    if (R == 2) return launch_viterbi_indexed<double, 2>(rows, T, x, table, *index, L, K, V, tail, scale, out, states, workspace, codes, code_bytes, st);
+    if (R == 1) return launch_viterbi_indexed<double, 1>(rows, T, x, table, *index, L, K, V, tail, scale, out, states, workspace, codes, code_bytes, st);
     return dtype == G2D_F32 ? trellis_dispatch<float>(rows, T, x, table, L, K, V, tail, scale, out, states, workspace, codes, code_bytes, st)
                             : trellis_dispatch<double>(rows, T, x, table, L, K, V, tail, scale, out, states, workspace, codes, code_bytes, st);
 }
@@ -399,6 +609,20 @@ extern "C" int g2d_trellis_quantize_packed(int dtype, int64_t rows, int32_t T, c
     if (!tail_biting && (int64_t)(T / V) * K * V + L - K * V < L) return G2D_ERR_BAD_ARGUMENT;
     if (!workspace || workspace_bytes < trellis_scratch_bytes(dtype, rows, T, L, K, V)) return G2D_ERR_WORKSPACE;
     return launch_trellis(dtype, rows, T, x, table, L, K, V, tail_biting, scale, out, nullptr, workspace, codes, (cudaStream_t)stream);
+}
+
+extern "C" int g2d_trellis_quantize_indexed(int dtype, int64_t rows, int32_t T, const void *x, const void *table, int32_t L, int32_t K,
+                                            int32_t V, int32_t tail_biting, const void *scale, void *out, int64_t *states, uint8_t *codes,
+                                            const void *distinct, int32_t distinct_count, const uint16_t *ids, void *workspace,
+                                            size_t workspace_bytes, void *stream) {
+    const int status = trellis_check(dtype, rows, T, L, K, V);
+    if (status != G2D_OK) return status;
+    if (rows == 0) return G2D_OK;
+    if (!x || !table || !out || !distinct || !ids || distinct_count <= 0 || distinct_count > 65536) return G2D_ERR_BAD_ARGUMENT;
+    if (((uintptr_t)ids & 15) != 0) return G2D_ERR_BAD_ARGUMENT;
+    if (!workspace || workspace_bytes < trellis_scratch_bytes(dtype, rows, T, L, K, V)) return G2D_ERR_WORKSPACE;
+    const TrellisIndex index{distinct, ids, distinct_count};
+    return launch_trellis(dtype, rows, T, x, table, L, K, V, tail_biting, scale, out, states, workspace, codes, (cudaStream_t)stream, &index);
 }
 
 extern "C" int g2d_trellis_decode(int dtype, int64_t rows, int32_t T, const uint8_t *codes, const void *table, int32_t L, int32_t K,

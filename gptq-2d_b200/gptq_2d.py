@@ -214,8 +214,12 @@ def _sweep_super(y, l, u, batch_shape, options: dict, quantizer_inputs, super_en
             except RuntimeError:
                 return None
             offsets = torch.arange(per_batch.numel(), dtype=torch.int64, device=y.device)
-        table = options["table"].to(y).contiguous()
-        keep += [per_batch, table, offsets]
+        import quantizer_trellis
+
+        table, index = quantizer_trellis.prepared_table(options["table"], y)
+        keep += [per_batch, table, offsets, index]
+        if index is not None:
+            desc.table_distinct, desc.table_ids, desc.table_distinct_count = index[0].data_ptr(), index[1].data_ptr(), index[0].size(0)
         desc.scale, desc.scale_offsets, desc.table = per_batch.data_ptr(), _abi.ptr(offsets), table.data_ptr()
         desc.trellis_L, desc.trellis_K, desc.trellis_V = table.size(0).bit_length() - 1, options["K"], table.size(1)
         desc.tail_biting = int(bool(options["tail_biting"]))

@@ -224,6 +224,56 @@ class LayerPipeline:
         z.record_stream(self.out)
         return done
 
+    def quantize_from_host_packed(self, host_w, host_g_packed, host_h_packed, host_codes, host_scales):
+        """``quantize_from_host`` in the transfer format that moves the fewest bytes: the two symmetric Hessian factors
+        come as packed lower triangles (``packed_codes.pack_symmetric``: half the bytes), and the result goes back as
+        packed ``bits``-wide integer codes ``host_codes`` (uint8 ``[m, ceil(n bits / 8)]``) with the per-row scales
+        ``host_scales`` (float16 ``[m]``) instead of dequantised floats.  Returns the event that marks both complete."""
+        import torch
+
+        import packed_codes as P
+        import quantizer_int as Q
+
+        main = torch.cuda.current_stream(self.device)
+        m, n = host_w.shape
+        bits = (self.qmax - self.qmin).bit_length()
+        key = ("packed", m, n, host_w.dtype)
+        if key not in self.slots:
+            make = lambda *shape, dtype=host_w.dtype: torch.empty(*shape, dtype=dtype, device=self.device)
+            self.slots[key] = [{"w": make(m, n), "gp": make(host_g_packed.numel()), "hp": make(host_h_packed.numel()), "g": make(m, m), "h": make(n, n),
+                                "free": None} for _ in range(2)]
+        slot = self.slots[key][self.count % 2]
+        self.count += 1
+        if slot["free"] is not None:  # the sweep that read this slot two layers ago has finished
+            self.front.wait_event(slot["free"])
+            self.copy.wait_event(slot["free"])
+        self._throttle()
+        with torch.cuda.stream(self.front):
+            slot["gp"].copy_(host_g_packed, non_blocking=True)
+            slot["hp"].copy_(host_h_packed, non_blocking=True)
+            P.unpack_symmetric(slot["gp"], m, out=slot["g"])
+            P.unpack_symmetric(slot["hp"], n, out=slot["h"])
+        with torch.cuda.stream(self.copy):
+            slot["w"].copy_(host_w, non_blocking=True)
+            arrived = torch.cuda.Event()
+            arrived.record(self.copy)
+        l, u = self._prepare(slot["g"], slot["h"], main)
+        main.wait_event(arrived)
+        z = self._sweep(slot["w"], l, u)
+        scale = Q.int_abs_max_scale_triton(slot["w"], qmin=self.qmin, qmax=self.qmax, dtype=torch.float16)
+        codes = P.pack_codes(z, scale, torch.zeros((), device=self.device, dtype=z.dtype), qmin=self.qmin, bits=bits)
+        scales16 = scale.reshape(m).to(torch.float16)
+        slot["free"] = self._after_sweep(main)
+        self.out.wait_event(slot["free"])
+        with torch.cuda.stream(self.out):  # behind the sweep, beside the next layer
+            host_codes.copy_(codes, non_blocking=True)
+            host_scales.copy_(scales16, non_blocking=True)
+            done = torch.cuda.Event()
+            done.record(self.out)
+        for t in (codes, scales16):
+            t.record_stream(self.out)
+        return done
+
 
 def quantize_matrix(item: dict, device, pipeline: LayerPipeline | None = None):
     """Generate one seeded layer on ``device``, prepare its factors, quantize it to INT4; returns timings and checks.

@@ -71,6 +71,31 @@ def hyb(L: int = 16, tlut: torch.Tensor | None = None, seed: int = 0, device=Non
     return table.to(dtype=dtype)
 
 
+# ---- an index of a code table: its distinct rows ----
+
+_TABLE_INDEX: dict = {}
+_INDEX_LIMIT = 2048  # distinct rows whose local costs fit shared memory beside the search's own buffers
+
+
+def prepared_table(table: torch.Tensor, like: torch.Tensor) -> tuple[torch.Tensor, tuple[torch.Tensor, torch.Tensor] | None]:
+    """The table in ``like``'s dtype and device, contiguous, and its index ``(distinct [D, V], ids int16 [2^L])`` when it has at
+    most 2048 distinct rows and at most 2^16 states (else None).  The shipped codes have about a thousand distinct rows
+    (``hyb``: 2^9 lookup rows times a sign), and the search is much faster when it knows them.  Both are remembered per
+    table (keyed by its storage and version), so a sweep that calls the quantizer a thousand times prepares them once."""
+    key = (table.data_ptr(), table._version, tuple(table.shape), table.dtype, table.device, like.dtype, like.device)
+    if key not in _TABLE_INDEX:
+        if len(_TABLE_INDEX) > 16:
+            _TABLE_INDEX.clear()
+        converted = table.to(like).contiguous()
+        index = None
+        if converted.is_cuda and 64 <= converted.size(0) <= 1 << 16:
+            distinct, inverse = torch.unique(converted, dim=0, return_inverse=True)
+            if distinct.size(0) <= _INDEX_LIMIT:
+                index = (distinct.contiguous(), inverse.to(torch.int16).contiguous())
+        _TABLE_INDEX[key] = (table, converted, index)  # the table itself is kept alive: its address is part of the key
+    return _TABLE_INDEX[key][1:]
+
+
 # ---- the search ------------------------------------------------------------------------------------------------------
 
 def _trellis_quantize_cuda(
@@ -93,7 +118,7 @@ def _trellis_quantize_cuda(
     L = num_states.bit_length() - 1
     assert out.is_contiguous() and out.numel() == rows * T and out.dtype == x.dtype, "out must be contiguous [..., T] in x's dtype"
     scale = scale.to(x.dtype).broadcast_to(out.shape[:-1]).reshape(rows).contiguous()
-    table = table.to(x).contiguous()
+    table, index = prepared_table(table, x)
     if states is not None:
         assert states.is_contiguous() and states.dtype == torch.int64 and states.numel() == rows * (T // V)
     lib = _abi.library()
@@ -105,9 +130,16 @@ def _trellis_quantize_cuda(
     capacity = 1 << max(size.value - 1, 0).bit_length()
     workspace = torch.empty(capacity, dtype=torch.uint8, device=x.device)
     with torch.cuda.device(x.device):
-        _abi.check(lib.g2d_trellis_quantize(
-            code, rows, T, x.data_ptr(), table.data_ptr(), L, K, V, int(bool(tail_biting)), scale.data_ptr(), out.data_ptr(),
-            _abi.ptr(states), workspace.data_ptr(), capacity, _abi.stream_of(x)), "g2d_trellis_quantize")
+        if index is not None:
+            distinct, ids = index
+            _abi.check(lib.g2d_trellis_quantize_indexed(
+                code, rows, T, x.data_ptr(), table.data_ptr(), L, K, V, int(bool(tail_biting)), scale.data_ptr(), out.data_ptr(),
+                _abi.ptr(states), None, distinct.data_ptr(), distinct.size(0), ids.data_ptr(), workspace.data_ptr(), capacity,
+                _abi.stream_of(x)), "g2d_trellis_quantize_indexed")
+        else:
+            _abi.check(lib.g2d_trellis_quantize(
+                code, rows, T, x.data_ptr(), table.data_ptr(), L, K, V, int(bool(tail_biting)), scale.data_ptr(), out.data_ptr(),
+                _abi.ptr(states), workspace.data_ptr(), capacity, _abi.stream_of(x)), "g2d_trellis_quantize")
 
 
 def _trellis_quantize(x: torch.Tensor, table: torch.Tensor, K: int, tail_biting: bool = True) -> tuple[torch.Tensor, torch.Tensor]:

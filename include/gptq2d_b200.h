@@ -145,6 +145,10 @@ typedef struct g2d_super_desc {
     uint8_t *codes;              /* TRELLIS, optional: packed paths, [batch, m / p, n / q, g2d_trellis_code_bytes] */
     void *workspace;             /* g2d_super_workspace_bytes() bytes, 256-byte aligned */
     size_t workspace_bytes;
+    const void *table_distinct;  /* TRELLIS, optional index of the table (see g2d_trellis_quantize_indexed): its distinct rows, */
+    const uint16_t *table_ids;   /* the row number of every state among them (16-byte aligned), */
+    int32_t table_distinct_count; /* and how many there are */
+    int32_t reserved;            /* must be 0 */
 } g2d_super_desc;
 int g2d_super_workspace_bytes(const g2d_super_desc *desc, size_t *bytes);
 int g2d_sweep_super_entry(const g2d_super_desc *desc, void *stream);
@@ -235,6 +239,17 @@ int g2d_trellis_quantize_packed(int dtype, int64_t rows, int32_t T, const void *
                                 void *workspace, size_t workspace_bytes, void *stream);
 int g2d_trellis_decode(int dtype, int64_t rows, int32_t T, const uint8_t *codes, const void *table, int32_t L, int32_t K,
                        int32_t V, int32_t tail_biting, const void *scale, void *out, int64_t *states, void *stream);
+
+/* The same search for a caller who knows which states of the table share their values.  The shipped codes map 2^16
+ * states onto about a thousand distinct value tuples (hyb: quantizer_trellis.py:63-79, a 2^9-row lookup table times a
+ * sign; one_mad: :28-33, a sum of four bytes), and a state's local cost depends on its tuple only.  `distinct` holds the
+ * distinct rows of `table` ([distinct_count, V], same dtype) and `ids[s]` the row of state s among them; tables of up to
+ * 2^16 states whose distinct rows fit shared memory are then searched from shared memory, others as by
+ * g2d_trellis_quantize.  Values, states and stored paths (states, codes: optional) are bit for bit the same. */
+int g2d_trellis_quantize_indexed(int dtype, int64_t rows, int32_t T, const void *x, const void *table, int32_t L, int32_t K,
+                                 int32_t V, int32_t tail_biting, const void *scale, void *out, int64_t *states, uint8_t *codes,
+                                 const void *distinct, int32_t distinct_count, const uint16_t *ids, void *workspace,
+                                 size_t workspace_bytes, void *stream);
 
 /* Unit (block) lower triangular factor of the inverse of a symmetric positive definite matrix:
  * a^{-1} = out Lambda out^T with size x size identity diagonal blocks.  a is [n, n] and is overwritten

@@ -51,7 +51,7 @@ def test_config2_int3_affine_groups(oracle):
     star = np.rint(z_star / scale + zero)
     mismatch = would_be != star
     assert mismatch.mean() <= 1e-3
-    assert (np.abs(np.abs(t - np.floor(t)) - 0.5)[mismatch] <= 5e-5).all()
+    assert (np.abs(np.abs(t - np.floor(t)) - 0.5)[mismatch] <= 1e-5).all()
     agree = (codes.cpu().numpy() == star).mean()
     assert agree > 0.5  # free-running fp32 trajectories drift apart; the bound only guards against gross errors
 
@@ -115,6 +115,23 @@ def test_layer_pipeline_equals_plain_calls():
     for event, out, want in zip(done, outs, expected):
         event.synchronize()
         assert torch.equal(out, want.cpu())
+    # the compact transfer format: packed lower triangles of the symmetric Hessian factors in, packed INT4 codes and
+    # fp16 row scales out; decoding the codes gives the same matrices
+    import packed_codes as P
+
+    packed = [[hw, P.pack_symmetric(hg).pin_memory(), P.pack_symmetric(hh).pin_memory()] for hw, hg, hh in host]
+    assert packed[0][1].numel() == 392 * 393 // 2
+    codes = [torch.empty(392, 260, dtype=torch.uint8).pin_memory() for _ in host]
+    scales = [torch.empty(392, dtype=torch.float16).pin_memory() for _ in host]
+    done = [pipeline.quantize_from_host_packed(hw, hg, hh, c, s) for (hw, hg, hh), c, s in zip(packed, codes, scales)]
+    for event, c, s, want in zip(done, codes, scales, expected):
+        event.synchronize()
+        back = P.unpack_codes(c.cuda(), s.cuda().float()[:, None], torch.zeros((), device=device), qmin=-8, bits=4, n=520)
+        assert torch.equal(back, want)
+    pipeline.check()
+    full = torch.randn(77, 77, device=device, dtype=torch.float64)
+    full = full + full.T
+    assert torch.equal(P.unpack_symmetric(P.pack_symmetric(full), 77), full)
 
 
 def test_shared_input_factors_equal_separate_calls():

@@ -174,14 +174,14 @@ def test_teacher_forced_fp32(api, oracle, m, n, schedule):
     _, y_pre_oracle = oracle.sweep(w, l, u, kind=oracle.Q_FORCED, forced_z=z_star.astype(np.float32), return_y_pre=True)
     y_pre = y_pre.cpu().numpy()
     units = np.abs(y_pre.astype(np.float64) - y_pre_oracle.astype(np.float64)) / full
-    assert units.max() < 5e-4, units.max()
+    assert units.max() < 2e-4, units.max()
     would_be = np.clip(np.rint(y_pre.astype(np.float64) / full), -8, 7)
     star = np.rint(z_star / full)
     mismatch = would_be != star
     assert mismatch.mean() <= 1e-3
     t = y_pre.astype(np.float64) / full
     distance_to_tie = np.abs(np.abs(t - np.floor(t)) - 0.5)
-    assert (distance_to_tie[mismatch] <= 2e-5).all()
+    assert (distance_to_tie[mismatch] <= 1e-5).all()
 
 
 def test_self_consistency_large_fp32(api, schedule):

@@ -30,7 +30,7 @@ def test_descriptor_layout_matches_header():
     # field order and C alignment rules give these sizes for the header's structs on LP64
     assert ctypes.sizeof(_abi.SweepDesc) == 8 + 3 * 8 + 9 * 8 + 4 * 8 + 2 * 8 + 2 * 8 + 2 * 8 + 8 + 8
     assert ctypes.sizeof(_abi.StageDesc) == 16 + 3 * 8 + 7 * 8
-    assert ctypes.sizeof(_abi.SuperDesc) == 6 * 4 + 3 * 8 + 5 * 8 + 2 * 4 + 4 * 8 + 4 * 8 + 4 * 8 + 4 * 8 + 2 * 8 + 8 + 4 * 4 + 8 + 2 * 8
+    assert ctypes.sizeof(_abi.SuperDesc) == 6 * 4 + 3 * 8 + 5 * 8 + 2 * 4 + 4 * 8 + 4 * 8 + 4 * 8 + 4 * 8 + 2 * 8 + 8 + 4 * 4 + 8 + 2 * 8 + 2 * 8 + 2 * 4
 
 
 def test_cpu_tensors_are_rejected_not_emulated():
