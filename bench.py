@@ -290,6 +290,7 @@ def main() -> None:
     parser.add_argument("--size", type=int, default=8192)
     parser.add_argument("--cpu-sample", type=int, default=0, help="side of the CPU arm's sweep sample; 0 chooses by the time budget")
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--no-peak-probe", action="store_true", help="skip the TF32 matrix-product measurement (for runs under a profiler)")
     parser.add_argument("--layer-set-blocks", type=int, default=8, help="blocks of the 70B-shaped layer set run after the timed steps (0: none)")
     args = parser.parse_args()
     if args.impl == "reference":
@@ -473,8 +474,8 @@ def main() -> None:
     far_tflops = far_flops / (far_ms * 1e-3) / 1e12 if far_ms > 0 else 0.0
     near_tflops = near_flops / (near_ms * 1e-3) / 1e12 if near_ms > 0 else 0.0
     panel_tflops = (near_flops + far_flops) / ((near_ms + far_ms) * 1e-3) / 1e12 if near_ms + far_ms > 0 else 0.0
-    tf32 = measure_tf32_peak(device)
-    measured_peak = tf32["sustained_tflops"] / 3.0
+    tf32 = {"burst_tflops": None, "sustained_tflops": None, "how": "skipped"} if args.no_peak_probe else measure_tf32_peak(device)
+    measured_peak = tf32["sustained_tflops"] / 3.0 if tf32["sustained_tflops"] else None
     rtn = torch.clamp(torch.round(w / scale), -8, 7) * scale
     objective_vs_rtn = synthetic.objective(z, w, g, h) / synthetic.objective(rtn, w, g, h)
     roofline = {

@@ -21,6 +21,10 @@
 //     the sub-tiles of the next sub-tile anti-diagonal.
 #include <type_traits>
 
+#ifndef G2D_ROLL
+#define G2D_ROLL 4  // rounding stages per iteration of the stage loop; 16 = the fully unrolled form
+#endif
+
 #include "g2d_common.cuh"
 
 namespace g2d {
@@ -129,6 +133,7 @@ __global__ void __launch_bounds__(TTH) tile_sweep_kernel(SweepArgs<F> P, int S, 
     F *LUs = Cs + TILE * LD;                  // strict lower part: L[I, I]; strict upper part: U[J, J]
     F *Dg = LUs + TILE * LD;                  // [2][NSUB] zero-padded diagonal blocks: L[a, a] and U[b, b]^T, strictly lower
     F *Zs = Dg + 2 * NSUB * DBLK;             // the rounded values, written out in one coalesced pass at the end
+    F *Ps = Zs + TILE * LD;                   // [3][SUB][64]: quantizer parameters of the sweeping lanes, by register number
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int k = lane & 15, half = lane >> 4;
@@ -388,8 +393,90 @@ __global__ void __launch_bounds__(TTH) tile_sweep_kernel(SweepArgs<F> P, int S, 
                         }
                     }
                 };
-                if (fast_division) stages(std::true_type{});
-                else stages(std::false_type{});
+                // The same stages as a loop over groups of ROLL stages.  The fully unrolled form above is 25 KB of
+                // straight-line code per pass that no instruction cache level close to the scheduler holds (a quarter
+                // of the sweeping warps' stall samples were "no instruction"); here the registers are renamed by moving
+                // them ROLL places after every group, the quantizer parameters wait in shared memory by register number,
+                // and the loop body is ROLL stages long.
+                auto stages_rolled = [&](auto fast_tag) {
+                    constexpr bool FASTDIV = decltype(fast_tag)::value;
+                    constexpr int ROLL = G2D_ROLL;
+                    if (KIND != G2D_Q_ROUND) {
+#pragma unroll
+                        for (int r = 0; r < SUB; ++r) {
+                            Ps[(0 * SUB + r) * 64 + tid] = sc[r];
+                            if (KIND == G2D_Q_AFFINE) {
+                                Ps[(1 * SUB + r) * 64 + tid] = zp[r];
+                                Ps[(2 * SUB + r) * 64 + tid] = rc[r];
+                            }
+                        }
+                    }
+                    const unsigned valid_bits = valid;
+#pragma unroll 1
+                    for (int group = 0; group < 2 * SUB / ROLL; ++group) {
+                        const int s_first = group * ROLL;
+#pragma unroll
+                        for (int j = 0; j < ROLL; ++j) {
+                            const int s = s_first + j, r = s & (SUB - 1);
+                            const int p = s - k;
+                            const bool active = tile_ok && p >= 0 && p < SUB;
+                            const int pw = p & (SUB - 1);
+                            const F yrow = __shfl_sync(0xffffffffu, yacc[j], pw, SUB);
+                            const F yv = yrow + cacc[j];
+                            const bool ok = active && ((valid_bits >> r) & 1u);
+                            F z;
+                            if (KIND == G2D_Q_AFFINE) {
+                                const F scv = Ps[(0 * SUB + r) * 64 + tid], zpv = Ps[(1 * SUB + r) * 64 + tid];
+                                z = FASTDIV ? affine_value_rcp(yv, scv, zpv, Ps[(2 * SUB + r) * 64 + tid], P.qmin, P.qmax) : affine_value(yv, scv, zpv, P.qmin, P.qmax);
+                            } else if (KIND == G2D_Q_FORCED) {
+                                z = Ps[(0 * SUB + r) * 64 + tid];
+                            } else {
+                                z = rint_even(yv);
+                            }
+                            const F ev = ok ? z - yv : (F)0;
+                            const F cc = cacc[j] + ev;
+                            const F ccrow = __shfl_sync(0xffffffffu, cc, pw, SUB);
+                            if (active) {
+                                Ys[entry0 + s * LD] = ev;
+                                Cs[entry0 + s * LD] = cc;
+                                Zs[entry0 + s * LD] = z;
+                            }
+                            if (ok && pre_ptr) pre_ptr[(int64_t)s * n] = yv;
+                            const F vcol = active ? ev : (F)0, vrow = active ? ccrow : (F)0;
+                            F kl[SUB], ku[SUB];
+#pragma unroll
+                            for (int v4 = 0; v4 < SUB; v4 += 4) {
+                                F t[4];
+                                load4(dgl + pw * DLD + v4, t);
+#pragma unroll
+                                for (int x = 0; x < 4; ++x) kl[v4 + x] = t[x];
+                                load4(dgu + pw * DLD + v4, t);
+#pragma unroll
+                                for (int x = 0; x < 4; ++x) ku[v4 + x] = t[x];
+                            }
+#pragma unroll
+                            for (int dd = 1; dd < SUB; ++dd) {
+                                cacc[(j + dd) & (SUB - 1)] += kl[dd] * vcol;
+                                yacc[(j + dd) & (SUB - 1)] += ku[dd] * vrow;
+                            }
+                        }
+                        // rename: what was register i + ROLL is register i from here on
+                        F keep_c[ROLL], keep_y[ROLL];
+#pragma unroll
+                        for (int i = 0; i < ROLL; ++i) { keep_c[i] = cacc[i]; keep_y[i] = yacc[i]; }
+#pragma unroll
+                        for (int i = 0; i < SUB - ROLL; ++i) { cacc[i] = cacc[i + ROLL]; yacc[i] = yacc[i + ROLL]; }
+#pragma unroll
+                        for (int i = 0; i < ROLL; ++i) { cacc[SUB - ROLL + i] = keep_c[i]; yacc[SUB - ROLL + i] = keep_y[i]; }
+                    }
+                };
+                if (G2D_ROLL < SUB) {
+                    if (fast_division) stages_rolled(std::true_type{});
+                    else stages_rolled(std::false_type{});
+                } else {
+                    if (fast_division) stages(std::true_type{});
+                    else stages(std::false_type{});
+                }
                 // fetch the parameters of this half-warp's next sub-tile while the updates run.  Both half-warps make the
                 // call (it ends in a warp-wide vote); one without a next sub-tile fetches a valid dummy and stays masked
                 const int bn = w + 1 - sub_a;
@@ -502,7 +589,7 @@ template <typename F, int KIND>
 static int launch_kind(const SweepArgs<F> &args, int S, int parity, cudaStream_t stream) {
     // the opt-in to more than 48 KB of dynamic shared memory is per device
     static PerDeviceOnce configured;
-    const size_t smem = sizeof(F) * (4 * TILE * LD + 2 * NSUB * DBLK);
+    const size_t smem = sizeof(F) * (4 * TILE * LD + 2 * NSUB * DBLK + 3 * SUB * 64);
     if (configured.run([&] { return cudaFuncSetAttribute(tile_sweep_kernel<F, KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess; }) != G2D_OK)
         return G2D_ERR_CUDA;
     const int i_lo = S - args.nJ + 1 > 0 ? S - args.nJ + 1 : 0;

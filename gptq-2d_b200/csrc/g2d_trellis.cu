@@ -538,25 +538,25 @@ static int launch_viterbi_indexed(int64_t rows, int T, const void *x, const void
     return check_launch();
 }
 
-// The indexed search serves tables of up to 2^16 states whose distinct rows fit shared memory beside the group minima.
+// The indexed search serves tables of up to 2^16 states whose distinct rows fit shared memory beside the group minima, and
+// only calls of at most one sequence per SM.  Measured on B200 (HYB, L = 16, T = 256): 148 sequences take 1.58 ms against
+// 1.87 ms for the search that reads the table from L2, but with two sequences per CTA the random look-ups of the local
+// costs collide in the shared-memory banks (256 sequences: 3.6 ms against 2.6 ms; 4096: 49 ms against 30 ms), so larger
+// calls keep the other kernel.
 template <typename F>
 static int indexed_sequences_per_cta(const TrellisIndex *index, int64_t rows, int L, int K, int V) {
     if (index == nullptr || index->ids == nullptr || index->distinct == nullptr || index->count <= 0) return 0;
     const int64_t S = (int64_t)1 << L, G = S >> (K * V);
-    if (L > 16 || G < 8 || S < 8) return 0;
-    auto bytes = [&](int R) { return (size_t)S * 2 + sizeof(F) * (2 * R * (size_t)G + (size_t)R * index->count); };
-    const size_t budget = 216 * 1024;
-    if (rows > 148 && bytes(2) <= budget) return 2;
-    return bytes(1) <= budget ? 1 : 0;
+    if (L > 16 || G < 8 || S < 8 || rows > 148) return 0;
+    const size_t bytes = (size_t)S * 2 + sizeof(F) * (2 * (size_t)G + (size_t)index->count);
+    return bytes <= 216 * 1024 ? 1 : 0;
 }
 
 int launch_trellis(int dtype, int64_t rows, int T, const void *x, const void *table, int L, int K, int V, int tail, const void *scale,
                    void *out, int64_t *states, void *workspace, uint8_t *codes, cudaStream_t st, const TrellisIndex *index) {
     const int64_t code_bytes = trellis_code_bytes(T, L, K, V, tail);
     const int R = dtype == G2D_F32 ? indexed_sequences_per_cta<float>(index, rows, L, K, V) : indexed_sequences_per_cta<double>(index, rows, L, K, V);
-    if (R == 2 && dtype == G2D_F32) return launch_viterbi_indexed<float, 2>(rows, T, x, table, *index, L, K, V, tail, scale, out, states, workspace, codes, code_bytes, st);
     if (R == 1 && dtype == G2D_F32) return launch_viterbi_indexed<float, 1>(rows, T, x, table, *index, L, K, V, tail, scale, out, states, workspace, codes, code_bytes, st);
-    if (R == 2) return launch_viterbi_indexed<double, 2>(rows, T, x, table, *index, L, K, V, tail, scale, out, states, workspace, codes, code_bytes, st);
     if (R == 1) return launch_viterbi_indexed<double, 1>(rows, T, x, table, *index, L, K, V, tail, scale, out, states, workspace, codes, code_bytes, st);
     return dtype == G2D_F32 ? trellis_dispatch<float>(rows, T, x, table, L, K, V, tail, scale, out, states, workspace, codes, code_bytes, st)
                             : trellis_dispatch<double>(rows, T, x, table, L, K, V, tail, scale, out, states, workspace, codes, code_bytes, st);
