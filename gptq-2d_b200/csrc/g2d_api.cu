@@ -168,7 +168,7 @@ int sweep_macro(const g2d_sweep_desc *d, SweepArgs<F> &a, BandArgs<F> &b64, cuda
 // capturable): during capture, a device whose lanes do not exist yet gets G2D_ERR_UNSUPPORTED.
 struct PipeLane {
     cudaStream_t tiles = nullptr, near = nullptr, far = nullptr;  // in falling priority
-    cudaEvent_t swept[8] = {}, near_done[8] = {}, far_done[4] = {}, fork = nullptr, join = nullptr;
+    cudaEvent_t swept[8] = {}, near_done[8] = {}, far_first[4] = {}, far_done[4] = {}, fork = nullptr, join = nullptr;
     std::mutex busy;
 };
 struct DeviceLanes {
@@ -184,6 +184,7 @@ void destroy_lane(PipeLane &l) {
     auto drop = [](cudaEvent_t &e) { if (e) { cudaEventDestroy(e); e = nullptr; } };
     for (auto &e : l.swept) drop(e);
     for (auto &e : l.near_done) drop(e);
+    for (auto &e : l.far_first) drop(e);
     for (auto &e : l.far_done) drop(e);
     drop(l.fork);
     drop(l.join);
@@ -202,7 +203,9 @@ bool build_lane(PipeLane &l) {
     for (int k = 0; k < 8 && ok; ++k)
         ok = cudaEventCreateWithFlags(&l.swept[k], cudaEventDisableTiming) == cudaSuccess &&
              cudaEventCreateWithFlags(&l.near_done[k], cudaEventDisableTiming) == cudaSuccess;
-    for (int k = 0; k < 4 && ok; ++k) ok = cudaEventCreateWithFlags(&l.far_done[k], cudaEventDisableTiming) == cudaSuccess;
+    for (int k = 0; k < 4 && ok; ++k)
+        ok = cudaEventCreateWithFlags(&l.far_first[k], cudaEventDisableTiming) == cudaSuccess &&
+             cudaEventCreateWithFlags(&l.far_done[k], cudaEventDisableTiming) == cudaSuccess;
     return ok;
 }
 
@@ -274,7 +277,10 @@ constexpr int kFarLagMacro = 2;  // a far update reaches the macro anti-diagonal
 //   * far update of a group of macro anti-diagonals (128 x 128 macro tiles = 2 x 2 tiles; rank 512 by default), on a
 //     second side stream, into planes of its own that a tile adds when it loads.  It reaches the macro anti-diagonals
 //     from kFarLagMacro past the group's end, which the tile launches get to four launches after the group's last
-//     tile; the near updates stop where the far update of their source's group starts.
+//     tile; the near updates stop where the far update of their source's group starts.  A far update runs as two
+//     launches: first the macro anti-diagonals that the tile launches reach before the next group's update (a few
+//     hundred macro tiles: short, and the only part the tile launches have to wait for soon), then everything beyond
+//     them, which the tile launches only need a whole group later.
 // The tile launches run on a stream of the library's own with the highest priority, the near updates below it, the far
 // updates lowest: a CTA slot that frees up goes to the critical path first.  Updates that share target planes are
 // ordered on one stream, so the additions have a fixed order.
@@ -301,8 +307,10 @@ int sweep_pipelined(const g2d_sweep_desc *d, SweepArgs<float> &a, const TcPlanes
         // what the tiles of s need: every near update up to s - 2, and the far update whose first targets they are
         if (s >= 2 && last_near >= s - 2 && cudaStreamWaitEvent(stream, lane->near_done[(s - 2) & 7], 0) != cudaSuccess) return G2D_ERR_CUDA;
         if (s % 2 == 0 && s / 2 - kFarLagMacro > 0 && (s / 2 - kFarLagMacro) % outer == 0) {
-            const int gf = (s / 2 - kFarLagMacro) / outer - 1;  // the group that ended kFarLagMacro macro anti-diagonals ago
-            if (last_far >= gf && cudaStreamWaitEvent(stream, lane->far_done[gf & 3], 0) != cudaSuccess) return G2D_ERR_CUDA;
+            // the group that ended kFarLagMacro macro anti-diagonals ago: the first part of its update; the group before it: the rest
+            const int gf = (s / 2 - kFarLagMacro) / outer - 1;
+            if (last_far >= gf && cudaStreamWaitEvent(stream, lane->far_first[gf & 3], 0) != cudaSuccess) return G2D_ERR_CUDA;
+            if (gf >= 1 && last_far >= gf - 1 && cudaStreamWaitEvent(stream, lane->far_done[(gf - 1) & 3], 0) != cudaSuccess) return G2D_ERR_CUDA;
         }
         if (timer) timer->begin_on(0, stream);
         status = launch_tile_sweep<float>(a, s, stream);
@@ -329,10 +337,18 @@ int sweep_pipelined(const g2d_sweep_desc *d, SweepArgs<float> &a, const TcPlanes
         if (feeds_far) {
             const int g = W1 / outer - 1;
             if (cudaStreamWaitEvent(lane->far, lane->swept[s & 7], 0) != cudaSuccess) return G2D_ERR_CUDA;
+            const int t_first = W1 + kFarLagMacro, t_split = t_first + outer < waves_macro ? t_first + outer : waves_macro;
             if (timer) timer->begin_on(2, lane->far);
-            status = launch_macro_update_tc(&far_maps, planes, yf, cf, d->m, d->n, W1 - outer, W1, waves_macro, lane->far, W1 + kFarLagMacro, 2);
+            status = launch_macro_update_tc(&far_maps, planes, yf, cf, d->m, d->n, W1 - outer, W1, t_split, lane->far, t_first, 2);
             if (timer) timer->end();
             if (status != G2D_OK) return status;
+            if (cudaEventRecord(lane->far_first[g & 3], lane->far) != cudaSuccess) return G2D_ERR_CUDA;
+            if (t_split < waves_macro) {
+                if (timer) timer->begin_on(2, lane->far);
+                status = launch_macro_update_tc(&far_maps, planes, yf, cf, d->m, d->n, W1 - outer, W1, waves_macro, lane->far, t_split, 2);
+                if (timer) timer->end();
+                if (status != G2D_OK) return status;
+            }
             if (flops)
                 flops[2] += band_flops(d->m, d->n, W1 - outer, W1, waves_macro, MACRO) - band_flops(d->m, d->n, W1 - outer, W1, W1 + kFarLagMacro, MACRO);
             if (cudaEventRecord(lane->far_done[g & 3], lane->far) != cudaSuccess) return G2D_ERR_CUDA;

@@ -9,21 +9,21 @@
 //   * the host launches one grid per tile anti-diagonal; the tiles of one anti-diagonal are
 //     independent, all feedback from earlier tiles is already in Y (right) and C (down);
 //   * inside the CTA the tile lives in shared memory; the 16 x 16 sub-tiles are taken on a sub-tile wavefront: the
-//     up to four sub-tiles of one sub-tile anti-diagonal are swept in registers by the four half-warps of warps 0 and 1,
-//     then all warps apply the finished sub-tiles' feedback to the rest of the tile as small dense products;
+//     up to four sub-tiles of one sub-tile anti-diagonal are swept in registers by the four half-warps of warps 0 and 1.
+//     These two warps are the critical path of the whole sweep and do nothing but the rounding stages: four helper
+//     warps, one per sub-tile row, carry everything else while a sub-tile anti-diagonal is swept (the quantizer
+//     parameters of the next one, the feedback of finished sub-tiles into sub-tiles two or more anti-diagonals ahead,
+//     the feedback of the neighbour tiles) and, between two sweeps, the one product pair per sub-tile that cannot
+//     be formed earlier: the feedback of the anti-diagonal just swept into the next one;
 //   * inside a sub-tile lane k of the half-warp owns column k (the down feedback, "C") and row k (the right feedback,
 //     "Y"), both skewed so that the entries of anti-diagonal s sit in register s mod 16 of every lane: the stage loop
-//     is fully unrolled and indexes registers statically; two shuffles per stage exchange the row accumulator and the
-//     completed C with the partner lane.  The feedback coefficients of a sub-tile come from zero-padded copies of the
-//     diagonal blocks of L and U^T, so the pushes need no bounds predicates: out-of-range pushes multiply by zero;
+//     runs in groups of ROLL stages that index registers statically, and the registers are renamed by moving them
+//     after every group; two shuffles per stage exchange the row accumulator and the completed C with the partner
+//     lane.  The feedback coefficients of a sub-tile come from zero-padded copies of the diagonal blocks of L and
+//     U^T, so the pushes need no bounds predicates: out-of-range pushes multiply by zero;
 //   * pipelined schedule: a tile also adds the far-feedback planes as it loads and applies the feedback of its two
-//     neighbours of the previous tile anti-diagonal itself; warps 2 and 3, idle during a sub-tile sweep, do that for
-//     the sub-tiles of the next sub-tile anti-diagonal.
+//     neighbours of the previous tile anti-diagonal itself (the helper warps, one sub-tile anti-diagonal ahead).
 #include <type_traits>
-
-#ifndef G2D_ROLL
-#define G2D_ROLL 4  // rounding stages per iteration of the stage loop; 16 = the fully unrolled form
-#endif
 
 #include "g2d_common.cuh"
 
@@ -34,7 +34,11 @@ namespace g2d {
 // block's end.  A lane fetches its row with four 16-byte loads; a row stride of 20 keeps eight lanes on distinct banks.
 constexpr int DLD = SUB + 4;            // row stride
 constexpr int DBLK = SUB * DLD;         // elements per block
-constexpr int TTH = NSUB * 32;          // threads per CTA
+constexpr int ROLL = 4;                 // rounding stages per iteration of the stage loop
+constexpr int SWEEPERS = NSUB / 2;      // warps that sweep: one half-warp per sub-tile row
+constexpr int HELPERS = NSUB;           // warps that feed them: one per sub-tile row
+constexpr int TTH = (SWEEPERS + HELPERS) * 32;  // threads per CTA
+constexpr int LANES = SWEEPERS * 32;    // sweeping lanes
 
 template <typename F>
 __device__ __forceinline__ void load4(const F *p, F (&v)[4]);
@@ -62,7 +66,7 @@ __device__ __forceinline__ void store4<double>(double *p, const double (&v)[4]) 
 
 template <typename F>
 __device__ __forceinline__ void mm16(F *__restrict__ D, const F *__restrict__ A, const F *__restrict__ B, int lane) {
-    // D[16x16] += A[16x16] * B[16x16], all in shared memory with row stride LD; 2 x 4 outputs per lane.
+    // D[16x16] += A[16x16] * B[16x16], all in shared memory with row stride LD; one warp, 2 x 4 outputs per lane
     const int r = (lane >> 2) * 2, c = (lane & 3) * 4;
     F d0[4], d1[4];
     load4(D + r * LD + c, d0);
@@ -87,6 +91,22 @@ __device__ __forceinline__ void mm16(F *__restrict__ D, const F *__restrict__ A,
     store4(D + (r + 1) * LD + c, d1);
 }
 
+// The one or two products that carry finished sub-tiles into sub-tile (ap, bp): the errors of (as, bp) down through
+// L[ap, as] into C, then the completed C of (ap, bs) right through U[bs, bp] into Y; a source index outside 0 .. NSUB - 1
+// means there is no such source.  One warp; a loop, so that the product's code exists once per call site.
+template <typename F>
+__device__ __forceinline__ void carry_into(F *Ys, F *Cs, const F *LUs, int ap, int bp, int as, int bs, int lane) {
+#pragma unroll 1
+    for (int prod = 0; prod < 2; ++prod) {
+        const int src = prod == 0 ? as : bs;
+        if (src < 0 || src >= NSUB) continue;
+        F *D = (prod == 0 ? Cs : Ys) + ap * SUB * LD + bp * SUB;
+        const F *A = prod == 0 ? LUs + ap * SUB * LD + src * SUB : Cs + ap * SUB * LD + src * SUB;
+        const F *B = prod == 0 ? Ys + src * SUB * LD + bp * SUB : LUs + src * SUB * LD + bp * SUB;
+        mm16(D, A, B, lane);
+    }
+}
+
 // Feedback of a neighbour tile into one 16 x 16 sub-tile, for a group of 16 threads (t = 0..15): thread t forms the
 // 4 x 4 patch at rows 4 (t / 4), columns 4 (t % 4) of  A[16 x K] B[K x 16]  over k = k0 .. k0 + kn - 1 and returns it
 // in acc.  A and B are row-major in global memory (written by an earlier launch, or constant); A points at the
@@ -100,7 +120,7 @@ __device__ __forceinline__ void neighbour_patch(F (&acc)[4][4], const F *__restr
     for (int x = 0; x < 4; ++x)
 #pragma unroll
         for (int y = 0; y < 4; ++y) acc[x][y] = (F)0;
-#pragma unroll 2
+#pragma unroll(sizeof(F) == sizeof(float) ? 4 : 2)
     for (int k = k0; k < k0 + kn; k += 4) {
         F a[4][4], b[4][4];
 #pragma unroll
@@ -133,7 +153,8 @@ __global__ void __launch_bounds__(TTH) tile_sweep_kernel(SweepArgs<F> P, int S, 
     F *LUs = Cs + TILE * LD;                  // strict lower part: L[I, I]; strict upper part: U[J, J]
     F *Dg = LUs + TILE * LD;                  // [2][NSUB] zero-padded diagonal blocks: L[a, a] and U[b, b]^T, strictly lower
     F *Zs = Dg + 2 * NSUB * DBLK;             // the rounded values, written out in one coalesced pass at the end
-    F *Ps = Zs + TILE * LD;                   // [3][SUB][64]: quantizer parameters of the sweeping lanes, by register number
+    F *Ps = Zs + TILE * LD;                   // [3][SUB][LANES]: quantizer parameters of the sweeping lanes, by register number
+    unsigned *Pv = reinterpret_cast<unsigned *>(Ps + 3 * SUB * LANES);  // [2][LANES] registers holding entries inside the matrix, one word per half of the registers; [2][SWEEPERS] reciprocal division allowed
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int k = lane & 15, half = lane >> 4;
@@ -141,6 +162,8 @@ __global__ void __launch_bounds__(TTH) tile_sweep_kernel(SweepArgs<F> P, int S, 
     const int64_t i0 = (int64_t)I * TILE, j0 = (int64_t)J * TILE;
     const int64_t m = P.m, n = P.n;
     const bool full = i0 + TILE <= m && j0 + TILE <= n;
+    const bool sweeper = warp < SWEEPERS;
+    const int helper = warp - SWEEPERS;  // 0 .. HELPERS - 1 for the helper warps: the sub-tile row the warp feeds
 
     for (int64_t batch = blockIdx.y; batch < P.batch; batch += gridDim.y) {
         F *yg = P.y + batch * m * n, *cg = P.c + batch * m * n, *eg = P.e + batch * m * n;
@@ -152,18 +175,97 @@ __global__ void __launch_bounds__(TTH) tile_sweep_kernel(SweepArgs<F> P, int S, 
         F *pre = P.y_pre ? P.y_pre + batch * m * n : nullptr;
         const F *yfg = P.yf ? P.yf + batch * m * n : nullptr, *cfg = P.yf ? P.cf + batch * m * n : nullptr;
 
+        // ---- quantizer parameters, prepared by the helper warps ----
+        // Helper warp h prepares, for the sweeping lane of its own lane number in sweeping warp h mod SWEEPERS, half
+        // h / SWEEPERS of that lane's registers: register r holds entry ((r - k) mod 16, k) of the lane's sub-tile.
+        // Scale, zero point and, for the float affine quantizer, the refined reciprocal of the scale (see
+        // affine_value_rcp) wait in shared memory by register number, with the bits that say which registers hold
+        // entries inside the matrix and the warp-wide decision whether every scale is in the range where the reciprocal
+        // form of the division is safe.  The loads are issued one sub-tile anti-diagonal ahead and travel while the
+        // helper does its other work.
+        constexpr int PR = SUB / (HELPERS / SWEEPERS);  // registers per helper lane
+        F sc[PR], zp[PR], rc[PR];
+        bool pfast = true;
+        unsigned pvalid = 0;
+        const int p_warp = helper & (SWEEPERS - 1), p_part = helper / SWEEPERS;  // helpers only
+        const int p_lane = p_warp * 32 + lane;
+        const int p_a = 2 * p_warp + half;  // sub-tile row of the lane prepared for
+        auto fetch_params = [&](int w_next) {
+            const int b_raw = w_next - p_a;
+            const int b = b_raw >= 0 && b_raw < NSUB ? b_raw : 0;  // a half-warp without a sub-tile gets valid dummies and stays masked
+            const int r0 = p_a * SUB, c0 = b * SUB;
+            unsigned bits = 0;
+#pragma unroll
+            for (int x = 0; x < PR; ++x) {
+                const int r = p_part * PR + x, o = (r - k) & (SUB - 1);
+                const int64_t gi = i0 + r0 + o, gj = j0 + c0 + k;
+                const bool in = full || (gi < m && gj < n);
+                bits |= in ? (1u << r) : 0u;
+                // entries outside the matrix load a value from inside it (no select waits on the load here) and get
+                // their neutral parameters in finish_params
+                const int64_t ci = gi < m ? gi : m - 1, cj = gj < n ? gj : n - 1;
+                if (KIND == G2D_Q_AFFINE) {
+                    sc[x] = sg[ci * P.srs + cj * P.scs];
+                    zp[x] = zg[ci * P.zrs + cj * P.zcs];
+                } else if (KIND == G2D_Q_FORCED) {
+                    sc[x] = fg[ci * n + cj];
+                }
+            }
+            pvalid = bits;
+        };
+        auto finish_params = [&]() {
+#pragma unroll
+            for (int x = 0; x < PR; ++x) {
+                const bool in = (pvalid >> (p_part * PR + x)) & 1u;
+                if (KIND == G2D_Q_AFFINE) {
+                    sc[x] = in ? sc[x] : (F)1;
+                    zp[x] = in ? zp[x] : (F)0;
+                } else if (KIND == G2D_Q_FORCED) {
+                    sc[x] = in ? sc[x] : (F)0;
+                }
+            }
+            if (KIND == G2D_Q_AFFINE && sizeof(F) == sizeof(float)) {
+                bool normal = true;
+#pragma unroll
+                for (int x = 0; x < PR; ++x) {
+                    const float sv = (float)sc[x], av = fabsf(sv);
+                    normal = normal && av > 1e-18f && av < 1e18f;
+                    float v = __frcp_rn(sv);
+                    v = fmaf(fmaf(-sv, v, 1.f), v, v);  // one Newton step: the reciprocal to within half an ulp
+                    rc[x] = (F)v;
+                }
+                pfast = __all_sync(0xffffffffu, normal);
+            }
+        };
+        auto store_params = [&]() {
+#pragma unroll
+            for (int x = 0; x < PR; ++x) {
+                const int r = p_part * PR + x;
+                if (KIND != G2D_Q_ROUND) Ps[(0 * SUB + r) * LANES + p_lane] = sc[x];
+                if (KIND == G2D_Q_AFFINE) {
+                    Ps[(1 * SUB + r) * LANES + p_lane] = zp[x];
+                    Ps[(2 * SUB + r) * LANES + p_lane] = rc[x];
+                }
+            }
+            Pv[p_part * LANES + p_lane] = pvalid;
+            if (lane == 0) Pv[2 * LANES + p_part * SWEEPERS + p_warp] = pfast ? 1u : 0u;
+        };
+        if (!sweeper) fetch_params(0);
+
         // ---- load the tile; all global loads of a pass are issued before its shared-memory stores ----
         const bool vec = full && (n % 4 == 0) && (m % 4 == 0) &&
                          ((reinterpret_cast<uintptr_t>(yg) | reinterpret_cast<uintptr_t>(cg) | reinterpret_cast<uintptr_t>(eg) |
                            reinterpret_cast<uintptr_t>(lg) | reinterpret_cast<uintptr_t>(ug)) % (4 * sizeof(F)) == 0);
         if (vec) {
-            constexpr int PER = TILE * TILE / 4 / TTH;  // vectors per thread and array
+            constexpr int VECS = TILE * TILE / 4;              // vectors per array
+            constexpr int PER = (VECS + TTH - 1) / TTH;        // per thread, the last one partly
 #pragma unroll
             for (int pass = 0; pass < 2; ++pass) {
                 F va[PER][4], vb[PER][4];
 #pragma unroll
                 for (int t = 0; t < PER; ++t) {
                     const int idx = t * TTH + tid, r = idx / (TILE / 4), c = (idx % (TILE / 4)) * 4;
+                    if (idx >= VECS) continue;
                     if (pass == 0) {
                         load4(yg + (i0 + r) * n + j0 + c, va[t]);
                         load4(cg + (i0 + r) * n + j0 + c, vb[t]);
@@ -178,20 +280,24 @@ __global__ void __launch_bounds__(TTH) tile_sweep_kernel(SweepArgs<F> P, int S, 
 #pragma unroll
                     for (int t = 0; t < PER; ++t) {
                         const int idx = t * TTH + tid, r = idx / (TILE / 4), c = (idx % (TILE / 4)) * 4;
+                        if (idx >= VECS) continue;
                         load4(yfg + (i0 + r) * n + j0 + c, fa[t]);
                         load4(cfg + (i0 + r) * n + j0 + c, fb[t]);
                     }
 #pragma unroll
-                    for (int t = 0; t < PER; ++t)
+                    for (int t = 0; t < PER; ++t) {
+                        if (t * TTH + tid >= VECS) continue;
 #pragma unroll
                         for (int x = 0; x < 4; ++x) {
                             va[t][x] += fa[t][x];
                             vb[t][x] += fb[t][x];
                         }
+                    }
                 }
 #pragma unroll
                 for (int t = 0; t < PER; ++t) {
                     const int idx = t * TTH + tid, r = idx / (TILE / 4), c = (idx % (TILE / 4)) * 4;
+                    if (idx >= VECS) continue;
                     if (pass == 0) {
                         store4(Ys + r * LD + c, va[t]);
                         store4(Cs + r * LD + c, vb[t]);
@@ -211,7 +317,7 @@ __global__ void __launch_bounds__(TTH) tile_sweep_kernel(SweepArgs<F> P, int S, 
                 for (int t = 0; t < UN; ++t) {
                     const int idx = base + t * TTH + tid, r = idx / TILE, c = idx % TILE;
                     const int64_t gi = i0 + r, gj = j0 + c;
-                    const bool in = gi < m && gj < n;
+                    const bool in = idx < TILE * TILE && gi < m && gj < n;
                     vy[t] = in ? yg[gi * n + gj] : (F)0;
                     vc[t] = in ? cg[gi * n + gj] : (F)0;
                     if (in && yfg != nullptr) {
@@ -219,15 +325,18 @@ __global__ void __launch_bounds__(TTH) tile_sweep_kernel(SweepArgs<F> P, int S, 
                         vc[t] += cfg[gi * n + gj];
                     }
                     vl[t] = (F)0;
-                    if (r > c) {
-                        if (gi < m) vl[t] = lg[gi * m + i0 + c];
-                    } else if (r < c) {
-                        if (gj < n) vl[t] = ug[(j0 + r) * n + gj];
+                    if (idx < TILE * TILE) {
+                        if (r > c) {
+                            if (gi < m) vl[t] = lg[gi * m + i0 + c];
+                        } else if (r < c) {
+                            if (gj < n) vl[t] = ug[(j0 + r) * n + gj];
+                        }
                     }
                 }
 #pragma unroll
                 for (int t = 0; t < UN; ++t) {
                     const int idx = base + t * TTH + tid, r = idx / TILE, c = idx % TILE;
+                    if (idx >= TILE * TILE) continue;
                     Ys[r * LD + c] = vy[t];
                     Cs[r * LD + c] = vc[t];
                     LUs[r * LD + c] = vl[t];
@@ -237,9 +346,9 @@ __global__ void __launch_bounds__(TTH) tile_sweep_kernel(SweepArgs<F> P, int S, 
         __syncthreads();
         // Pipelined schedule: the feedback of the two tiles finished one launch ago, which no update kernel has carried yet:
         //     C[I, J] += L[I, I - 1] E[I - 1, J],      Y[I, J] += C[I, J - 1] U[J - 1, J]  (the completed C of the left neighbour).
-        // Only the first sub-tile needs it before the sweep starts (here, all threads: eight groups of 16 split the two
+        // Only the first sub-tile needs it before the sweep starts (here: eight groups of 16 threads split the two
         // products and four quarters of k, partial patches are summed in a fixed order through shared memory); the
-        // sub-tiles of a later sub-tile anti-diagonal get theirs from the two warps that idle while the one before is swept.
+        // sub-tiles of a later sub-tile anti-diagonal get theirs from the helper warps while the one before is swept.
         const int nb_rows = (int)(m - i0 < TILE ? m - i0 : TILE), nb_cols = (int)(n - j0 < TILE ? n - j0 : TILE);
         const F *const nb_a[2] = {lg + i0 * m + (i0 - TILE), cg + i0 * n + (j0 - TILE)};       // A operands: L block, left C
         const F *const nb_b[2] = {eg + (i0 - TILE) * n + j0, ug + (j0 - TILE) * n + j0};       // B operands: upper E, U block
@@ -248,7 +357,7 @@ __global__ void __launch_bounds__(TTH) tile_sweep_kernel(SweepArgs<F> P, int S, 
         if (P.neighbours) {
             const int group = tid >> 4, t = tid & 15, prod = group & 1, quarter = group >> 1;
             F acc[4][4];
-            if (nb_on[prod]) {
+            if (group < 8 && nb_on[prod]) {
                 neighbour_patch<F>(acc, nb_a[prod], nb_lda[prod], nb_b[prod], n, t, quarter * (TILE / 4), TILE / 4, nb_rows, nb_cols, vec);
 #pragma unroll
                 for (int x = 0; x < 4; ++x)
@@ -266,7 +375,6 @@ __global__ void __launch_bounds__(TTH) tile_sweep_kernel(SweepArgs<F> P, int S, 
                     *dst = sum;
                 }
             }
-            __syncthreads();
         }
         for (int idx = tid; idx < 2 * NSUB * DBLK; idx += TTH) {
             const int which = idx / (NSUB * DBLK), blk = idx / DBLK % NSUB, p = idx % DBLK / DLD, dd = idx % DLD;
@@ -274,6 +382,10 @@ __global__ void __launch_bounds__(TTH) tile_sweep_kernel(SweepArgs<F> P, int S, 
             if (dd >= 1 && dd < SUB && p + dd < SUB)
                 v = which == 0 ? LUs[(blk * SUB + p + dd) * LD + blk * SUB + p] : LUs[(blk * SUB + p) * LD + blk * SUB + p + dd];
             Dg[idx] = v;
+        }
+        if (!sweeper) {
+            finish_params();
+            store_params();
         }
         __syncthreads();
 
@@ -283,56 +395,16 @@ __global__ void __launch_bounds__(TTH) tile_sweep_kernel(SweepArgs<F> P, int S, 
         // anti-diagonal s sit in register s mod 16.  At stage s lane k rounds its column's entry (p, k), p = s - k; the
         // lane that owns row p is lane p, and lane p in turn rounds (k, p), the entry of this lane's row: the two lanes
         // exchange the row accumulator before rounding and the completed C after it.
-        F sc[SUB], zp[SUB];  // quantizer parameters of this lane's column entries, register r holds entry ((r - k) mod 16, k)
-        F rc[SUB];           // float affine only: refined reciprocals of the scales, see affine_value_rcp
-        bool fast_division = false;
-        bool have_params = false;
-        unsigned valid = 0xFFFFu;  // bit r: the entry held in register r lies inside the matrix
-        const int sub_a = 2 * warp + half;  // sub-tile row of this half-warp (warps 0 and 1 only)
-
-        auto fetch_params = [&](int b) {
-            const int r0 = sub_a * SUB, c0 = b * SUB;
-            unsigned bits = 0;
-#pragma unroll
-            for (int r = 0; r < SUB; ++r) {
-                const int o = (r - k) & (SUB - 1);
-                const int64_t gi = i0 + r0 + o, gj = j0 + c0 + k;
-                const bool in = full || (gi < m && gj < n);
-                bits |= in ? (1u << r) : 0u;
-                if (KIND == G2D_Q_AFFINE) {
-                    sc[r] = in ? sg[gi * P.srs + gj * P.scs] : (F)1;
-                    zp[r] = in ? zg[gi * P.zrs + gj * P.zcs] : (F)0;
-                } else if (KIND == G2D_Q_FORCED) {
-                    sc[r] = in ? fg[gi * n + gj] : (F)0;
-                }
-            }
-            valid = bits;
-        };
-        // second half of the fetch, run when the loads above have had an update phase to land: reciprocals and the
-        // warp-wide decision whether every scale is in the range where the reciprocal form of the division is safe
-        auto finish_params = [&]() {
-            if (KIND == G2D_Q_AFFINE && sizeof(F) == sizeof(float)) {
-                bool normal = true;
-#pragma unroll
-                for (int r = 0; r < SUB; ++r) {
-                    const float sv = (float)sc[r], av = fabsf(sv);
-                    normal = normal && av > 1e-18f && av < 1e18f;
-                    float x = __frcp_rn(sv);
-                    x = fmaf(fmaf(-sv, x, 1.f), x, x);  // one Newton step: the reciprocal to within half an ulp
-                    rc[r] = (F)x;
-                }
-                fast_division = __all_sync(0xffffffffu, normal);
-            }
-        };
-
         for (int w = 0; w < 2 * NSUB - 1; ++w) {
-            if (warp < 2) {
+            const bool more = w + 1 < 2 * NSUB - 1;
+            if (sweeper) {
+                const int sub_a = 2 * warp + half;
                 const int b_raw = w - sub_a;
                 const bool tile_ok = b_raw >= 0 && b_raw < NSUB;  // a half-warp without a sub-tile runs along with everything masked
                 const int b = tile_ok ? b_raw : 0;
                 const int r0 = sub_a * SUB, c0 = b * SUB;
-                if (!have_params) fetch_params(b);
-                finish_params();
+                const unsigned valid_bits = Pv[tid] | Pv[LANES + tid];
+                const bool fast_division = (Pv[2 * LANES + warp] & Pv[2 * LANES + SWEEPERS + warp]) != 0u;
                 F cacc[SUB], yacc[SUB];
 #pragma unroll
                 for (int r = 0; r < SUB; ++r) {
@@ -344,104 +416,43 @@ __global__ void __launch_bounds__(TTH) tile_sweep_kernel(SweepArgs<F> P, int S, 
                 const int entry0 = (r0 - k) * LD + c0 + k;
                 F *pre_ptr = pre ? pre + (i0 + r0 - k) * n + j0 + c0 + k : nullptr;
                 const F *const dgl = Dg + sub_a * DBLK, *const dgu = Dg + (NSUB + b) * DBLK;
+                // The 32 stages in groups of ROLL: inside a group the registers are indexed statically, after it they are
+                // renamed by moving them ROLL places, so that the loop body is ROLL stages long (the fully unrolled form
+                // is 25 KB of straight-line code per pass that no instruction cache level close to the scheduler holds).
                 auto stages = [&](auto fast_tag) {
                     constexpr bool FASTDIV = decltype(fast_tag)::value;
-#pragma unroll 1
-                    for (int pass = 0; pass < 2; ++pass) {
-                        const int s0 = pass * SUB;
-                        F *const e_ptr = Ys + entry0 + s0 * LD, *const c_ptr = Cs + entry0 + s0 * LD, *const z_ptr = Zs + entry0 + s0 * LD;
-#pragma unroll
-                        for (int r = 0; r < SUB; ++r) {
-                            const int p = s0 + r - k;  // row of this lane's column entry = column of its row entry = partner lane
-                            const bool active = tile_ok && p >= 0 && p < SUB;
-                            const int pw = p & (SUB - 1);
-                            const F yrow = __shfl_sync(0xffffffffu, yacc[r], pw, SUB);  // Y accumulator of (p, k) from the owner of row p
-                            const F yv = yrow + cacc[r];
-                            const bool ok = active && ((valid >> r) & 1u);
-                            F z;
-                            if (KIND == G2D_Q_AFFINE) z = FASTDIV ? affine_value_rcp(yv, sc[r], zp[r], rc[r], P.qmin, P.qmax) : affine_value(yv, sc[r], zp[r], P.qmin, P.qmax);
-                            else if (KIND == G2D_Q_FORCED) z = sc[r];
-                            else z = rint_even(yv);
-                            const F ev = ok ? z - yv : (F)0;
-                            const F cc = cacc[r] + ev;
-                            const F ccrow = __shfl_sync(0xffffffffu, cc, pw, SUB);  // completed C of (k, p), rounded by lane p
-                            if (active) {
-                                e_ptr[r * LD] = ev;
-                                c_ptr[r * LD] = cc;
-                                z_ptr[r * LD] = z;
-                            }
-                            if (ok && pre_ptr) pre_ptr[(int64_t)(s0 + r) * n] = yv;
-                            // pushes: the error down column k through L, the completed C of (k, p) right along row k through U;
-                            // rows past the block's end read the zero padding, inactive lanes push zero
-                            const F vcol = active ? ev : (F)0, vrow = active ? ccrow : (F)0;
-                            F kl[SUB], ku[SUB];
-#pragma unroll
-                            for (int v4 = 0; v4 < SUB; v4 += 4) {
-                                F t[4];
-                                load4(dgl + pw * DLD + v4, t);
-#pragma unroll
-                                for (int x = 0; x < 4; ++x) kl[v4 + x] = t[x];
-                                load4(dgu + pw * DLD + v4, t);
-#pragma unroll
-                                for (int x = 0; x < 4; ++x) ku[v4 + x] = t[x];
-                            }
-#pragma unroll
-                            for (int dd = 1; dd < SUB; ++dd) {
-                                cacc[(r + dd) & (SUB - 1)] += kl[dd] * vcol;
-                                yacc[(r + dd) & (SUB - 1)] += ku[dd] * vrow;
-                            }
-                        }
-                    }
-                };
-                // The same stages as a loop over groups of ROLL stages.  The fully unrolled form above is 25 KB of
-                // straight-line code per pass that no instruction cache level close to the scheduler holds (a quarter
-                // of the sweeping warps' stall samples were "no instruction"); here the registers are renamed by moving
-                // them ROLL places after every group, the quantizer parameters wait in shared memory by register number,
-                // and the loop body is ROLL stages long.
-                auto stages_rolled = [&](auto fast_tag) {
-                    constexpr bool FASTDIV = decltype(fast_tag)::value;
-                    constexpr int ROLL = G2D_ROLL;
-                    if (KIND != G2D_Q_ROUND) {
-#pragma unroll
-                        for (int r = 0; r < SUB; ++r) {
-                            Ps[(0 * SUB + r) * 64 + tid] = sc[r];
-                            if (KIND == G2D_Q_AFFINE) {
-                                Ps[(1 * SUB + r) * 64 + tid] = zp[r];
-                                Ps[(2 * SUB + r) * 64 + tid] = rc[r];
-                            }
-                        }
-                    }
-                    const unsigned valid_bits = valid;
 #pragma unroll 1
                     for (int group = 0; group < 2 * SUB / ROLL; ++group) {
                         const int s_first = group * ROLL;
 #pragma unroll
                         for (int j = 0; j < ROLL; ++j) {
                             const int s = s_first + j, r = s & (SUB - 1);
-                            const int p = s - k;
+                            const int p = s - k;  // row of this lane's column entry = column of its row entry = partner lane
                             const bool active = tile_ok && p >= 0 && p < SUB;
                             const int pw = p & (SUB - 1);
-                            const F yrow = __shfl_sync(0xffffffffu, yacc[j], pw, SUB);
+                            const F yrow = __shfl_sync(0xffffffffu, yacc[j], pw, SUB);  // Y accumulator of (p, k) from the owner of row p
                             const F yv = yrow + cacc[j];
                             const bool ok = active && ((valid_bits >> r) & 1u);
                             F z;
                             if (KIND == G2D_Q_AFFINE) {
-                                const F scv = Ps[(0 * SUB + r) * 64 + tid], zpv = Ps[(1 * SUB + r) * 64 + tid];
-                                z = FASTDIV ? affine_value_rcp(yv, scv, zpv, Ps[(2 * SUB + r) * 64 + tid], P.qmin, P.qmax) : affine_value(yv, scv, zpv, P.qmin, P.qmax);
+                                const F scv = Ps[(0 * SUB + r) * LANES + tid], zpv = Ps[(1 * SUB + r) * LANES + tid];
+                                z = FASTDIV ? affine_value_rcp(yv, scv, zpv, Ps[(2 * SUB + r) * LANES + tid], P.qmin, P.qmax) : affine_value(yv, scv, zpv, P.qmin, P.qmax);
                             } else if (KIND == G2D_Q_FORCED) {
-                                z = Ps[(0 * SUB + r) * 64 + tid];
+                                z = Ps[(0 * SUB + r) * LANES + tid];
                             } else {
                                 z = rint_even(yv);
                             }
                             const F ev = ok ? z - yv : (F)0;
                             const F cc = cacc[j] + ev;
-                            const F ccrow = __shfl_sync(0xffffffffu, cc, pw, SUB);
+                            const F ccrow = __shfl_sync(0xffffffffu, cc, pw, SUB);  // completed C of (k, p), rounded by lane p
                             if (active) {
                                 Ys[entry0 + s * LD] = ev;
                                 Cs[entry0 + s * LD] = cc;
                                 Zs[entry0 + s * LD] = z;
                             }
                             if (ok && pre_ptr) pre_ptr[(int64_t)s * n] = yv;
+                            // pushes: the error down column k through L, the completed C of (k, p) right along row k through U;
+                            // rows past the block's end read the zero padding, inactive lanes push zero
                             const F vcol = active ? ev : (F)0, vrow = active ? ccrow : (F)0;
                             F kl[SUB], ku[SUB];
 #pragma unroll
@@ -470,58 +481,48 @@ __global__ void __launch_bounds__(TTH) tile_sweep_kernel(SweepArgs<F> P, int S, 
                         for (int i = 0; i < ROLL; ++i) { cacc[SUB - ROLL + i] = keep_c[i]; yacc[SUB - ROLL + i] = keep_y[i]; }
                     }
                 };
-                if (G2D_ROLL < SUB) {
-                    if (fast_division) stages_rolled(std::true_type{});
-                    else stages_rolled(std::false_type{});
-                } else {
-                    if (fast_division) stages(std::true_type{});
-                    else stages(std::false_type{});
+                if (fast_division) stages(std::true_type{});
+                else stages(std::false_type{});
+            } else {
+                // Helper warp of sub-tile row ap, while sub-tile anti-diagonal w is swept.  Everything written here goes
+                // to sub-tiles of row ap on later anti-diagonals, which no other warp touches before the barrier.
+                const int ap = helper;
+                if (more) fetch_params(w + 1);
+                // the neighbour tiles' feedback for the row's sub-tile on the next anti-diagonal: lanes 0-15 form the down
+                // product, lanes 16-31 the right product, a 4 x 4 patch each; the operands come from global memory, so
+                // this goes first and is added to the sub-tile last
+                const int bn = w + 1 - ap;
+                const bool patch = P.neighbours && bn >= 0 && bn < NSUB && nb_on[half];
+                F acc[4][4];
+                if (patch)
+                    neighbour_patch<F>(acc, nb_a[half] + (int64_t)ap * SUB * nb_lda[half], nb_lda[half], nb_b[half] + bn * SUB, n, k, 0, TILE,
+                                       nb_rows - ap * SUB, nb_cols - bn * SUB, vec);
+                if (w >= 1) {
+                    // the sub-tiles swept one anti-diagonal ago, carried into the sub-tiles two or more ahead of them
+                    const int first = w + 1 - ap > 0 ? w + 1 - ap : 0;
+                    for (int bp = first; bp < NSUB; ++bp) carry_into(Ys, Cs, LUs, ap, bp, w - 1 - bp, w - 1 - ap, lane);
+                    __syncwarp();
                 }
-                // fetch the parameters of this half-warp's next sub-tile while the updates run.  Both half-warps make the
-                // call (it ends in a warp-wide vote); one without a next sub-tile fetches a valid dummy and stays masked
-                const int bn = w + 1 - sub_a;
-                fetch_params(bn >= 0 && bn < NSUB ? bn : 0);
-                have_params = true;
-            } else if (P.neighbours && w + 1 < 2 * NSUB - 1) {
-                // warps 2 and 3: the neighbour feedback for the sub-tiles of the next sub-tile anti-diagonal, one group of 16
-                // threads per sub-tile row; nobody else touches those sub-tiles until the barrier below
-                const int group = (tid - 2 * 32) >> 4, t = tid & 15;
-                const int ap = group, bp = w + 1 - ap;
-                if (bp >= 0 && bp < NSUB) {
-#pragma unroll 1
-                    for (int prod = 0; prod < 2; ++prod) {
-                        if (!nb_on[prod]) continue;
-                        F acc[4][4];
-                        neighbour_patch<F>(acc, nb_a[prod] + (int64_t)ap * SUB * nb_lda[prod], nb_lda[prod], nb_b[prod] + bp * SUB, n, t, 0, TILE,
-                                           nb_rows - ap * SUB, nb_cols - bp * SUB, vec);
-                        F *dst = (prod == 0 ? Cs : Ys) + (ap * SUB + (t >> 2) * 4) * LD + bp * SUB + (t & 3) * 4;
+                if (patch) {
+                    F *dst = (half == 0 ? Cs : Ys) + (ap * SUB + (k >> 2) * 4) * LD + bn * SUB + (k & 3) * 4;
 #pragma unroll
-                        for (int x = 0; x < 4; ++x) {
-                            F d[4];
-                            load4(dst + x * LD, d);
+                    for (int x = 0; x < 4; ++x) {
+                        F d[4];
+                        load4(dst + x * LD, d);
 #pragma unroll
-                            for (int y = 0; y < 4; ++y) d[y] += acc[x][y];
-                            store4(dst + x * LD, d);
-                        }
+                        for (int y = 0; y < 4; ++y) d[y] += acc[x][y];
+                        store4(dst + x * LD, d);
                     }
                 }
+                if (more) finish_params();
             }
             __syncthreads();
-            // ---- apply the finished sub-tiles to the rest of the tile ----
-            if (w < 2 * NSUB - 2) {
-                int count = 0;
-                for (int ap = 0; ap < NSUB; ++ap) {
-                    for (int bp = 0; bp < NSUB; ++bp) {
-                        if (ap + bp <= w) continue;
-                        const int as = w - bp, bs = w - ap;
-                        const bool down = as >= 0 && as < NSUB, right = bs >= 0 && bs < NSUB;
-                        if (!down && !right) continue;
-                        if ((count++ & (NSUB - 1)) != warp) continue;
-                        if (down)  // C[ap, bp] += L[ap, as] E[as, bp]
-                            mm16(Cs + ap * SUB * LD + bp * SUB, LUs + ap * SUB * LD + as * SUB, Ys + as * SUB * LD + bp * SUB, lane);
-                        if (right)  // Y[ap, bp] += C[ap, bs] U[bs, bp]
-                            mm16(Ys + ap * SUB * LD + bp * SUB, Cs + ap * SUB * LD + bs * SUB, LUs + bs * SUB * LD + bp * SUB, lane);
-                    }
+            // ---- between two sweeps: the anti-diagonal just swept, carried into the next one; the next parameters ----
+            if (more) {
+                if (!sweeper) {
+                    store_params();
+                    const int ap = helper, bn = w + 1 - ap;
+                    if (bn >= 0 && bn < NSUB) carry_into(Ys, Cs, LUs, ap, bn, ap - 1, bn - 1, lane);
                 }
                 __syncthreads();
             }
@@ -558,10 +559,8 @@ __global__ void __launch_bounds__(TTH) tile_sweep_kernel(SweepArgs<F> P, int S, 
         }
         // ---- store the rounded values, the errors and the completed C of the tile ----
         if (vec) {
-            constexpr int PER = TILE * TILE / 4 / TTH;
-#pragma unroll
-            for (int t = 0; t < PER; ++t) {
-                const int idx = t * TTH + tid, r = idx / (TILE / 4), c = (idx % (TILE / 4)) * 4;
+            for (int idx = tid; idx < TILE * TILE / 4; idx += TTH) {
+                const int r = idx / (TILE / 4), c = (idx % (TILE / 4)) * 4;
                 F ve[4], vc[4], vz[4];
                 load4(Ys + r * LD + c, ve);
                 load4(Cs + r * LD + c, vc);
@@ -589,7 +588,7 @@ template <typename F, int KIND>
 static int launch_kind(const SweepArgs<F> &args, int S, int parity, cudaStream_t stream) {
     // the opt-in to more than 48 KB of dynamic shared memory is per device
     static PerDeviceOnce configured;
-    const size_t smem = sizeof(F) * (4 * TILE * LD + 2 * NSUB * DBLK + 3 * SUB * 64);
+    const size_t smem = sizeof(F) * (4 * TILE * LD + 2 * NSUB * DBLK + 3 * SUB * LANES) + sizeof(unsigned) * (2 * LANES + 2 * SWEEPERS);
     if (configured.run([&] { return cudaFuncSetAttribute(tile_sweep_kernel<F, KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess; }) != G2D_OK)
         return G2D_ERR_CUDA;
     const int i_lo = S - args.nJ + 1 > 0 ? S - args.nJ + 1 : 0;
