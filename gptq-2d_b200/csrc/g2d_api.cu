@@ -80,7 +80,7 @@ inline bool tc_eligible(const g2d_sweep_desc *d) {
 }
 inline size_t tc_extra_bytes(const g2d_sweep_desc *d) {
     const size_t mn = align256(4 * (size_t)d->m * d->n), mm = align256(4 * (size_t)d->m * d->m), nn = align256(4 * (size_t)d->n * d->n);
-    return 256 + 4 * mn + 2 * mm + 2 * nn + 2 * mn;  // flag, E^T and C splits, L and U^T splits, far planes of the pipelined schedule
+    return 256 + 4 * mn + 2 * mm + 2 * nn + 4 * mn;  // flag, E^T and C splits, L and U^T splits, far and neighbour planes of the pipelined schedule
 }
 
 int check_sweep(const g2d_sweep_desc *d) {
@@ -409,6 +409,7 @@ int sweep_fused(const g2d_sweep_desc *d, cudaStream_t stream, LaunchTimer *timer
         if constexpr (sizeof(F) == sizeof(float)) {
             if (d->reserved == 3 || d->reserved == 0) {
                 float *yf = (float *)p, *cf = (float *)(p + mn);
+                a.yn = (float *)(p + 2 * mn); a.cn = (float *)(p + 3 * mn);  // written before they are read: no clearing
                 if (cudaMemsetAsync(yf, 0, 2 * mn, stream) != cudaSuccess) return G2D_ERR_CUDA;
                 return sweep_pipelined(d, a, planes, yf, cf, stream, timer, flops);
             }

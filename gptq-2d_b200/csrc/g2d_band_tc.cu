@@ -182,7 +182,12 @@ int band_tc_prepare(BandTcMaps *opaque, const TcPlanes &pl, int64_t m, int64_t n
         !make_map(&maps->c_hi, pl.c_hi, m, n, BN) || !make_map(&maps->c_lo, pl.c_lo, m, n, BN))
         return G2D_ERR_CUDA;
     static PerDeviceOnce configured;
-    return configured.run([&] { return cudaFuncSetAttribute(band_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BAND_STAGES * BAND_STAGE_BYTES + 1024) == cudaSuccess; });
+    // The kernels of the pipelined schedule share SMs.  Each asks for the largest shared-memory carve-out: an SM that a
+    // kernel with a smaller one had configured takes no CTA of another kernel beside it until it has drained.
+    return configured.run([&] {
+        return cudaFuncSetAttribute(band_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BAND_STAGES * BAND_STAGE_BYTES + 1024) == cudaSuccess &&
+               cudaFuncSetAttribute(band_tc_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared) == cudaSuccess;
+    });
 }
 
 int launch_band_tc(const BandTcMaps *opaque, float *y, float *c, int64_t m, int64_t n, int s0, int s1, int t0, int t1, int outer_macro,

@@ -123,6 +123,9 @@ struct SweepArgs {
     // tile is loaded, and the switch that makes a tile apply the feedback of its two nearest finished neighbours itself
     const F *yf = nullptr, *cf = nullptr;
     int neighbours = 0;
+    // pipelined schedule only: the planes through which a tile hands the feedback for its lower and its right neighbour
+    // on (the neighbour adds them when it loads); every entry that is read has been written one launch before
+    F *yn = nullptr, *cn = nullptr;
 };
 
 // fp32 -> tf32 hi (round to nearest) and the fp32 remainder: a = hi + lo exactly, and hi*hi' + lo*hi' + hi*lo' recovers

@@ -21,8 +21,11 @@
 //     after every group; two shuffles per stage exchange the row accumulator and the completed C with the partner
 //     lane.  The feedback coefficients of a sub-tile come from zero-padded copies of the diagonal blocks of L and
 //     U^T, so the pushes need no bounds predicates: out-of-range pushes multiply by zero;
-//   * pipelined schedule: a tile also adds the far-feedback planes as it loads and applies the feedback of its two
-//     neighbours of the previous tile anti-diagonal itself (the helper warps, one sub-tile anti-diagonal ahead).
+//   * pipelined schedule: a tile also adds the far-feedback planes as it loads, and the feedback between neighbour
+//     tiles of consecutive tile anti-diagonals travels as a push: the helper warps of tile (I, J) form, from the
+//     errors and the completed C in shared memory,  L[I + 1, I] E[I, J]  and  C[I, J] U[J, J + 1]  while the tile is
+//     still being swept and store them into two planes of their own, which the tiles (I + 1, J) and (I, J + 1) add
+//     as they load one launch later.  No load from another tile's results sits on a tile's critical path.
 #include <type_traits>
 
 #include "g2d_common.cuh"
@@ -39,6 +42,7 @@ constexpr int SWEEPERS = NSUB / 2;      // warps that sweep: one half-warp per s
 constexpr int HELPERS = NSUB;           // warps that feed them: one per sub-tile row
 constexpr int TTH = (SWEEPERS + HELPERS) * 32;  // threads per CTA
 constexpr int LANES = SWEEPERS * 32;    // sweeping lanes
+constexpr int ZLD = SUB;                // row stride of the staging blocks of the rounded values (the walk down an anti-diagonal moves 15 words: no conflicts)
 
 template <typename F>
 __device__ __forceinline__ void load4(const F *p, F (&v)[4]);
@@ -107,41 +111,63 @@ __device__ __forceinline__ void carry_into(F *Ys, F *Cs, const F *LUs, int ap, i
     }
 }
 
-// Feedback of a neighbour tile into one 16 x 16 sub-tile, for a group of 16 threads (t = 0..15): thread t forms the
-// 4 x 4 patch at rows 4 (t / 4), columns 4 (t % 4) of  A[16 x K] B[K x 16]  over k = k0 .. k0 + kn - 1 and returns it
-// in acc.  A and B are row-major in global memory (written by an earlier launch, or constant); A points at the
-// sub-tile's row strip, B at its column strip.  Rows of A from `rows` on and columns of B from `cols` on read as zero
-// (ragged last tiles); `vec` promises whole, 16-byte aligned operands.
+// The products of the neighbour push: the 2 x 4 outputs of a lane stay in registers.  d += A B with A and B in shared
+// memory (row stride LD), and the same with the lane's two rows of A held in registers.
 template <typename F>
-__device__ __forceinline__ void neighbour_patch(F (&acc)[4][4], const F *__restrict__ A, int64_t lda, const F *__restrict__ B, int64_t ldb,
-                                                int t, int k0, int kn, int rows, int cols, bool vec) {
-    const int pr = (t >> 2) * 4, pc = (t & 3) * 4;
+__device__ __forceinline__ void mm16_acc(F (&d0)[4], F (&d1)[4], const F *__restrict__ A, const F *__restrict__ B, int lane) {
+    const int r = (lane >> 2) * 2, c = (lane & 3) * 4;
 #pragma unroll
-    for (int x = 0; x < 4; ++x)
+    for (int k = 0; k < SUB; k += 4) {
+        F a0[4], a1[4];
+        load4(A + r * LD + k, a0);
+        load4(A + (r + 1) * LD + k, a1);
 #pragma unroll
-        for (int y = 0; y < 4; ++y) acc[x][y] = (F)0;
-#pragma unroll(sizeof(F) == sizeof(float) ? 4 : 2)
-    for (int k = k0; k < k0 + kn; k += 4) {
-        F a[4][4], b[4][4];
+        for (int kk = 0; kk < 4; ++kk) {
+            F b[4];
+            load4(B + (k + kk) * LD + c, b);
 #pragma unroll
-        for (int x = 0; x < 4; ++x) {
-            if (vec) {
-                load4(A + (pr + x) * lda + k, a[x]);
-                load4(B + (k + x) * ldb + pc, b[x]);
-            } else {
-#pragma unroll
-                for (int y = 0; y < 4; ++y) {
-                    a[x][y] = pr + x < rows ? A[(pr + x) * lda + k + y] : (F)0;
-                    b[x][y] = pc + y < cols ? B[(k + x) * ldb + pc + y] : (F)0;
-                }
+            for (int y = 0; y < 4; ++y) {
+                d0[y] += a0[kk] * b[y];
+                d1[y] += a1[kk] * b[y];
             }
         }
+    }
+}
+template <typename F>
+__device__ __forceinline__ void mm16_areg(F (&d0)[4], F (&d1)[4], const F *a0, const F *a1, const F *__restrict__ B, int lane) {
+    // a0 / a1: this lane's quarter of its two rows of A (columns 4 (lane % 4) .. + 3); the four lanes that share the
+    // rows hand each other their quarters by shuffle
+    const int c = (lane & 3) * 4;
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
+    for (int k = 0; k < SUB; ++k) {
+        F b[4];
+        load4(B + k * LD + c, b);
+        const F v0 = __shfl_sync(0xffffffffu, a0[k & 3], k >> 2, 4), v1 = __shfl_sync(0xffffffffu, a1[k & 3], k >> 2, 4);
 #pragma unroll
-            for (int x = 0; x < 4; ++x)
+        for (int y = 0; y < 4; ++y) {
+            d0[y] += v0 * b[y];
+            d1[y] += v1 * b[y];
+        }
+    }
+}
+// Stores a lane's 2 x 4 outputs of a 16 x 16 block at `dst` (row stride ld); rows / columns from rows_left / cols_left on lie
+// outside the matrix.  `vec`: rows are 16-byte aligned and columns come in whole groups of four.
+template <typename F>
+__device__ __forceinline__ void store_block(F *dst, int64_t ld, const F (&d0)[4], const F (&d1)[4], int lane, int64_t rows_left, int64_t cols_left, bool vec) {
+    const int r = (lane >> 2) * 2, c = (lane & 3) * 4;
+    if (vec) {
+        if (c < cols_left) {
+            if (r < rows_left) store4(dst + r * ld + c, d0);
+            if (r + 1 < rows_left) store4(dst + (r + 1) * ld + c, d1);
+        }
+    } else {
 #pragma unroll
-                for (int y = 0; y < 4; ++y) acc[x][y] += a[x][kk] * b[kk][y];
+        for (int y = 0; y < 4; ++y) {
+            if (c + y < cols_left) {
+                if (r < rows_left) dst[r * ld + c + y] = d0[y];
+                if (r + 1 < rows_left) dst[(r + 1) * ld + c + y] = d1[y];
+            }
+        }
     }
 }
 
@@ -152,9 +178,10 @@ __global__ void __launch_bounds__(TTH) tile_sweep_kernel(SweepArgs<F> P, int S, 
     F *Cs = Ys + TILE * LD;                   // down feedback; the completed C once a sub-tile is swept
     F *LUs = Cs + TILE * LD;                  // strict lower part: L[I, I]; strict upper part: U[J, J]
     F *Dg = LUs + TILE * LD;                  // [2][NSUB] zero-padded diagonal blocks: L[a, a] and U[b, b]^T, strictly lower
-    F *Zs = Dg + 2 * NSUB * DBLK;             // the rounded values, written out in one coalesced pass at the end
-    F *Ps = Zs + TILE * LD;                   // [3][SUB][LANES]: quantizer parameters of the sweeping lanes, by register number
-    unsigned *Pv = reinterpret_cast<unsigned *>(Ps + 3 * SUB * LANES);  // [2][LANES] registers holding entries inside the matrix, one word per half of the registers; [2][SWEEPERS] reciprocal division allowed
+    F *Ubs = Dg + 2 * NSUB * DBLK;            // pipelined schedule: U[J, J + 1], the right neighbour's coupling block
+    F *Ps = Ubs + TILE * LD;                   // [3][SUB][LANES]: quantizer parameters of the sweeping lanes, by register number
+    F *Zst = Ps + 3 * SUB * LANES;            // [NSUB][SUB][ZLD]: rounded values of the sub-tiles being swept, written out by the helpers after the sweep
+    unsigned *Pv = reinterpret_cast<unsigned *>(Zst + NSUB * SUB * ZLD);  // [2][LANES] registers holding entries inside the matrix, one word per half of the registers; [2][SWEEPERS] reciprocal division allowed
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int k = lane & 15, half = lane >> 4;
@@ -174,6 +201,10 @@ __global__ void __launch_bounds__(TTH) tile_sweep_kernel(SweepArgs<F> P, int S, 
         const F *fg = KIND == G2D_Q_FORCED ? P.forced + batch * m * n : nullptr;
         F *pre = P.y_pre ? P.y_pre + batch * m * n : nullptr;
         const F *yfg = P.yf ? P.yf + batch * m * n : nullptr, *cfg = P.yf ? P.cf + batch * m * n : nullptr;
+        // neighbour push (pipelined schedule): what this tile receives and what it owes
+        F *yng = P.yn ? P.yn + batch * m * n : nullptr, *cng = P.yn ? P.cn + batch * m * n : nullptr;
+        const bool gets_right = yng != nullptr && J > 0, gets_down = yng != nullptr && I > 0;
+        const bool owes_right = yng != nullptr && J + 1 < P.nJ, owes_down = yng != nullptr && I + 1 < P.nI;
 
         // ---- quantizer parameters, prepared by the helper warps ----
         // Helper warp h prepares, for the sweeping lane of its own lane number in sweeping warp h mod SWEEPERS, half
@@ -252,6 +283,8 @@ __global__ void __launch_bounds__(TTH) tile_sweep_kernel(SweepArgs<F> P, int S, 
         };
         if (!sweeper) fetch_params(0);
 
+        constexpr bool PUSH = sizeof(F) == sizeof(float);  // the neighbour push exists for float (pipelined schedule) only
+
         // ---- load the tile; all global loads of a pass are issued before its shared-memory stores ----
         const bool vec = full && (n % 4 == 0) && (m % 4 == 0) &&
                          ((reinterpret_cast<uintptr_t>(yg) | reinterpret_cast<uintptr_t>(cg) | reinterpret_cast<uintptr_t>(eg) |
@@ -294,6 +327,40 @@ __global__ void __launch_bounds__(TTH) tile_sweep_kernel(SweepArgs<F> P, int S, 
                         }
                     }
                 }
+                if constexpr (PUSH) {
+                    if (pass == 0 && (gets_right || gets_down)) {
+                        // what the left and the upper neighbour pushed one launch ago
+                        F fa[PER][4], fb[PER][4];
+#pragma unroll
+                        for (int t = 0; t < PER; ++t) {
+                            const int idx = t * TTH + tid, r = idx / (TILE / 4), c = (idx % (TILE / 4)) * 4;
+                            if (idx >= VECS) continue;
+#pragma unroll
+                            for (int x = 0; x < 4; ++x) fa[t][x] = fb[t][x] = (F)0;
+                            if (gets_right) load4(yng + (i0 + r) * n + j0 + c, fa[t]);
+                            if (gets_down) load4(cng + (i0 + r) * n + j0 + c, fb[t]);
+                        }
+#pragma unroll
+                        for (int t = 0; t < PER; ++t) {
+                            if (t * TTH + tid >= VECS) continue;
+#pragma unroll
+                            for (int x = 0; x < 4; ++x) {
+                                va[t][x] += fa[t][x];
+                                vb[t][x] += fb[t][x];
+                            }
+                        }
+                    }
+                }
+                if (pass == 1 && owes_right) {
+#pragma unroll
+                    for (int t = 0; t < PER; ++t) {
+                        const int idx = t * TTH + tid, r = idx / (TILE / 4), c = (idx % (TILE / 4)) * 4;
+                        if (idx >= VECS) continue;
+                        F uv[4] = {(F)0, (F)0, (F)0, (F)0};
+                        if (j0 + TILE + c < n) load4(ug + (j0 + r) * n + j0 + TILE + c, uv);
+                        store4(Ubs + r * LD + c, uv);
+                    }
+                }
 #pragma unroll
                 for (int t = 0; t < PER; ++t) {
                     const int idx = t * TTH + tid, r = idx / (TILE / 4), c = (idx % (TILE / 4)) * 4;
@@ -323,6 +390,8 @@ __global__ void __launch_bounds__(TTH) tile_sweep_kernel(SweepArgs<F> P, int S, 
                     if (in && yfg != nullptr) {
                         vy[t] += yfg[gi * n + gj];
                         vc[t] += cfg[gi * n + gj];
+                        if (gets_right) vy[t] += yng[gi * n + gj];
+                        if (gets_down) vc[t] += cng[gi * n + gj];
                     }
                     vl[t] = (F)0;
                     if (idx < TILE * TILE) {
@@ -342,40 +411,13 @@ __global__ void __launch_bounds__(TTH) tile_sweep_kernel(SweepArgs<F> P, int S, 
                     LUs[r * LD + c] = vl[t];
                 }
             }
+            if (owes_right)
+                for (int idx = tid; idx < TILE * TILE; idx += TTH) {
+                    const int r = idx / TILE, c = idx % TILE;
+                    Ubs[r * LD + c] = (j0 + r < n && j0 + TILE + c < n) ? ug[(j0 + r) * n + j0 + TILE + c] : (F)0;
+                }
         }
         __syncthreads();
-        // Pipelined schedule: the feedback of the two tiles finished one launch ago, which no update kernel has carried yet:
-        //     C[I, J] += L[I, I - 1] E[I - 1, J],      Y[I, J] += C[I, J - 1] U[J - 1, J]  (the completed C of the left neighbour).
-        // Only the first sub-tile needs it before the sweep starts (here: eight groups of 16 threads split the two
-        // products and four quarters of k, partial patches are summed in a fixed order through shared memory); the
-        // sub-tiles of a later sub-tile anti-diagonal get theirs from the helper warps while the one before is swept.
-        const int nb_rows = (int)(m - i0 < TILE ? m - i0 : TILE), nb_cols = (int)(n - j0 < TILE ? n - j0 : TILE);
-        const F *const nb_a[2] = {lg + i0 * m + (i0 - TILE), cg + i0 * n + (j0 - TILE)};       // A operands: L block, left C
-        const F *const nb_b[2] = {eg + (i0 - TILE) * n + j0, ug + (j0 - TILE) * n + j0};       // B operands: upper E, U block
-        const int64_t nb_lda[2] = {m, n};
-        const bool nb_on[2] = {P.neighbours && I > 0, P.neighbours && J > 0};
-        if (P.neighbours) {
-            const int group = tid >> 4, t = tid & 15, prod = group & 1, quarter = group >> 1;
-            F acc[4][4];
-            if (group < 8 && nb_on[prod]) {
-                neighbour_patch<F>(acc, nb_a[prod], nb_lda[prod], nb_b[prod], n, t, quarter * (TILE / 4), TILE / 4, nb_rows, nb_cols, vec);
-#pragma unroll
-                for (int x = 0; x < 4; ++x)
-#pragma unroll
-                    for (int y = 0; y < 4; ++y) Zs[group * (SUB * SUB) + ((t >> 2) * 4 + x) * SUB + (t & 3) * 4 + y] = acc[x][y];
-            }
-            __syncthreads();
-            for (int idx = tid; idx < 2 * SUB * SUB; idx += TTH) {
-                const int prod2 = idx / (SUB * SUB), e = idx % (SUB * SUB);
-                if (nb_on[prod2]) {
-                    F *dst = (prod2 == 0 ? Cs : Ys) + (e / SUB) * LD + e % SUB;
-                    F sum = *dst;
-#pragma unroll
-                    for (int q4 = 0; q4 < 4; ++q4) sum += Zs[((q4 << 1) | prod2) * (SUB * SUB) + e];
-                    *dst = sum;
-                }
-            }
-        }
         for (int idx = tid; idx < 2 * NSUB * DBLK; idx += TTH) {
             const int which = idx / (NSUB * DBLK), blk = idx / DBLK % NSUB, p = idx % DBLK / DLD, dd = idx % DLD;
             F v = (F)0;
@@ -395,9 +437,9 @@ __global__ void __launch_bounds__(TTH) tile_sweep_kernel(SweepArgs<F> P, int S, 
         // anti-diagonal s sit in register s mod 16.  At stage s lane k rounds its column's entry (p, k), p = s - k; the
         // lane that owns row p is lane p, and lane p in turn rounds (k, p), the entry of this lane's row: the two lanes
         // exchange the row accumulator before rounding and the completed C after it.
-        for (int w = 0; w < 2 * NSUB - 1; ++w) {
-            const bool more = w + 1 < 2 * NSUB - 1;
-            if (sweeper) {
+        // The two roles run the same sequence of barriers from loops of their own, so that neither holds the other's registers.
+        if (sweeper) {
+            for (int w = 0; w < 2 * NSUB - 1; ++w) {
                 const int sub_a = 2 * warp + half;
                 const int b_raw = w - sub_a;
                 const bool tile_ok = b_raw >= 0 && b_raw < NSUB;  // a half-warp without a sub-tile runs along with everything masked
@@ -415,6 +457,7 @@ __global__ void __launch_bounds__(TTH) tile_sweep_kernel(SweepArgs<F> P, int S, 
                 // entry (s - k, k) of the sub-tile: a lane-constant address plus s rows
                 const int entry0 = (r0 - k) * LD + c0 + k;
                 F *pre_ptr = pre ? pre + (i0 + r0 - k) * n + j0 + c0 + k : nullptr;
+                const int zst0 = (r0 - k) * ZLD + k;
                 const F *const dgl = Dg + sub_a * DBLK, *const dgu = Dg + (NSUB + b) * DBLK;
                 // The 32 stages in groups of ROLL: inside a group the registers are indexed statically, after it they are
                 // renamed by moving them ROLL places, so that the loop body is ROLL stages long (the fully unrolled form
@@ -448,7 +491,7 @@ __global__ void __launch_bounds__(TTH) tile_sweep_kernel(SweepArgs<F> P, int S, 
                             if (active) {
                                 Ys[entry0 + s * LD] = ev;
                                 Cs[entry0 + s * LD] = cc;
-                                Zs[entry0 + s * LD] = z;
+                                Zst[zst0 + s * ZLD] = z;
                             }
                             if (ok && pre_ptr) pre_ptr[(int64_t)s * n] = yv;
                             // pushes: the error down column k through L, the completed C of (k, p) right along row k through U;
@@ -483,51 +526,141 @@ __global__ void __launch_bounds__(TTH) tile_sweep_kernel(SweepArgs<F> P, int S, 
                 };
                 if (fast_division) stages(std::true_type{});
                 else stages(std::false_type{});
-            } else {
+                __syncthreads();
+                if (w + 1 < 2 * NSUB - 1) __syncthreads();  // the helpers carry the anti-diagonal just swept into the next one
+            }
+        } else {
+            // ---- neighbour push: registers of the helper warps (float, pipelined schedule) ----
+            // Helper warp h keeps, in the layout of mm16 (rows 2 (lane / 4) and the next one), its two rows of the strip
+            // L[I + 1, I](rows 16 h ..) for the down push (of each block of 16 columns the four that belong to lane % 4:
+            // the four lanes of a row pair share them by shuffle), the running sums of the right push of sub-tile row h (four blocks;
+            // not for the last row, whose four blocks are spread over the four helpers so that the work left after the
+            // last sweep is one product each), and the last column's down push up to its last term.
+            F lb0[PUSH ? TILE / 4 : 1], lb1[PUSH ? TILE / 4 : 1];
+            F yn0[PUSH ? NSUB : 1][4], yn1[PUSH ? NSUB : 1][4], y30[4], y31[4], c30[4], c31[4];
+            if constexpr (PUSH) {
+    #pragma unroll
+                for (int y = 0; y < 4; ++y) {
+    #pragma unroll
+                    for (int cb = 0; cb < NSUB; ++cb) yn0[cb][y] = yn1[cb][y] = (F)0;
+                    y30[y] = y31[y] = c30[y] = c31[y] = (F)0;
+                }
+            }
+            for (int w = 0; w < 2 * NSUB - 1; ++w) {
+                const bool more = w + 1 < 2 * NSUB - 1;
                 // Helper warp of sub-tile row ap, while sub-tile anti-diagonal w is swept.  Everything written here goes
                 // to sub-tiles of row ap on later anti-diagonals, which no other warp touches before the barrier.
                 const int ap = helper;
                 if (more) fetch_params(w + 1);
-                // the neighbour tiles' feedback for the row's sub-tile on the next anti-diagonal: lanes 0-15 form the down
-                // product, lanes 16-31 the right product, a 4 x 4 patch each; the operands come from global memory, so
-                // this goes first and is added to the sub-tile last
-                const int bn = w + 1 - ap;
-                const bool patch = P.neighbours && bn >= 0 && bn < NSUB && nb_on[half];
-                F acc[4][4];
-                if (patch)
-                    neighbour_patch<F>(acc, nb_a[half] + (int64_t)ap * SUB * nb_lda[half], nb_lda[half], nb_b[half] + bn * SUB, n, k, 0, TILE,
-                                       nb_rows - ap * SUB, nb_cols - bn * SUB, vec);
                 if (w >= 1) {
                     // the sub-tiles swept one anti-diagonal ago, carried into the sub-tiles two or more ahead of them
                     const int first = w + 1 - ap > 0 ? w + 1 - ap : 0;
                     for (int bp = first; bp < NSUB; ++bp) carry_into(Ys, Cs, LUs, ap, bp, w - 1 - bp, w - 1 - ap, lane);
                     __syncwarp();
                 }
-                if (patch) {
-                    F *dst = (half == 0 ? Cs : Ys) + (ap * SUB + (k >> 2) * 4) * LD + bn * SUB + (k & 3) * 4;
+                if constexpr (PUSH) {
+                    const bool pvec = n % 4 == 0 && reinterpret_cast<uintptr_t>(yng) % (4 * sizeof(F)) == 0;
+                            if (owes_down && w == 1) {  // the strip of L[I + 1, I]: first used three anti-diagonals from here
+                        const int64_t gi = i0 + TILE + ap * SUB + (lane >> 2) * 2;
+                        const bool lvec = m % 4 == 0 && reinterpret_cast<uintptr_t>(lg) % (4 * sizeof(F)) == 0;
 #pragma unroll
-                    for (int x = 0; x < 4; ++x) {
-                        F d[4];
-                        load4(dst + x * LD, d);
+                        for (int as = 0; as < NSUB; ++as) {
+                            const int64_t col = i0 + as * SUB + (lane & 3) * 4;
+                            F t0[4] = {(F)0, (F)0, (F)0, (F)0}, t1[4] = {(F)0, (F)0, (F)0, (F)0};
+                            if (lvec) {
+                                if (gi < m) load4(lg + gi * m + col, t0);
+                                if (gi + 1 < m) load4(lg + (gi + 1) * m + col, t1);
+                            } else {
 #pragma unroll
-                        for (int y = 0; y < 4; ++y) d[y] += acc[x][y];
-                        store4(dst + x * LD, d);
+                                for (int x = 0; x < 4; ++x) {
+                                    if (gi < m) t0[x] = lg[gi * m + col + x];
+                                    if (gi + 1 < m) t1[x] = lg[(gi + 1) * m + col + x];
+                                }
+                            }
+#pragma unroll
+                            for (int x = 0; x < 4; ++x) { lb0[as * 4 + x] = t0[x]; lb1[as * 4 + x] = t1[x]; }
+                        }
+                    }
+                    if (owes_right && w >= 1) {
+                        // right push: the completed C of the row's sub-tile swept one anti-diagonal ago times its block
+                        // row of U[J, J + 1]; a row is stored once its last sub-tile has gone in
+                        const int b = w - 1 - ap;
+                        if (ap < NSUB - 1 && b >= 0 && b < NSUB) {
+#pragma unroll
+                            for (int cb = 0; cb < NSUB; ++cb) mm16_acc(yn0[cb], yn1[cb], Cs + ap * SUB * LD + b * SUB, Ubs + b * SUB * LD + cb * SUB, lane);
+                            if (b == NSUB - 1) {
+#pragma unroll
+                                for (int cb = 0; cb < NSUB; ++cb)
+                                    store_block(yng + (i0 + ap * SUB) * n + j0 + TILE + cb * SUB, n, yn0[cb], yn1[cb], lane, m - (i0 + ap * SUB), n - (j0 + TILE + cb * SUB), pvec);
+                            }
+                        }
+                        const int b3 = w - NSUB;  // the last row's sub-tile swept one anti-diagonal ago: this helper's column block of it
+                        if (b3 >= 0 && b3 < NSUB) mm16_acc(y30, y31, Cs + (NSUB - 1) * SUB * LD + b3 * SUB, Ubs + b3 * SUB * LD + ap * SUB, lane);
+                    }
+                    if (owes_down) {
+                        // down push: a column of sub-tiles is complete three anti-diagonals after its first; this helper's
+                        // row strip of L[I + 1, I] times the column's errors, stored at once
+                        const int b = w - NSUB;
+                        if (b >= 0) {
+                            F d0[4] = {(F)0, (F)0, (F)0, (F)0}, d1[4] = {(F)0, (F)0, (F)0, (F)0};
+#pragma unroll
+                            for (int as = 0; as < NSUB; ++as) mm16_areg(d0, d1, lb0 + as * 4, lb1 + as * 4, Ys + as * SUB * LD + b * SUB, lane);
+                            store_block(cng + (i0 + TILE + ap * SUB) * n + j0 + b * SUB, n, d0, d1, lane, m - (i0 + TILE + ap * SUB), n - (j0 + b * SUB), pvec);
+                        }
+                        if (!more) {  // the last column, up to the term of the sub-tile being swept now
+#pragma unroll
+                            for (int as = 0; as < NSUB - 1; ++as) mm16_areg(c30, c31, lb0 + as * 4, lb1 + as * 4, Ys + as * SUB * LD + (NSUB - 1) * SUB, lane);
+                        }
                     }
                 }
                 if (more) finish_params();
-            }
-            __syncthreads();
-            // ---- between two sweeps: the anti-diagonal just swept, carried into the next one; the next parameters ----
-            if (more) {
-                if (!sweeper) {
-                    store_params();
-                    const int ap = helper, bn = w + 1 - ap;
-                    if (bn >= 0 && bn < NSUB) carry_into(Ys, Cs, LUs, ap, bn, ap - 1, bn - 1, lane);
-                }
                 __syncthreads();
+                {   // the rounded values of the sub-tiles just swept: helper warp ap writes out the block of its row
+                    const int bz = w - ap;
+                    if (bz >= 0 && bz < NSUB) {
+                        const bool zvec = n % 4 == 0 && reinterpret_cast<uintptr_t>(yg) % (4 * sizeof(F)) == 0;
+#pragma unroll
+                        for (int q = 0; q < 2; ++q) {
+                            const int e = lane * 2 + q, row = e >> 2, c4 = (e & 3) * 4;
+                            const int64_t gi = i0 + ap * SUB + row, gj = j0 + bz * SUB + c4;
+                            F v[4];
+                            load4(Zst + (ap * SUB + row) * ZLD + c4, v);
+                            if (gi < m) {
+                                if (zvec) {
+                                    if (gj < n) store4(yg + gi * n + gj, v);
+                                } else {
+#pragma unroll
+                                    for (int x = 0; x < 4; ++x)
+                                        if (gj + x < n) yg[gi * n + gj + x] = v[x];
+                                }
+                            }
+                        }
+                    }
+                }
+                // ---- between two sweeps: the anti-diagonal just swept, carried into the next one; the next parameters ----
+                if (more) {
+                    store_params();
+                    const int bn = w + 1 - ap;
+                    if (bn >= 0 && bn < NSUB) carry_into(Ys, Cs, LUs, ap, bn, ap - 1, bn - 1, lane);
+                    __syncthreads();
+                }
+            }
+            // ---- neighbour push: the last sub-tile's terms, one product per helper and plane ----
+            if constexpr (PUSH) {
+                {
+                    const bool pvec = n % 4 == 0 && reinterpret_cast<uintptr_t>(yng) % (4 * sizeof(F)) == 0;
+                    const int x = helper, last = NSUB - 1;
+                    if (owes_right) {
+                        mm16_acc(y30, y31, Cs + last * SUB * LD + last * SUB, Ubs + last * SUB * LD + x * SUB, lane);
+                        store_block(yng + (i0 + last * SUB) * n + j0 + TILE + x * SUB, n, y30, y31, lane, m - (i0 + last * SUB), n - (j0 + TILE + x * SUB), pvec);
+                    }
+                    if (owes_down) {
+                        mm16_areg(c30, c31, lb0 + last * 4, lb1 + last * 4, Ys + last * SUB * LD + last * SUB, lane);
+                        store_block(cng + (i0 + TILE + x * SUB) * n + j0 + last * SUB, n, c30, c31, lane, m - (i0 + TILE + x * SUB), n - (j0 + last * SUB), pvec);
+                    }
+                }
             }
         }
-
         // ---- operands of the tensor-core macro updates: tf32 hi / lo of E (transposed) and of the completed C ----
         if (P.c_hi != nullptr) {
             if constexpr (sizeof(F) == sizeof(float)) {
@@ -557,17 +690,15 @@ __global__ void __launch_bounds__(TTH) tile_sweep_kernel(SweepArgs<F> P, int S, 
                 }
             }
         }
-        // ---- store the rounded values, the errors and the completed C of the tile ----
+        // ---- store the errors and the completed C of the tile ----
         if (vec) {
             for (int idx = tid; idx < TILE * TILE / 4; idx += TTH) {
                 const int r = idx / (TILE / 4), c = (idx % (TILE / 4)) * 4;
-                F ve[4], vc[4], vz[4];
+                F ve[4], vc[4];
                 load4(Ys + r * LD + c, ve);
                 load4(Cs + r * LD + c, vc);
-                load4(Zs + r * LD + c, vz);
                 store4(eg + (i0 + r) * n + j0 + c, ve);
                 store4(cg + (i0 + r) * n + j0 + c, vc);
-                store4(yg + (i0 + r) * n + j0 + c, vz);
             }
         } else {
             for (int idx = tid; idx < TILE * TILE; idx += TTH) {
@@ -576,7 +707,6 @@ __global__ void __launch_bounds__(TTH) tile_sweep_kernel(SweepArgs<F> P, int S, 
                 if (gi < m && gj < n) {
                     eg[gi * n + gj] = Ys[r * LD + c];
                     cg[gi * n + gj] = Cs[r * LD + c];
-                    yg[gi * n + gj] = Zs[r * LD + c];
                 }
             }
         }
@@ -588,8 +718,12 @@ template <typename F, int KIND>
 static int launch_kind(const SweepArgs<F> &args, int S, int parity, cudaStream_t stream) {
     // the opt-in to more than 48 KB of dynamic shared memory is per device
     static PerDeviceOnce configured;
-    const size_t smem = sizeof(F) * (4 * TILE * LD + 2 * NSUB * DBLK + 3 * SUB * LANES) + sizeof(unsigned) * (2 * LANES + 2 * SWEEPERS);
-    if (configured.run([&] { return cudaFuncSetAttribute(tile_sweep_kernel<F, KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess; }) != G2D_OK)
+    const size_t smem = sizeof(F) * (4 * TILE * LD + 2 * NSUB * DBLK + 3 * SUB * LANES + NSUB * SUB * ZLD) + sizeof(unsigned) * (2 * LANES + 2 * SWEEPERS);
+    // and the largest carve-out, so that the update kernels' CTAs find room beside a tile's on any SM (and the other way round)
+    if (configured.run([&] {
+            return cudaFuncSetAttribute(tile_sweep_kernel<F, KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess &&
+                   cudaFuncSetAttribute(tile_sweep_kernel<F, KIND>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared) == cudaSuccess;
+        }) != G2D_OK)
         return G2D_ERR_CUDA;
     const int i_lo = S - args.nJ + 1 > 0 ? S - args.nJ + 1 : 0;
     const int i_hi = S + 1 < args.nI ? S + 1 : args.nI;
