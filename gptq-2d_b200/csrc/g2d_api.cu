@@ -271,7 +271,9 @@ constexpr int kFarLagMacro = 2;  // a far update reaches the macro anti-diagonal
 
 // Pipelined schedule (float, tensor cores): one tile launch per tile anti-diagonal, and the feedback between tiles
 // carried by three mechanisms with growing lag, so that only the tile launches remain on the critical path:
-//   * a tile applies the feedback of its two neighbours of the previous anti-diagonal itself, as it loads;
+//   * a tile hands the feedback for its lower and its right neighbour on itself: its helper warps form the two products
+//     from shared memory while the tile is swept and store them into planes of their own, which the neighbours add as they
+//     load one launch later;
 //   * near update of the tile anti-diagonal s (its tiles as sources, targets from s + 2 on), on a side stream,
 //     concurrent with the tile launch of s + 1;
 //   * far update of a group of macro anti-diagonals (128 x 128 macro tiles = 2 x 2 tiles; rank 512 by default), on a
@@ -282,7 +284,10 @@ constexpr int kFarLagMacro = 2;  // a far update reaches the macro anti-diagonal
 //     hundred macro tiles: short, and the only part the tile launches have to wait for soon), then everything beyond
 //     them, which the tile launches only need a whole group later.
 // The tile launches run on a stream of the library's own with the highest priority, the near updates below it, the far
-// updates lowest: a CTA slot that frees up goes to the critical path first.  Updates that share target planes are
+// updates lowest: a CTA slot that frees up goes to the critical path first.  A CTA of the tile sweep fills the registers
+// of two of its SM's four schedulers (six warps of up to 240 registers), so no CTA of an update kernel ever shares an SM
+// with it: the updates run on the SMs that the tile launch of the moment leaves free, and the far update may as well use
+// its full three-stage ring there.  Updates that share target planes are
 // ordered on one stream, so the additions have a fixed order.
 int sweep_pipelined(const g2d_sweep_desc *d, SweepArgs<float> &a, const TcPlanes &planes, float *yf, float *cf, cudaStream_t caller,
                     LaunchTimer *timer, double *flops) {
@@ -339,13 +344,13 @@ int sweep_pipelined(const g2d_sweep_desc *d, SweepArgs<float> &a, const TcPlanes
             if (cudaStreamWaitEvent(lane->far, lane->swept[s & 7], 0) != cudaSuccess) return G2D_ERR_CUDA;
             const int t_first = W1 + kFarLagMacro, t_split = t_first + outer < waves_macro ? t_first + outer : waves_macro;
             if (timer) timer->begin_on(2, lane->far);
-            status = launch_macro_update_tc(&far_maps, planes, yf, cf, d->m, d->n, W1 - outer, W1, t_split, lane->far, t_first, 2);
+            status = launch_macro_update_tc(&far_maps, planes, yf, cf, d->m, d->n, W1 - outer, W1, t_split, lane->far, t_first, 3);
             if (timer) timer->end();
             if (status != G2D_OK) return status;
             if (cudaEventRecord(lane->far_first[g & 3], lane->far) != cudaSuccess) return G2D_ERR_CUDA;
             if (t_split < waves_macro) {
                 if (timer) timer->begin_on(2, lane->far);
-                status = launch_macro_update_tc(&far_maps, planes, yf, cf, d->m, d->n, W1 - outer, W1, waves_macro, lane->far, t_split, 2);
+                status = launch_macro_update_tc(&far_maps, planes, yf, cf, d->m, d->n, W1 - outer, W1, waves_macro, lane->far, t_split, 3);
                 if (timer) timer->end();
                 if (status != G2D_OK) return status;
             }

@@ -18,7 +18,7 @@ namespace g2d {
 constexpr int BN = 64;                               // N of the MMA: one tile
 constexpr int B_TILE_BYTES = BN * KC * 4;            // 8 KB
 constexpr int BAND_STAGE_BYTES = 2 * TILE_BYTES + 2 * B_TILE_BYTES;  // A_hi, A_lo, B_hi, B_lo
-constexpr int BAND_STAGES = 1;  // 48 KB: the updates are short and latency-bound, so several CTAs per SM beside one of the tile sweep
+constexpr int BAND_STAGES = 1;  // 48 KB: the updates are short and latency-bound, so several CTAs per SM
 constexpr uint32_t BAND_TMEM_COLS = 64;
 // D fp32, A and B tf32, both K-major, M = 128, N = 64
 constexpr uint32_t IDESC_N64 = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(MT >> 4) << 24);
@@ -182,8 +182,9 @@ int band_tc_prepare(BandTcMaps *opaque, const TcPlanes &pl, int64_t m, int64_t n
         !make_map(&maps->c_hi, pl.c_hi, m, n, BN) || !make_map(&maps->c_lo, pl.c_lo, m, n, BN))
         return G2D_ERR_CUDA;
     static PerDeviceOnce configured;
-    // The kernels of the pipelined schedule share SMs.  Each asks for the largest shared-memory carve-out: an SM that a
-    // kernel with a smaller one had configured takes no CTA of another kernel beside it until it has drained.
+    // Several CTAs of this kernel share an SM, with one another and with other kernels' CTAs.  It asks for the largest
+    // shared-memory carve-out: an SM that a kernel with a smaller one had configured takes no CTA beside it that needs
+    // more until it has drained.
     return configured.run([&] {
         return cudaFuncSetAttribute(band_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BAND_STAGES * BAND_STAGE_BYTES + 1024) == cudaSuccess &&
                cudaFuncSetAttribute(band_tc_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared) == cudaSuccess;

@@ -226,7 +226,7 @@ int tc_prepare_operands(const float *l, const float *u, int64_t m, int64_t n, co
 }
 
 // Sources: the macro anti-diagonals s0..s1-1; targets: t_first..s_end-1 (t_first >= s1).  `stages` 3 is the full pipeline
-// (one CTA per SM); 2 leaves room for a CTA of the tile sweep beside it (pipelined schedule).
+// (one CTA per SM); 2 leaves shared memory for CTAs of other kernels beside it.
 static_assert(sizeof(TcMaps) <= sizeof(MacroTcMaps), "opaque tensor-map storage is too small");
 
 // Tensor maps of one sweep (encoded once, reused by every macro update of the sweep) and the kernels' one-time set-up.

@@ -719,7 +719,7 @@ static int launch_kind(const SweepArgs<F> &args, int S, int parity, cudaStream_t
     // the opt-in to more than 48 KB of dynamic shared memory is per device
     static PerDeviceOnce configured;
     const size_t smem = sizeof(F) * (4 * TILE * LD + 2 * NSUB * DBLK + 3 * SUB * LANES + NSUB * SUB * ZLD) + sizeof(unsigned) * (2 * LANES + 2 * SWEEPERS);
-    // and the largest carve-out, so that the update kernels' CTAs find room beside a tile's on any SM (and the other way round)
+    // and the largest shared-memory carve-out, like the update kernels that run on the neighbouring SMs
     if (configured.run([&] {
             return cudaFuncSetAttribute(tile_sweep_kernel<F, KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess &&
                    cudaFuncSetAttribute(tile_sweep_kernel<F, KIND>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared) == cudaSuccess;
