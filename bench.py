@@ -469,6 +469,16 @@ def main() -> None:
     _abi.check(lib.g2d_sweep_fused_profile(ctypes.byref(desc), torch.cuda.current_stream().cuda_stream, prof), "profile")
     assert torch.equal(y, z), "the profiled pass must reproduce the timed result"
     tile_ms, near_ms, far_ms, tile_n, near_n, far_n, total_flops, near_flops, far_flops = list(prof)
+    # the same far-update kernel with the GPU to itself: one pass of the macro schedule (everything on one stream, so no
+    # other kernel runs beside it); tells the kernel's own rate from what its low priority costs it in the pipelined schedule
+    y_alone = w.clone()
+    desc.y, desc.reserved = y_alone.data_ptr(), 2
+    prof_alone = (ctypes.c_double * 9)()
+    _abi.check(lib.g2d_sweep_fused_profile(ctypes.byref(desc), torch.cuda.current_stream().cuda_stream, prof_alone), "profile of the macro schedule")
+    desc.y, desc.reserved = y.data_ptr(), 0
+    alone_ms, alone_n, alone_flops = prof_alone[2], prof_alone[5], prof_alone[8]
+    alone_tflops = alone_flops / (alone_ms * 1e-3) / 1e12 if alone_ms > 0 else 0.0
+    del y_alone
     pk = peaks()
     tensor_peak = pk["bf16_tflops_sustained"] / 6.0  # fp32-faithful tensor roofline: TF32 = bf16 / 2, three TF32 products per fp32 product
     far_tflops = far_flops / (far_ms * 1e-3) / 1e12 if far_ms > 0 else 0.0
@@ -479,7 +489,7 @@ def main() -> None:
     rtn = torch.clamp(torch.round(w / scale), -8, 7) * scale
     objective_vs_rtn = synthetic.objective(z, w, g, h) / synthetic.objective(rtn, w, g, h)
     roofline = {
-        "bound": "tensor", "kernel": "macro_update_tc_kernel (tcgen05 kind::tf32, 3xTF32 split; far updates, running beside the tile launches)",
+        "bound": "tensor", "kernel": "macro_update_tc_kernel (tcgen05 kind::tf32, 3xTF32 split; far updates: the lowest-priority stream of three, on the SMs that the tile launch of the moment leaves free)",
         "achieved": far_tflops, "peak": tensor_peak, "unit": "TFLOP/s", "frac": far_tflops / tensor_peak if tensor_peak else None,
         # DRAM bytes of one launch are not measured live: an ncu capture of this kernel at 4096 x 4096 read and wrote
         # 149.7 MB for 946 target macro tiles; that figure scaled by the target tiles of an average launch here
@@ -492,6 +502,9 @@ def main() -> None:
         "panel_gemms": {"what": "near + far updates: their algorithmic flops over their summed stream time", "achieved": panel_tflops,
                         "frac": panel_tflops / tensor_peak if tensor_peak else None, "algorithmic_flops": near_flops + far_flops,
                         "share_of_sweep_flops": (near_flops + far_flops) / total_flops if total_flops else None},
+        "far_kernel_alone": {"what": "the same kernel in the macro schedule of the same matrix: one stream, nothing beside it", "achieved": alone_tflops,
+                             "frac": alone_tflops / tensor_peak if tensor_peak else None, "launches": int(alone_n),
+                             "avg_launch_ms": alone_ms / alone_n if alone_n else None, "algorithmic_flops": alone_flops},
         "launches": int(far_n), "avg_launch_ms": far_ms / far_n if far_n else None,
         "algorithmic_flops_per_launch": far_flops / far_n if far_n else None,
         "kernel_ms": {"tile_sweep": tile_ms, "near_update": near_ms, "far_update": far_ms},
@@ -499,7 +512,7 @@ def main() -> None:
         "whole_sweep_tflops": sweep_flops(m, n) / (parts["sweep"] * 1e-3) / 1e12,
         "prep_tflops": 2 * (2 * float(n) ** 3 / 3) / (parts["prep"] * 1e-3) / 1e12,
         "timed_in": "separate profiled pass of the same step inside bench.py, one CUDA event pair per launch on the launching stream",
-        # the critical path: one tile launch per tile anti-diagonal, each a chain of 7 x 31 dependent rounding stages;
+        # the critical path: one tile launch per tile anti-diagonal, each a chain of 7 x 32 dependent rounding stages;
         # bound by that latency, not by memory or arithmetic throughput
         "critical_path": {"kernel": "tile_sweep_kernel", "launches": int(tile_n), "avg_launch_us": 1e3 * tile_ms / tile_n if tile_n else None,
                           "bound": "latency"},
