@@ -51,6 +51,8 @@ def config1(divide: int, device) -> dict:
     quantizer = functools.partial(Q.affine_quantizer_triton, qmin=-8, qmax=7)
     l, u = K.feedback_factors_from_grams(g, h, check=True)
     G.gptq_2d(w, l, u, quantizer=quantizer, quantizer_inputs=(scale, zero))  # module load, streams
+    K.feedback_factors_from_grams(g, h)  # the timed call once untimed: its workspace comes from the allocator's cache afterwards
+    torch.cuda.synchronize()
     (l, u), prep_ms = _timed(lambda: K.feedback_factors_from_grams(g, h))
     z, sweep_ms = _timed(lambda: G.gptq_2d(w, l, u, quantizer=quantizer, quantizer_inputs=(scale, zero)))
     K.check_pending()
@@ -92,7 +94,9 @@ def config2(divide: int, device) -> dict:
     K.feedback_factors_from_grams(g[:256, :256].contiguous(), h[:256, :256].contiguous())  # module load, streams
     G.gptq_2d(w[:256, :256].contiguous(), *K.feedback_factors_from_grams(g[:256, :256].contiguous(), g[:256, :256].contiguous()),
               quantizer=quantizer, quantizer_inputs=(scale[:256, :256].contiguous(), zero[:256, :256].contiguous()))
+    K.feedback_factors_from_grams(g, h, check=True)  # once untimed: the 30 GB of workspace come from the allocator's cache afterwards
     (l, u), prep_ms = _timed(lambda: K.feedback_factors_from_grams(g, h, check=True))
+    G.gptq_2d(w, l, u, quantizer=quantizer, quantizer_inputs=(scale, zero))
     z, sweep_ms = _timed(lambda: G.gptq_2d(w, l, u, quantizer=quantizer, quantizer_inputs=(scale, zero)))
     codes = torch.round(z / scale + zero)
     rtn = (torch.clamp(torch.round(w / scale + zero), 0, 7) - zero) * scale

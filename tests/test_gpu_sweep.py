@@ -156,7 +156,7 @@ def test_config0_fp32(api, schedule):
         assert (torch.round(z2 / scale) == expected_codes).double().mean().item() >= 0.999
 
 
-@pytest.mark.parametrize("m,n", [(256, 256), (1024, 1024), (320, 1100)])
+@pytest.mark.parametrize("m,n", [(256, 256), (1024, 1024), (320, 1100), (196, 332)])
 def test_teacher_forced_fp32(api, oracle, m, n, schedule):
     """Teacher-forced parity at fp32: with the rounding decisions imposed from the oracle's run, the engine's
     pre-rounding values must lead to the same codes except within 1e-5 code units of a tie."""
