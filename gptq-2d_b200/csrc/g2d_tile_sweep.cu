@@ -308,14 +308,21 @@ __global__ void __launch_bounds__(TTH) tile_sweep_kernel(SweepArgs<F> P, int S, 
                     }
                 }
                 if (pass == 0 && yfg != nullptr) {
-                    // the far planes, in a batch of their own so that no addition waits between two loads
-                    F fa[PER][4], fb[PER][4];
+                    // the far planes and what the left and the upper neighbour pushed one launch ago: all loads are
+                    // issued before the first addition, so that the tile waits for global memory once
+                    F fa[PER][4], fb[PER][4], na[PER][4], nb[PER][4];
 #pragma unroll
                     for (int t = 0; t < PER; ++t) {
                         const int idx = t * TTH + tid, r = idx / (TILE / 4), c = (idx % (TILE / 4)) * 4;
                         if (idx >= VECS) continue;
                         load4(yfg + (i0 + r) * n + j0 + c, fa[t]);
                         load4(cfg + (i0 + r) * n + j0 + c, fb[t]);
+                        if constexpr (PUSH) {
+#pragma unroll
+                            for (int x = 0; x < 4; ++x) na[t][x] = nb[t][x] = (F)0;
+                            if (gets_right) load4(yng + (i0 + r) * n + j0 + c, na[t]);
+                            if (gets_down) load4(cng + (i0 + r) * n + j0 + c, nb[t]);
+                        }
                     }
 #pragma unroll
                     for (int t = 0; t < PER; ++t) {
@@ -324,29 +331,9 @@ __global__ void __launch_bounds__(TTH) tile_sweep_kernel(SweepArgs<F> P, int S, 
                         for (int x = 0; x < 4; ++x) {
                             va[t][x] += fa[t][x];
                             vb[t][x] += fb[t][x];
-                        }
-                    }
-                }
-                if constexpr (PUSH) {
-                    if (pass == 0 && (gets_right || gets_down)) {
-                        // what the left and the upper neighbour pushed one launch ago
-                        F fa[PER][4], fb[PER][4];
-#pragma unroll
-                        for (int t = 0; t < PER; ++t) {
-                            const int idx = t * TTH + tid, r = idx / (TILE / 4), c = (idx % (TILE / 4)) * 4;
-                            if (idx >= VECS) continue;
-#pragma unroll
-                            for (int x = 0; x < 4; ++x) fa[t][x] = fb[t][x] = (F)0;
-                            if (gets_right) load4(yng + (i0 + r) * n + j0 + c, fa[t]);
-                            if (gets_down) load4(cng + (i0 + r) * n + j0 + c, fb[t]);
-                        }
-#pragma unroll
-                        for (int t = 0; t < PER; ++t) {
-                            if (t * TTH + tid >= VECS) continue;
-#pragma unroll
-                            for (int x = 0; x < 4; ++x) {
-                                va[t][x] += fa[t][x];
-                                vb[t][x] += fb[t][x];
+                            if constexpr (PUSH) {
+                                va[t][x] += na[t][x];
+                                vb[t][x] += nb[t][x];
                             }
                         }
                     }
@@ -539,9 +526,9 @@ __global__ void __launch_bounds__(TTH) tile_sweep_kernel(SweepArgs<F> P, int S, 
             F lb0[PUSH ? TILE / 4 : 1], lb1[PUSH ? TILE / 4 : 1];
             F yn0[PUSH ? NSUB : 1][4], yn1[PUSH ? NSUB : 1][4], y30[4], y31[4], c30[4], c31[4];
             if constexpr (PUSH) {
-    #pragma unroll
+#pragma unroll
                 for (int y = 0; y < 4; ++y) {
-    #pragma unroll
+#pragma unroll
                     for (int cb = 0; cb < NSUB; ++cb) yn0[cb][y] = yn1[cb][y] = (F)0;
                     y30[y] = y31[y] = c30[y] = c31[y] = (F)0;
                 }
@@ -560,7 +547,7 @@ __global__ void __launch_bounds__(TTH) tile_sweep_kernel(SweepArgs<F> P, int S, 
                 }
                 if constexpr (PUSH) {
                     const bool pvec = n % 4 == 0 && reinterpret_cast<uintptr_t>(yng) % (4 * sizeof(F)) == 0;
-                            if (owes_down && w == 1) {  // the strip of L[I + 1, I]: first used three anti-diagonals from here
+                    if (owes_down && w == 1) {  // the strip of L[I + 1, I]: first used three anti-diagonals from here
                         const int64_t gi = i0 + TILE + ap * SUB + (lane >> 2) * 2;
                         const bool lvec = m % 4 == 0 && reinterpret_cast<uintptr_t>(lg) % (4 * sizeof(F)) == 0;
 #pragma unroll
@@ -664,27 +651,61 @@ __global__ void __launch_bounds__(TTH) tile_sweep_kernel(SweepArgs<F> P, int S, 
         // ---- operands of the tensor-core macro updates: tf32 hi / lo of E (transposed) and of the completed C ----
         if (P.c_hi != nullptr) {
             if constexpr (sizeof(F) == sizeof(float)) {
-                for (int idx = tid; idx < TILE * TILE; idx += TTH) {
-                    {   // C[i][j], consecutive threads along j
-                        const int r = idx / TILE, c = idx % TILE;
-                        const int64_t gi = i0 + r, gj = j0 + c;
-                        if (gi < m && gj < n) {
-                            const float v = (float)Cs[r * LD + c];
-                            uint32_t h;
-                            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(v));
-                            P.c_hi[gi * n + gj] = __uint_as_float(h);
-                            P.c_lo[gi * n + gj] = v - __uint_as_float(h);
+                auto split4 = [](const float (&v)[4], float (&hi)[4], float (&lo)[4]) {
+#pragma unroll
+                    for (int x = 0; x < 4; ++x) {
+                        uint32_t h;
+                        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(v[x]));
+                        hi[x] = __uint_as_float(h);
+                        lo[x] = v[x] - hi[x];
+                    }
+                };
+                if (vec) {
+                    // whole tile, rows of 16-byte multiples: four entries per thread and store.  C along its rows; E
+                    // transposed: a thread gathers four rows of one column (consecutive threads take consecutive
+                    // columns, so the shared-memory reads do not collide) and writes them as one vector of a row of E^T
+                    for (int idx = tid; idx < TILE * TILE / 4; idx += TTH) {
+                        {
+                            const int r = idx / (TILE / 4), c = (idx % (TILE / 4)) * 4;
+                            float v[4], hi[4], lo[4];
+                            load4(reinterpret_cast<const float *>(Cs) + r * LD + c, v);
+                            split4(v, hi, lo);
+                            store4(P.c_hi + (i0 + r) * n + j0 + c, hi);
+                            store4(P.c_lo + (i0 + r) * n + j0 + c, lo);
+                        }
+                        {
+                            const int c = idx % TILE, r = (idx / TILE) * 4;
+                            float v[4], hi[4], lo[4];
+#pragma unroll
+                            for (int x = 0; x < 4; ++x) v[x] = (float)Ys[(r + x) * LD + c];
+                            split4(v, hi, lo);
+                            store4(P.et_hi + (j0 + c) * m + i0 + r, hi);
+                            store4(P.et_lo + (j0 + c) * m + i0 + r, lo);
                         }
                     }
-                    {   // E^T[j][i], consecutive threads along i
-                        const int c = idx / TILE, r = idx % TILE;
-                        const int64_t gi = i0 + r, gj = j0 + c;
-                        if (gi < m && gj < n) {
-                            const float v = (float)Ys[r * LD + c];
-                            uint32_t h;
-                            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(v));
-                            P.et_hi[gj * m + gi] = __uint_as_float(h);
-                            P.et_lo[gj * m + gi] = v - __uint_as_float(h);
+                } else {
+                    for (int idx = tid; idx < TILE * TILE; idx += TTH) {
+                        {   // C[i][j], consecutive threads along j
+                            const int r = idx / TILE, c = idx % TILE;
+                            const int64_t gi = i0 + r, gj = j0 + c;
+                            if (gi < m && gj < n) {
+                                const float v = (float)Cs[r * LD + c];
+                                uint32_t h;
+                                asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(v));
+                                P.c_hi[gi * n + gj] = __uint_as_float(h);
+                                P.c_lo[gi * n + gj] = v - __uint_as_float(h);
+                            }
+                        }
+                        {   // E^T[j][i], consecutive threads along i
+                            const int c = idx / TILE, r = idx % TILE;
+                            const int64_t gi = i0 + r, gj = j0 + c;
+                            if (gi < m && gj < n) {
+                                const float v = (float)Ys[r * LD + c];
+                                uint32_t h;
+                                asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(v));
+                                P.et_hi[gj * m + gi] = __uint_as_float(h);
+                                P.et_lo[gj * m + gi] = v - __uint_as_float(h);
+                            }
                         }
                     }
                 }
