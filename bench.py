@@ -55,12 +55,14 @@ def peaks() -> dict:
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs.  The sampler is started before
+    the warm-up steps (nvidia-smi needs a few hundred milliseconds to print its first line, about as long as ten
+    steps take) and every line is stamped on arrival; the summary keeps the lines that arrived inside the timed region."""
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index: int):
-        self.index, self.lines, self.proc = index, [], None
+        self.index, self.lines, self.stamps, self.proc = index, [], [], None
 
     def __enter__(self):
         try:
@@ -76,6 +78,7 @@ class ClockSampler:
     def _read(self):
         for line in self.proc.stdout:
             self.lines.append(line.strip())
+            self.stamps.append(time.monotonic())
 
     def __exit__(self, *exc):
         if self.proc is not None:
@@ -85,10 +88,20 @@ class ClockSampler:
             except subprocess.TimeoutExpired:
                 self.proc.kill()
 
-    def summary(self) -> dict:
+    def summary(self, window=None) -> dict:
+        """`window`: (start, end) on the time.monotonic clock; without a line inside it, the first line after it counts
+        (the GPU goes on working on the per-part timings then)."""
         sm, sm_max, reasons = [], [], set()
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        for line in self.lines:
+        lines = list(zip(self.stamps, self.lines))
+        if window is not None:
+            inside = [line for stamp, line in lines if window[0] <= stamp <= window[1] + 0.05]
+            if not inside:
+                inside = [line for stamp, line in lines if stamp > window[1]][:1]
+            chosen = inside
+        else:
+            chosen = [line for _, line in lines]
+        for line in chosen:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 9:
                 continue
@@ -284,7 +297,7 @@ def measure_tf32_peak(device) -> dict:
 def main() -> None:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=5)
+    parser.add_argument("--steps", type=int, default=None, help="timed steps; default 20 (about 0.65 s, several clock samples) and 5 for --impl reference (whose step is seconds of CPU work)")
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", default="ours", choices=("ours", "reference"))
     parser.add_argument("--size", type=int, default=8192)
@@ -293,6 +306,8 @@ def main() -> None:
     parser.add_argument("--no-peak-probe", action="store_true", help="skip the TF32 matrix-product measurement (for runs under a profiler)")
     parser.add_argument("--layer-set-blocks", type=int, default=8, help="blocks of the 70B-shaped layer set run after the timed steps (0: none)")
     args = parser.parse_args()
+    if args.steps is None:
+        args.steps = 5 if args.impl == "reference" else 20
     if args.impl == "reference":
         run_reference(args)
         return
@@ -345,20 +360,27 @@ def main() -> None:
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(args.warmup):
-        z = step(w)
-    barrier()
-    launches_before = lib.g2d_launch_count()
     begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local) as clocks:
+        for _ in range(args.warmup):
+            z = step(w)
         barrier()
+        launches_before = lib.g2d_launch_count()
+        window_start = time.monotonic()
         begin.record()
         for _ in range(args.steps):
             z = step(w)
         end.record()
         barrier()
+        window = (window_start, time.monotonic())
+        launches = lib.g2d_launch_count() - launches_before
+        for _ in range(3):  # keeps the GPU at work until the sampler has printed a line for certain
+            if any(window[0] <= stamp for stamp in clocks.stamps):
+                break
+            z_extra = step(w)
+            torch.cuda.synchronize()
+            del z_extra
     elapsed_ms = begin.elapsed_time(end)
-    launches = lib.g2d_launch_count() - launches_before
     if world > 1:
         t = torch.tensor([elapsed_ms], device=device, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -531,7 +553,7 @@ def main() -> None:
             "stages": m + n - 1, "sweep_us_per_stage": parts["sweep"] * 1e3 / (m + n - 1),
             "objective_vs_round_to_nearest": objective_vs_rtn, "status": "factor pivots and kernel wait flags read after the timed regions: clean",
         },
-        "clocks": clocks.summary(),
+        "clocks": clocks.summary(window),
         "e2e": {"value": e2e_ms / 1e3 / world, "unit": "s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "format": "LayerPipeline.quantize_from_host_packed: W float32, G and H as packed lower triangles in; INT4 codes and fp16 row scales out"},
         "e2e_float_io": {"value": e2e_float_ms / 1e3 / world, "unit": "s", "h2d_bytes_per_step": h2d_float, "d2h_bytes_per_step": d2h_float,
