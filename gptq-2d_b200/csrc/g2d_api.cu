@@ -267,7 +267,7 @@ double near_flops(int64_t m, int64_t n, int s, int t0, int t1, int outer_macro, 
     return flops;
 }
 
-constexpr int kFarLagMacro = 2;  // a far update reaches the macro anti-diagonals from this many past its group's end
+constexpr int kFarLagMacro = 1;  // a far update reaches the macro anti-diagonals from this many past its group's end (its first, short launch has two tile launches of time; measured against 2 and 3: less work for the near updates, the sweep 2 % shorter at 8192 x 8192 and unchanged at 2048 and 4096)
 
 // Pipelined schedule (float, tensor cores): one tile launch per tile anti-diagonal, and the feedback between tiles
 // carried by three mechanisms with growing lag, so that only the tile launches remain on the critical path:
@@ -278,7 +278,7 @@ constexpr int kFarLagMacro = 2;  // a far update reaches the macro anti-diagonal
 //     concurrent with the tile launch of s + 1;
 //   * far update of a group of macro anti-diagonals (128 x 128 macro tiles = 2 x 2 tiles; rank 512 by default), on a
 //     second side stream, into planes of its own that a tile adds when it loads.  It reaches the macro anti-diagonals
-//     from kFarLagMacro past the group's end, which the tile launches get to four launches after the group's last
+//     from kFarLagMacro past the group's end, which the tile launches get to two launches after the group's last
 //     tile; the near updates stop where the far update of their source's group starts.  A far update runs as two
 //     launches: first the macro anti-diagonals that the tile launches reach before the next group's update (a few
 //     hundred macro tiles: short, and the only part the tile launches have to wait for soon), then everything beyond
