@@ -184,12 +184,14 @@ def test_teacher_forced_fp32(api, oracle, m, n, schedule):
     assert (distance_to_tie[mismatch] <= 1e-5).all()
 
 
-def test_self_consistency_large_fp32(api, schedule):
+@pytest.mark.parametrize("m,n", [(2048, 3072), (1000, 1356)])
+def test_self_consistency_large_fp32(api, schedule, m, n):
     """Size-independent properties on a larger free run: Z is the quantizer applied to the engine's own
-    pre-rounding values, and Z - X = L E U with E = Z - Y_pre (the defining identity of the sweep)."""
+    pre-rounding values, and Z - X = L E U with E = Z - Y_pre (the defining identity of the sweep).  The second shape
+    ends in ragged tiles in both directions (multiples of 4, so every schedule takes it): the parameters of entries
+    outside the matrix and the feedback pushed to ragged neighbour tiles."""
     import _abi
     G, Q = api
-    m, n = 2048, 3072
     gen = torch.Generator(device="cuda").manual_seed(1)
     w = 0.02 * torch.randn(m, n, generator=gen, device="cuda")
     l = torch.tril(torch.randn(m, m, generator=gen, device="cuda") * (0.3 / m ** .5), -1)
